@@ -1,0 +1,106 @@
+// Execution context and buffer staging of the host layer code.
+//
+// Mirrors the contract of the reference's ExecutionContext / BufferWrapper
+// (include/execution_context.hpp:33-77, include/buffer_wrapper.hpp:46-122): a context carries the
+// caller's lookup and modify streams plus lazily grown, named scratch buffers; user buffers that
+// are not device memory are staged through that scratch with cudaMemcpyAsync on the stream of the
+// operation.  A context is not thread-safe; distinct contexts of one layer may run concurrently.
+#pragma once
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../common.hpp"
+
+namespace nve_b200 {
+
+class ContextRegistry;
+
+class ExecutionContext {
+ public:
+  ExecutionContext(int device, cudaStream_t lookup_stream, cudaStream_t modify_stream,
+                   std::shared_ptr<ContextRegistry> registry);
+  ~ExecutionContext();
+  ExecutionContext(const ExecutionContext&) = delete;
+  ExecutionContext& operator=(const ExecutionContext&) = delete;
+
+  cudaStream_t lookup_stream() const { return lookup_stream_; }
+  cudaStream_t modify_stream() const { return modify_stream_; }
+  int device() const { return device_; }
+
+  // Named scratch, grown on demand (never shrunk).  Growing a buffer waits for the device first,
+  // so earlier work that still reads the old allocation is safe.
+  void* scratch(const std::string& name, size_t bytes, bool pinned_host);
+
+  // Per-context device miss counter (int64), zeroed at creation.
+  int64_t* miss_counter();
+
+  // Blocks until both streams are idle.
+  void wait();
+
+ private:
+  struct Buffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    bool host = false;
+  };
+  int device_;
+  cudaStream_t lookup_stream_;
+  cudaStream_t modify_stream_;
+  std::shared_ptr<ContextRegistry> registry_;
+  std::mutex mu_;
+  std::map<std::string, Buffer> buffers_;
+  int64_t* miss_counter_ = nullptr;
+};
+
+using context_ptr_t = std::shared_ptr<ExecutionContext>;
+
+// Lookup streams of the live contexts of one layer / table, so that a modify operation can be
+// ordered after every lookup already enqueued (reference: ContextRegistry,
+// src/layer_utils.cpp:30-60).
+class ContextRegistry {
+ public:
+  void add(ExecutionContext* ctx);
+  void remove(ExecutionContext* ctx);
+  // Makes `waiter` wait for all work currently enqueued on every registered lookup stream.
+  void order_after_lookups(cudaStream_t waiter);
+  // Makes every registered lookup stream wait for `event`.
+  void lookups_wait_event(cudaEvent_t event);
+
+ private:
+  std::mutex mu_;
+  std::set<ExecutionContext*> contexts_;
+};
+
+enum class Residency { Device, Other };
+Residency residency_of(const void* ptr);
+
+// Device-visible view of a caller buffer.  A device pointer is used as is; anything else is
+// staged into context scratch `name` (contents copied when `copy_in`).
+struct Staged {
+  void* device = nullptr;   // pointer kernels use
+  void* user = nullptr;     // caller's pointer
+  size_t bytes = 0;
+  bool staged = false;
+  // Copies device -> user when staged (results of a lookup).
+  void copy_back(cudaStream_t stream) const;
+};
+Staged stage_in(ExecutionContext& ctx, const std::string& name, const void* user, size_t bytes,
+                bool copy_in, cudaStream_t stream);
+
+// RAII device selection.
+class ScopedDevice {
+ public:
+  explicit ScopedDevice(int device);
+  ~ScopedDevice();
+
+ private:
+  int prev_ = -1;
+  bool changed_ = false;
+};
+
+}  // namespace nve_b200

@@ -1,0 +1,17 @@
+// Instantiates the fused lookup+pool kernel for rows stored as F16 values.
+#include "lookup_pool.cuh"
+
+namespace nve_b200 {
+
+template <>
+void launch_lookup_pool<In::F16>(const PoolKernelParams& p, int vb, cudaStream_t stream) {
+  constexpr int EB = InTraits<In::F16>::kElemBytes;
+  switch (vb) {
+    case 16: launch_lookup_pool_vb<In::F16, 16>(p, stream); break;
+    case 8: launch_lookup_pool_vb<In::F16, 8>(p, stream); break;
+    case 4: launch_lookup_pool_vb<In::F16, 4>(p, stream); break;
+    default: launch_lookup_pool_vb<In::F16, EB>(p, stream); break;
+  }
+}
+
+}  // namespace nve_b200

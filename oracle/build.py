@@ -1,0 +1,106 @@
+"""Build recipe for the parity checker (test infrastructure, not the product).
+
+Two artefacts, both written under ``oracle/_ref/`` (git-ignored, shipped to the GPU box as built):
+
+* ``libnve_oracle.so``  – the plain-C restatement in ``oracle/nve_oracle.c`` (always built).
+* ``libnve_ref.so``     – the UNMODIFIED reference CPU path (HostEmbeddingLayer, LinearHostTable,
+  cpu_ops) compiled straight from the reference checkout, wrapped by ``oracle/ref_driver.cpp``.
+  Built only where the reference checkout is present; elsewhere the prebuilt file is used.
+
+No reference source is copied: the compiler reads the files where they lie.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+REFERENCE = Path(os.environ.get("NVE_REFERENCE_DIR", "/root/reference"))
+
+REF_SOURCES = [
+    "host_embedding_layer", "linear_host_table", "host_table", "host_table_detail", "table",
+    "layer_utils", "execution_context", "default_allocator", "thread_pool", "thread_pool_base",
+    "common", "numa_support", "insert_heuristic",
+]
+
+REF_DEFINES = [
+    "-DNVE_CACHE_LINE_SIZE=64", "-DNVE_DRIVERLESS_BUILD", "-DNVE_DISABLE_MPI",
+    "-DNVE_FEATURE_HT_KEY_64=1", "-DNVE_FEATURE_HT_KEY_32=1", "-DNVE_FEATURE_HT_PART_FNV1A=1",
+    "-DNVE_FEATURE_HT_KERNEL_8=1",
+]
+
+
+def _newer(target: Path, sources) -> bool:
+    if not target.exists():
+        return False
+    t = target.stat().st_mtime
+    return all(Path(s).stat().st_mtime <= t for s in sources)
+
+
+def _find_nlohmann() -> Path | None:
+    site = Path(sysconfig.get_paths()["purelib"])
+    cand = site / "include" / "cudnn_frontend" / "thirdparty"
+    if (cand / "nlohmann" / "json.hpp").exists():
+        return cand
+    for p in site.rglob("nlohmann/json.hpp"):
+        return p.parent.parent
+    return None
+
+
+def build_oracle(verbose: bool = False) -> Path:
+    """Compile the C restatement with gcc.  -ffp-contract=off keeps a*b+c unfused so that the
+    arithmetic is the same on every host the library is rebuilt on."""
+    OUT.mkdir(exist_ok=True)
+    src = HERE / "nve_oracle.c"
+    out = OUT / "libnve_oracle.so"
+    if _newer(out, [src]):
+        return out
+    cmd = ["gcc", "-std=c11", "-O2", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
+           "-Wall", "-Wextra", "-o", str(out), str(src), "-lm"]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return out
+
+
+def build_reference(verbose: bool = False) -> Path | None:
+    """Compile the reference CPU path from its own sources (only where the checkout exists)."""
+    OUT.mkdir(exist_ok=True)
+    out = OUT / "libnve_ref.so"
+    if not (REFERENCE / "src" / "host_embedding_layer.cpp").exists():
+        return out if out.exists() else None
+    driver = HERE / "ref_driver.cpp"
+    if _newer(out, [driver]):
+        return out
+    nl = _find_nlohmann()
+    if nl is None:
+        raise RuntimeError("nlohmann/json.hpp not found in site-packages")
+    shim = OUT / "shim" / "nlohmann"
+    shim.mkdir(parents=True, exist_ok=True)
+    (shim / "json_fwd.hpp").write_text("#pragma once\n#include <nlohmann/json.hpp>\n")
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    cmd = ["g++", "-std=c++17", "-O3", "-mavx2", "-fPIC", "-shared", "-w", *REF_DEFINES,
+           f"-I{REFERENCE}", f"-I{REFERENCE / 'include'}", f"-I{cuda_inc}", f"-I{nl}",
+           f"-I{shim.parent}", str(driver),
+           *[str(REFERENCE / "src" / f"{s}.cpp") for s in REF_SOURCES],
+           "-o", str(out),
+           f"-L{cuda_inc.parent / 'lib64'}", "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return out
+
+
+def build_all(verbose: bool = False):
+    return build_oracle(verbose), build_reference(verbose)
+
+
+if __name__ == "__main__":
+    o, r = build_all(verbose=True)
+    print("oracle:", o)
+    print("reference:", r)
+    sys.exit(0)

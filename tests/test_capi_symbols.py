@@ -1,0 +1,61 @@
+"""CPU checks of the C-ABI library: it loads, and it exports every symbol include/*.h declares."""
+import ctypes as C
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    names = set()
+    for hdr in sorted((ROOT / "include").glob("*.h")):
+        text = hdr.read_text()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        for m in re.finditer(r"NVE_C_API\s+[\w\s\*]+?\b(nve_\w+)\s*\(", text):
+            names.add(m.group(1))
+    return names
+
+
+def test_every_declared_symbol_is_exported(capi):
+    declared = _declared_symbols()
+    assert len(declared) >= 50
+    missing = [n for n in sorted(declared) if not hasattr(capi.lib, n)]
+    assert not missing, f"declared in include/*.h but not exported: {missing}"
+    unbound = sorted(declared - set(capi.PROTOTYPES))
+    assert not unbound, f"no ctypes prototype for: {unbound}"
+
+
+def test_versions_and_defaults(capi):
+    a, b, c = C.c_int32(), C.c_int32(), C.c_int32()
+    assert capi.lib.nve_version(C.byref(a), C.byref(b), C.byref(c)) == 0
+    assert (a.value, b.value) == (26, 9)
+    assert capi.lib.nve_abi_version(C.byref(a), C.byref(b)) == 0
+    assert (a.value, b.value) == (1, 0)
+    t = capi.lib.nve_gpu_table_config_default()
+    assert (t.count_misses, t.max_modify_size, t.uvm_cpu_accumulate, t.modify_on_gpu, t.invalid_key) == \
+        (1, 1 << 20, 1, 1, -1)
+    g = capi.lib.nve_gpu_embedding_layer_config_default()
+    assert g.default_row_index == -1 and g.value_dtype == 0
+    u = capi.lib.nve_linear_uvm_layer_config_default()
+    assert u.min_insert_size_gpu == 1 << 16 and u.default_row_index == -1
+
+
+def test_null_handles_are_invalid_argument(capi):
+    st = capi.lib.nve_layer_lookup(None, None, 0, None, None, 0, None, None)
+    assert st == capi.NVE_ERROR_INVALID_ARGUMENT
+    assert "must not be NULL" in capi.last_error()
+    assert capi.lib.nve_context_wait(None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    assert capi.lib.nve_table_find(None, None, 0, None, None, 0, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    assert capi.lib.nve_version(None, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    out = C.c_void_p()
+    assert capi.lib.nve_thread_pool_create(C.byref(out), b"{}") == capi.NVE_ERROR_NOT_IMPLEMENTED
+    assert capi.lib.nve_gpu_embedding_layer_create(None, 1, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
+
+
+def test_heuristic_handles(capi):
+    h = C.c_void_p()
+    assert capi.lib.nve_heuristic_create_never(C.byref(h)) == 0 and h.value
+    assert capi.lib.nve_heuristic_destroy(h) == 0
+    assert capi.lib.nve_heuristic_create_default(C.byref(h), None, 0) == 0
+    assert capi.lib.nve_heuristic_destroy(h) == 0
+    assert capi.lib.nve_heuristic_destroy(None) == capi.NVE_ERROR_INVALID_ARGUMENT
