@@ -369,8 +369,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tables", type=int, default=NUM_TABLES,
+                    help="tables per GPU (profiling runs use fewer; the benchmark config is 8)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    globals()["NUM_TABLES"] = max(1, min(8, args.tables))
     if args.impl == "reference":
         run_reference_arm(args)
     else:

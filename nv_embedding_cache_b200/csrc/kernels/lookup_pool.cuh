@@ -10,6 +10,8 @@
 // Bytes per bag: len * (key + row) read, one output row written.  Bound: HBM bandwidth.
 #pragma once
 
+#include <cstdlib>
+
 #include "device_common.cuh"
 
 namespace nve_b200 {
@@ -194,10 +196,21 @@ __global__ void __launch_bounds__(128) lookup_pool_kernel(const PoolKernelParams
 }
 
 // Chooses GROUP / VPL from the number of vectors per row and launches.
+// Threads per block of the pooled lookup.  Small blocks let the hardware scheduler backfill an SM
+// as soon as a few short bags finish; NVE_B200_POOL_BLOCK (32..128, multiple of 32) overrides.
+inline int pool_block_threads() {
+  static const int value = [] {
+    const char* e = std::getenv("NVE_B200_POOL_BLOCK");
+    const int v = e ? std::atoi(e) : 0;
+    return (v >= 32 && v <= 128 && v % 32 == 0) ? v : 128;
+  }();
+  return value;
+}
+
 template <In IN, int VB>
 void launch_lookup_pool_vb(const PoolKernelParams& p, cudaStream_t stream) {
   if (p.num_bags <= 0) return;
-  constexpr int BLOCK = 128;
+  const int BLOCK = pool_block_threads();
   auto grid_for = [&](int group) {
     return static_cast<unsigned>((p.num_bags * group + BLOCK - 1) / BLOCK);
   };

@@ -10,6 +10,7 @@ void launch_lookup_pool<In::F16>(const PoolKernelParams& p, int vb, cudaStream_t
     case 16: launch_lookup_pool_vb<In::F16, 16>(p, stream); break;
     case 8: launch_lookup_pool_vb<In::F16, 8>(p, stream); break;
     case 4: launch_lookup_pool_vb<In::F16, 4>(p, stream); break;
+    case 2: launch_lookup_pool_vb<In::F16, (EB <= 2 ? 2 : EB)>(p, stream); break;
     default: launch_lookup_pool_vb<In::F16, EB>(p, stream); break;
   }
 }
