@@ -114,6 +114,79 @@ NVE_C_API nve_status_t nve_b200_update_rows(void* table, int64_t num_rows, int64
                                             int64_t value_stride, int accumulate, int keys_unique,
                                             void* stream);
 
+/*
+ * Kernel-side view of a GPU cache table, for user kernels that probe the cache themselves.
+ * Replaces EmbedCacheBase::get_cache_data (include/ecache/embed_cache.h, used as in
+ * samples/ecache/simple_sample/simple_sample.cu:60-200).  `misses` points at the miss counter of
+ * `ctx`.  The view stays valid while the table lives; tags change under insert / erase.
+ */
+NVE_C_API nve_status_t nve_b200_gpu_table_get_cache_data(nve_table_t table, nve_context_t ctx,
+                                                         nve_b200_cache_data_t* out);
+
+/*
+ * Replacement-policy state of a GPU cache table: per-way counters [num_sets][8] (fp32) and the
+ * per-set insert number of the last touch [num_sets] (int64), both device pointers.  Exposed for
+ * inspection and parity tests (the reference keeps them in CacheSADeviceModify::d_counters_ /
+ * d_set_timestamps_, include/ecache/ec_set_associative_device_modify.cuh:476-485).
+ */
+NVE_C_API nve_status_t nve_b200_gpu_table_get_policy_state(nve_table_t table,
+                                                           const float** counters,
+                                                           const int64_t** set_timestamps);
+
+/*
+ * Insert keys whose rows are read from the table's backing (uvm) table, row = backing[key].
+ * Replaces GpuTable::insert_from_uvm (src/gpu_table.cu:494-576), which the reference exposes to
+ * C++ callers only.
+ */
+NVE_C_API nve_status_t nve_b200_gpu_table_insert_from_backing(nve_table_t table, nve_context_t ctx,
+                                                              int64_t n, const void* keys);
+
+/* ---- key de-duplication and gradient reduction ------------------------------------------ */
+typedef struct nve_b200_deduper_s* nve_b200_deduper_t;
+
+/*
+ * Deduper with its workspace for batches of up to max_keys keys (allocates device memory once,
+ * on the current device).  max_run_size: -1 keeps every group whole; a positive value splits the
+ * positions of a key into chunks of at most that many entries (the pynve binding uses 1024).
+ * Replaces Deduper<IndexT, MAX_RUN_SIZE> construction + get_alloc_requirements +
+ * set_and_init_buffers (cuda_ops/deduper.cuh:113-131, :224-310).
+ */
+NVE_C_API nve_status_t nve_b200_deduper_create(nve_b200_deduper_t* out, nve_key_type_t key_type,
+                                               int64_t max_run_size, int64_t max_keys);
+NVE_C_API nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t deduper);
+
+/*
+ * Replaces Deduper::dedup (cuda_ops/deduper.cuh:136-221), same outputs, every array of the key
+ * type:  d_unique_out[U] ascending distinct keys; d_counts_out[U]; d_inverse_buffer[n] positions
+ * grouped by key, ascending inside a group; d_offsets[C+1] chunk starts in the inverse buffer
+ * (C == U without splitting); d_loc_map_out[C] group of each chunk (only when splitting);
+ * h_num_runs_out[0] = U, [1] = C (host memory, valid on return: the call synchronises `stream`
+ * once).  Only the low `end_bit` bits of the keys take part in the ordering (0 = all bits).
+ */
+NVE_C_API nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t deduper, const void* d_keys,
+                                              int64_t num_keys, void* d_unique_out,
+                                              void* d_counts_out, void* d_loc_map_out,
+                                              void* h_num_runs_out, void* d_inverse_buffer,
+                                              void* d_offsets, void* stream, int32_t end_bit);
+
+/*
+ * Per-unique-key sum of fp32 gradient rows after a dedup() on the same deduper:
+ *   apply_to_table == 0:  d_dst[u] = sum over the positions of group u of d_grads[position]
+ *   apply_to_table != 0:  d_dst is a dense table: d_dst[unique[u]] += alpha * sum  (keys outside
+ *                         [0, table_rows) skipped) -- reduction fused with update_accumulate.
+ * Rows are summed in ascending position, chunk sums in chunk order, so the result is the same on
+ * every run.  Replaces DedupGradients / GradientDedup (cuda_ops/dedup_grads_kernel.cuh:56-253)
+ * and, in the fused form, the UpdateAccumulateTable call that follows it
+ * (cuda_ops/update_accumulate.cuh:61-251).  Uses scratch owned by the deduper for split groups.
+ */
+NVE_C_API nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t deduper, const void* d_grads,
+                                            int64_t grad_stride, int64_t row_bytes,
+                                            int64_t num_keys, const void* d_unique,
+                                            const void* d_inverse, const void* d_offsets,
+                                            const void* d_loc_map, void* d_dst, int64_t dst_stride,
+                                            int32_t apply_to_table, int64_t table_rows, float alpha,
+                                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -144,6 +144,14 @@ PROTOTYPES = {
     # kernel-level ABI (include/nve_b200_ops.h)
     "nve_b200_lookup_pool": (_i32, [C.POINTER(PoolArgs), _vp]),
     "nve_b200_gather_rows": (_i32, [C.POINTER(GatherArgs), _vp]),
+    "nve_b200_gpu_table_get_cache_data": (_i32, [_vp, _vp, C.POINTER(CacheData)]),
+    "nve_b200_gpu_table_get_policy_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "nve_b200_gpu_table_insert_from_backing": (_i32, [_vp, _vp, _i64, _vp]),
+    "nve_b200_deduper_create": (_i32, [C.POINTER(_vp), C.c_int, _i64, _i64]),
+    "nve_b200_deduper_destroy": (_i32, [_vp]),
+    "nve_b200_deduper_dedup": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32]),
+    "nve_b200_dedup_grads": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
+                                     _i32, _i64, C.c_float, _vp]),
     "nve_b200_update_rows": (_i32, [_vp, _i64, _i64, _i32, _i64, C.c_int, _vp, _i64, _vp, _i64,
                                      C.c_int, C.c_int, _vp]),
 }

@@ -225,6 +225,23 @@ nve_status_t nve_table_get_lookup_counter(const nve_table_t table, nve_context_t
   return guarded([&] { table->ptr->get_lookup_counter(ctx->ptr, counter); });
 }
 
+// ---- GPU cache table extensions (include/nve_b200_ops.h) ----
+nve_status_t nve_b200_gpu_table_get_cache_data(nve_table_t table, nve_context_t ctx,
+                                               nve_b200_cache_data_t* out) {
+  if (!table || !table->ptr || !ctx || !ctx->ptr || !out) return bad_arg("table, ctx and out must not be NULL");
+  return guarded([&] { nve_b200::gpu_table_cache_data(*table->ptr, *ctx->ptr, out); });
+}
+nve_status_t nve_b200_gpu_table_get_policy_state(nve_table_t table, const float** counters,
+                                                 const int64_t** set_timestamps) {
+  if (!table || !table->ptr) return bad_arg("table must not be NULL");
+  return guarded([&] { nve_b200::gpu_table_policy_state(*table->ptr, counters, set_timestamps); });
+}
+nve_status_t nve_b200_gpu_table_insert_from_backing(nve_table_t table, nve_context_t ctx,
+                                                    int64_t n, const void* keys) {
+  NVE_TABLE_CTX_CHECK();
+  return guarded([&] { nve_b200::gpu_table_insert_from_backing(*table->ptr, ctx->ptr, n, keys); });
+}
+
 // ---- host-table plugins ----
 nve_status_t nve_create_table_factory(nve_table_factory_t*, const char*, const char*) { return not_impl("nve_create_table_factory"); }
 nve_status_t nve_table_factory_destroy(nve_table_factory_t) { return not_impl("nve_table_factory_destroy"); }

@@ -1,0 +1,132 @@
+// C ABI of the Deduper and the gradient reduction (include/nve_b200_ops.h).
+#include <algorithm>
+#include <cstring>
+
+#include "../kernels/dedup.cuh"
+#include "context.hpp"
+
+struct nve_b200_deduper_s {
+  nve_key_type_t key_type;
+  int64_t max_run;
+  int64_t capacity;
+  int device;
+  void* workspace = nullptr;
+  void* pinned = nullptr;      // {U, C}
+  float* partial = nullptr;    // partial sums of split groups
+  int64_t partial_rows = 0;
+  int64_t partial_row_bytes = 0;
+};
+
+namespace nve_b200 {
+namespace {
+
+void ensure_partial(nve_b200_deduper_s* d, int64_t n, int64_t row_bytes) {
+  if (d->max_run <= 0) return;
+  const int64_t rows = 2 * (n / d->max_run + 1) + 2;
+  if (rows <= d->partial_rows && row_bytes <= d->partial_row_bytes) return;
+  if (d->partial) {
+    NVE_B200_CUDA(cudaDeviceSynchronize());
+    NVE_B200_CUDA(cudaFree(d->partial));
+    d->partial = nullptr;
+  }
+  d->partial_rows = std::max(rows, d->partial_rows);
+  d->partial_row_bytes = std::max(row_bytes, d->partial_row_bytes);
+  NVE_B200_CUDA(cudaMalloc(&d->partial, size_t(d->partial_rows) * size_t(d->partial_row_bytes)));
+}
+
+}  // namespace
+}  // namespace nve_b200
+
+using nve_b200::guarded;
+using nve_b200::set_last_error;
+
+extern "C" {
+
+nve_status_t nve_b200_deduper_create(nve_b200_deduper_t* out, nve_key_type_t key_type,
+                                     int64_t max_run_size, int64_t max_keys) {
+  if (!out) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "out must not be NULL");
+  return guarded([&] {
+    NVE_B200_ARG(key_type == NVE_KEY_INT32 || key_type == NVE_KEY_INT64, "Unsupported key type");
+    NVE_B200_ARG(max_keys > 0 && max_keys < (int64_t{1} << 31), "max_keys out of range");
+    NVE_B200_ARG(max_run_size == -1 || max_run_size > 0, "max_run_size must be -1 or positive");
+    auto d = std::make_unique<nve_b200_deduper_s>();
+    d->key_type = key_type;
+    d->max_run = max_run_size;
+    d->capacity = max_keys;
+    NVE_B200_CUDA(cudaGetDevice(&d->device));
+    NVE_B200_CUDA(cudaMalloc(&d->workspace, nve_b200::dedup_workspace_bytes(key_type, max_keys)));
+    NVE_B200_CUDA(cudaMallocHost(&d->pinned, 16));
+    *out = d.release();
+  });
+}
+
+nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t d) {
+  if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
+  (void)cudaFree(d->workspace);
+  (void)cudaFreeHost(d->pinned);
+  if (d->partial) (void)cudaFree(d->partial);
+  (void)cudaGetLastError();
+  delete d;
+  return NVE_SUCCESS;
+}
+
+nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, int64_t num_keys,
+                                    void* d_unique_out, void* d_counts_out, void* d_loc_map_out,
+                                    void* h_num_runs_out, void* d_inverse_buffer, void* d_offsets,
+                                    void* stream, int32_t end_bit) {
+  if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
+  return guarded([&] {
+    const int kb = nve_b200::key_bytes(d->key_type);
+    NVE_B200_ARG(num_keys >= 0, "negative key count");
+    NVE_B200_ARG(num_keys <= d->capacity,
+                 "dedup called with more keys than the deduper was created for");
+    NVE_B200_ARG(h_num_runs_out != nullptr, "h_num_runs_out must not be NULL");
+    if (end_bit <= 0 || end_bit > kb * 8) end_bit = kb * 8;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (num_keys == 0) {
+      std::memset(h_num_runs_out, 0, size_t(2) * kb);
+      if (d_offsets) NVE_B200_CUDA(cudaMemsetAsync(d_offsets, 0, kb, s));
+      NVE_B200_CUDA(cudaMemsetAsync(const_cast<void*>(nve_b200::dedup_device_num_runs(
+                                        d->key_type, d->workspace, d->capacity)),
+                                    0, size_t(2) * kb, s));
+      return;
+    }
+    NVE_B200_ARG(d_keys && d_unique_out && d_counts_out && d_inverse_buffer && d_offsets,
+                 "dedup: NULL buffer");
+    NVE_B200_ARG(d->max_run <= 0 || d_loc_map_out != nullptr,
+                 "dedup: d_loc_map_out is required when runs are split");
+    nve_b200::dedup_run(d->key_type, d->workspace, d->capacity, d_keys, num_keys, d_unique_out,
+                        d_counts_out, d_loc_map_out, d_inverse_buffer, d_offsets, d->max_run,
+                        end_bit, d->pinned, s);
+    NVE_B200_CUDA(cudaStreamSynchronize(s));  // the counts are part of the return value
+    std::memcpy(h_num_runs_out, d->pinned, size_t(2) * kb);
+  });
+}
+
+nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int64_t grad_stride,
+                                  int64_t row_bytes, int64_t num_keys, const void* d_unique,
+                                  const void* d_inverse, const void* d_offsets,
+                                  const void* d_loc_map, void* d_dst, int64_t dst_stride,
+                                  int32_t apply_to_table, int64_t table_rows, float alpha,
+                                  void* stream) {
+  if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
+  return guarded([&] {
+    if (num_keys <= 0) return;
+    NVE_B200_ARG(d_grads && d_inverse && d_offsets && d_dst, "dedup_grads: NULL buffer");
+    NVE_B200_ARG(!apply_to_table || d_unique != nullptr, "dedup_grads: unique keys are required");
+    NVE_B200_ARG(d->max_run <= 0 || d_loc_map != nullptr,
+                 "dedup_grads: the chunk map is required when runs are split");
+    nve_b200::ensure_partial(d, num_keys, row_bytes);
+    // chunks <= unique + n / max_run <= n + n / max_run
+    const int64_t max_chunks = d->max_run > 0 ? num_keys + num_keys / d->max_run + 1 : num_keys;
+    nve_b200::dedup_grads_run(
+        d->key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
+        d->max_run > 0 ? d_loc_map : nullptr, d_unique,
+        nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
+        dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
+        d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0,
+        static_cast<cudaStream_t>(stream));
+  });
+}
+
+}  // extern "C"

@@ -1,14 +1,545 @@
-#include "tables.hpp"
+// GPU cache table (nve_gpu_table_create): a set-associative cache in HBM, optionally in front of
+// a linear backing table that may live in device, managed or pinned host memory.
+//
+// Mirrors the contract of the reference's GpuTable<KeyType> (src/gpu_table.cu:194-1104,
+// include/gpu_table.hpp:44-74) with its device-side modify policy (modify_on_gpu = true, the
+// pynve default).  Differences in mechanism, not in results:
+//   * no host synchronisation inside insert / update / erase: lookups enqueued after a modify wait
+//     (on the device) for that modify's tag invalidation, and the modify waits (on the device) for
+//     every lookup enqueued before it, which gives the reference's invalidate -> drain -> copy ->
+//     commit guarantee without stalling the calling thread;
+//   * the backing-table write-through of update / update_accumulate always runs as a GPU kernel.
+#include <algorithm>
+#include <mutex>
+
+#include "../kernels/cache_modify.cuh"
 #include "layers.hpp"
+#include "ops_internal.hpp"
+#include "tables.hpp"
 
 namespace nve_b200 {
 
-std::shared_ptr<Table> make_gpu_table(const nve_gpu_table_config_t&, nve_key_type_t) {
-  throw NotImplemented("GPU cache table: not built yet");
+namespace {
+
+constexpr int kWays = 8;
+constexpr float kDecayRate = 0.95f;  // reference include/ecache/ec_set_associative.h:120
+
+inline uint64_t align16(uint64_t x) { return (x + 15u) & ~uint64_t{15}; }
+
+class GpuTable : public Table {
+ public:
+  GpuTable(const nve_gpu_table_config_t& cfg, nve_key_type_t key_type)
+      : cfg_(cfg), key_type_(key_type) {
+    NVE_B200_CHECK(cfg.row_size_in_bytes > 0 && cfg.row_size_in_bytes % 2 == 0,
+                   "Invalid cache row size (must divide by 2)");
+    NVE_B200_CHECK(cfg.uvm_table == nullptr || cfg.uvm_num_rows > 0,
+                   "uvm_num_rows must be set to the number of rows in uvm_table");
+    if (!cfg.modify_on_gpu) {
+      throw NotImplemented("host-side cache modification (modify_on_gpu = 0) is not provided");
+    }
+    if (cfg.data_storage_on_host) {
+      throw NotImplemented("cache data storage on host is not provided");
+    }
+    const int kb = key_bytes(key_type);
+    // sets that fit: tags + rows + counters per set, each rounded up to 16 bytes
+    // (reference include/ecache/ec_set_associative.h:666-685, device-modify counters
+    //  include/ecache/ec_set_associative_device_modify.cuh:472-474)
+    const uint64_t per_set = align16(uint64_t(kWays) * kb) +
+                             align16(uint64_t(kWays) * cfg.row_size_in_bytes) +
+                             align16(uint64_t(kWays) * sizeof(float));
+    const uint64_t sets = cfg.cache_size / per_set;
+    NVE_B200_CHECK(sets > 0, "Failed to Init cache: memory allocated to cache too small");
+    NVE_B200_CHECK(sets <= 0xffffffffull, "cache has too many sets");
+    num_sets_ = static_cast<uint32_t>(sets);
+    hash_.num_sets = num_sets_;
+    fast_div_params(num_sets_, &hash_.magic, &hash_.shift);
+
+    ScopedDevice sd(cfg_.device_id);
+    const size_t lines = size_t(num_sets_) * kWays;
+    NVE_B200_CUDA(cudaMalloc(&cs_.tags, lines * kb));
+    NVE_B200_CUDA(cudaMalloc(&cs_.data, lines * size_t(cfg.row_size_in_bytes)));
+    NVE_B200_CUDA(cudaMalloc(&cs_.counters, lines * sizeof(float)));
+    NVE_B200_CUDA(cudaMalloc(&cs_.set_ts, size_t(num_sets_) * sizeof(int64_t)));
+    cs_.row_bytes = cfg.row_size_in_bytes;
+    cs_.sentinel = cfg.invalid_key;
+    cache_clear(cs_, key_type_, num_sets_, nullptr);
+    NVE_B200_CUDA(cudaStreamSynchronize(nullptr));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&invalidate_done_, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&modify_done_, cudaEventDisableTiming));
+    contexts_ = std::make_shared<ContextRegistry>();
+  }
+
+  ~GpuTable() override {
+    int prev = -1;
+    (void)cudaGetDevice(&prev);
+    (void)cudaSetDevice(cfg_.device_id);
+    (void)cudaDeviceSynchronize();
+    (void)cudaFree(cs_.tags);
+    (void)cudaFree(cs_.data);
+    (void)cudaFree(cs_.counters);
+    (void)cudaFree(cs_.set_ts);
+    if (invalidate_done_) (void)cudaEventDestroy(invalidate_done_);
+    if (modify_done_) (void)cudaEventDestroy(modify_done_);
+    if (prev >= 0) (void)cudaSetDevice(prev);
+    (void)cudaGetLastError();
+  }
+
+  const nve_gpu_table_config_t& config() const { return cfg_; }
+  nve_key_type_t key_type() const { return key_type_; }
+
+  nve_b200_cache_data_t cache_view(ExecutionContext& ctx) const {
+    nve_b200_cache_data_t v{};
+    v.cache_ptr = reinterpret_cast<int8_t*>(cs_.data);
+    v.tags_ptr = reinterpret_cast<const int8_t*>(cs_.tags);
+    v.num_sets = num_sets_;
+    v.row_size_in_bytes = static_cast<uint64_t>(cfg_.row_size_in_bytes);
+    v.count_misses = cfg_.count_misses != 0;
+    v.misses = ctx.miss_counter();
+    return v;
+  }
+
+  // Every lookup must see the tag invalidation of the modifies enqueued before it.
+  void order_lookup(cudaStream_t lookup_stream) {
+    std::lock_guard<std::mutex> lock(order_mu_);
+    NVE_B200_CUDA(cudaStreamWaitEvent(lookup_stream, invalidate_done_, 0));
+  }
+
+  // ---- Table interface -----------------------------------------------------------------
+  void find(context_ptr_t& ctx, int64_t n, const void* keys, uint64_t* hit_mask,
+            int64_t value_stride, void* values, int64_t* value_sizes) override {
+    ScopedDevice sd(cfg_.device_id);
+    NVE_B200_CHECK(value_sizes == nullptr, "value_sizes must be nullptr for GPU table");
+    if (n <= 0) return;
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.lookup_stream();
+    const Staged d_keys = stage_in(c, "keys", keys, size_t(n) * key_bytes(key_type_), true, s);
+    const size_t mask_bytes = size_t((n + 63) / 64) * 8;
+    Staged d_mask;
+    if (hit_mask && !cfg_.uvm_table) d_mask = stage_in(c, "hit_mask", hit_mask, mask_bytes, true, s);
+    Staged d_vals;
+    if (values) d_vals = stage_in(c, "values", values, size_t(n) * value_stride, false, s);
+    find_device(c, n, d_keys.device, static_cast<uint64_t*>(d_mask.device), value_stride,
+                d_vals.device, -1, s);
+    d_vals.copy_back(s);
+    d_mask.copy_back(s);
+  }
+
+  // Device-pointer core of find(); also used by the cached layer (default_row fused in).
+  void find_device(ExecutionContext& c, int64_t n, const void* d_keys, uint64_t* d_hit_mask,
+                   int64_t value_stride, void* d_values, int64_t default_row, cudaStream_t s) {
+    nve_b200_cache_data_t view = cache_view(c);
+    nve_b200_gather_args_t g{};
+    g.table = cfg_.uvm_table;
+    g.num_rows = cfg_.uvm_num_rows;
+    g.row_stride = cfg_.row_size_in_bytes;
+    g.value_dtype = cfg_.value_dtype;
+    g.default_row_index = default_row;
+    g.cache = &view;
+    g.key_type = key_type_;
+    g.keys = d_keys;
+    g.num_keys = n;
+    g.output = d_values;
+    g.output_stride = value_stride;
+    g.output_dtype = cfg_.value_dtype;   // raw rows
+    g.row_copy_bytes = cfg_.row_size_in_bytes;
+    g.hit_mask = d_hit_mask;
+    order_lookup(s);
+    gather_rows(g, cfg_.invalid_key, s);
+  }
+
+  void insert(context_ptr_t& ctx, int64_t n, const void* keys, int64_t value_stride,
+              int64_t value_size, const void* values) override {
+    if (n <= 0) return;
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    NVE_B200_CHECK(values != nullptr, "Invalid cache insert params");
+    NVE_B200_CHECK(value_size == cfg_.row_size_in_bytes, "Unsupported value_size");
+    insert_impl(ctx, n, keys, values, value_stride, false);
+  }
+
+  // Rows come from the backing table (reference insert_from_uvm, src/gpu_table.cu:494-576).
+  void insert_from_table(context_ptr_t& ctx, int64_t n, const void* keys) {
+    if (n <= 0) return;
+    NVE_B200_CHECK(cfg_.uvm_table != nullptr, "insert_from_uvm requires a UVM table");
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    insert_impl(ctx, n, keys, nullptr, cfg_.row_size_in_bytes, true);
+  }
+
+  void update(context_ptr_t& ctx, int64_t n, const void* keys, int64_t stride, int64_t size,
+              const void* values) override {
+    if (n <= 0) return;
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    NVE_B200_CHECK(values != nullptr, "Invalid cache update params");
+    NVE_B200_CHECK(size == cfg_.row_size_in_bytes, "Unsupported update_size");
+    modify_resident(ctx, n, keys, values, stride, /*mode=*/0, cfg_.value_dtype);
+  }
+
+  void update_accumulate(context_ptr_t& ctx, int64_t n, const void* keys, int64_t stride,
+                         int64_t size, const void* updates, nve_data_type_t dtype) override {
+    if (n <= 0) return;
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    NVE_B200_CHECK(updates != nullptr, "Invalid cache accumulate params");
+    NVE_B200_CHECK(size == cfg_.row_size_in_bytes, "Row/update size mismatch");
+    NVE_B200_CHECK(dtype == NVE_DTYPE_FLOAT32 || dtype == NVE_DTYPE_FLOAT16,
+                   "Unsupported update type combination");
+    NVE_B200_CHECK(cfg_.value_dtype == dtype || cfg_.value_dtype == NVE_DTYPE_UNKNOWN,
+                   "Unsupported update type combination");
+    modify_resident(ctx, n, keys, updates, stride, dtype == NVE_DTYPE_FLOAT32 ? 1 : 2, dtype);
+  }
+
+  void erase(context_ptr_t& ctx, int64_t n, const void* keys) override {
+    if (n <= 0) return;
+    NVE_B200_ARG(keys != nullptr, "keys must not be null");
+    modify_resident(ctx, n, keys, nullptr, 0, /*mode=*/-1, cfg_.value_dtype);
+  }
+
+  void clear(context_ptr_t& ctx) override {
+    ScopedDevice sd(cfg_.device_id);
+    std::lock_guard<std::mutex> lock(modify_mu_);
+    const cudaStream_t s = ctx->modify_stream();
+    contexts_->order_after_lookups(s);
+    cache_clear(cs_, key_type_, num_sets_, s);
+    global_ts_ = 0;
+    publish_invalidate(s);
+  }
+
+  context_ptr_t create_execution_context(cudaStream_t lookup_stream,
+                                         cudaStream_t modify_stream) override {
+    return std::make_shared<ExecutionContext>(cfg_.device_id, lookup_stream, modify_stream,
+                                              contexts_);
+  }
+  int32_t get_device_id() const override { return cfg_.device_id; }
+  int64_t get_max_row_size() const override { return cfg_.row_size_in_bytes; }
+  int64_t get_key_size() const override { return key_bytes(key_type_); }
+
+  void reset_lookup_counter(context_ptr_t& ctx) override {
+    ScopedDevice sd(cfg_.device_id);
+    NVE_B200_CUDA(cudaMemsetAsync(ctx->miss_counter(), 0, sizeof(int64_t), ctx->lookup_stream()));
+  }
+  void get_lookup_counter(context_ptr_t& ctx, int64_t* counter) override {
+    ScopedDevice sd(cfg_.device_id);
+    // asynchronous on the lookup stream, like the reference: synchronise that stream before reading
+    NVE_B200_CUDA(cudaMemcpyAsync(counter, ctx->miss_counter(), sizeof(int64_t),
+                                  cudaMemcpyDeviceToHost, ctx->lookup_stream()));
+  }
+
+ private:
+  void publish_invalidate(cudaStream_t s) {
+    std::lock_guard<std::mutex> lock(order_mu_);
+    NVE_B200_CUDA(cudaEventRecord(invalidate_done_, s));
+  }
+
+  // Rows that kernels read through `values` must outlive the call: host buffers were staged
+  // into context scratch, device buffers belong to the caller (who must keep them until the
+  // modify stream has run).
+  void insert_impl(context_ptr_t& ctx, int64_t n, const void* keys, const void* values,
+                   int64_t value_stride, bool from_table) {
+    ScopedDevice sd(cfg_.device_id);
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.modify_stream();
+    const Staged d_keys = stage_in(c, "keys", keys, size_t(n) * key_bytes(key_type_), true, s);
+    const uint8_t* src = static_cast<const uint8_t*>(cfg_.uvm_table);
+    if (!from_table) {
+      src = static_cast<const uint8_t*>(
+          stage_in(c, "values", values, size_t(n) * value_stride, true, s).device);
+    }
+    void* scratch = c.scratch("cache_insert", cache_insert_scratch_bytes(key_type_, n), false);
+    auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(n) * sizeof(ModifyEntry), false));
+    auto* count = static_cast<uint32_t*>(c.scratch("cache_entry_count", 256, false));
+
+    std::lock_guard<std::mutex> lock(modify_mu_);
+    // an earlier modify of another context must be complete before this one reads the tags
+    NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
+    cache_insert_select(cs_, hash_, key_type_, d_keys.device, n, src, value_stride, from_table,
+                        std::max<int64_t>(cfg_.max_modify_size, 0), ++global_ts_, kDecayRate,
+                        scratch, entries, count, s);
+    const uint32_t cap = static_cast<uint32_t>(n);
+    commit_entries(s, entries, count, cap, /*mode=*/0, value_stride, src);
+  }
+
+  void modify_resident(context_ptr_t& ctx, int64_t n, const void* keys, const void* values,
+                       int64_t stride, int mode, nve_data_type_t dtype) {
+    ScopedDevice sd(cfg_.device_id);
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.modify_stream();
+    const Staged d_keys = stage_in(c, "keys", keys, size_t(n) * key_bytes(key_type_), true, s);
+    const uint8_t* d_vals = nullptr;
+    if (values) {
+      d_vals = static_cast<const uint8_t*>(
+          stage_in(c, "values", values, size_t(n) * stride, true, s).device);
+    }
+    // a key may sit in more than one way, so leave room for every way of every key
+    const uint32_t cap = static_cast<uint32_t>(std::min<int64_t>(n * kWays, 0x7fffffff));
+    auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(cap) * sizeof(ModifyEntry), false));
+    auto* count = static_cast<uint32_t*>(c.scratch("cache_entry_count", 256, false));
+
+    std::lock_guard<std::mutex> lock(modify_mu_);
+    NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
+    cache_find_resident(cs_, hash_, key_type_, d_keys.device, n, d_vals, stride, entries, count,
+                        cap, s);
+    if (mode < 0) {
+      cache_write_tags(cs_, key_type_, entries, count, cap, /*invalidate=*/true, s);
+      publish_invalidate(s);
+      NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
+      return;
+    }
+    commit_entries(s, entries, count, cap, mode, stride, d_vals);
+
+    // write-through to the backing table
+    if (cfg_.uvm_table && !cfg_.disable_uvm_update) {
+      contexts_->order_after_lookups(s);
+      update_rows(cfg_.uvm_table, cfg_.uvm_num_rows, cfg_.row_size_in_bytes, dtype,
+                  cfg_.row_size_in_bytes, key_type_, d_keys.device, n, d_vals, stride, mode != 0,
+                  /*keys_unique=*/true, s);
+      NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
+      contexts_->lookups_wait_event(modify_done_);
+    }
+  }
+
+  // invalidate victims -> drain lookups in flight -> write rows -> commit tags
+  void commit_entries(cudaStream_t s, const ModifyEntry* entries, const uint32_t* count,
+                      uint32_t cap, int mode, int64_t src_stride, const uint8_t* src_base) {
+    cache_write_tags(cs_, key_type_, entries, count, cap, /*invalidate=*/true, s);
+    publish_invalidate(s);
+    contexts_->order_after_lookups(s);
+    int vb = 16;
+    const uint64_t q[] = {reinterpret_cast<uint64_t>(cs_.data), uint64_t(cfg_.row_size_in_bytes),
+                          reinterpret_cast<uint64_t>(src_base), uint64_t(src_stride)};
+    for (uint64_t v : q) {
+      while (vb > 1 && v % vb != 0) vb /= 2;
+    }
+    cache_apply_rows(cs_, entries, count, cap, mode, vb, s);
+    cache_write_tags(cs_, key_type_, entries, count, cap, /*invalidate=*/false, s);
+    NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
+  }
+
+  nve_gpu_table_config_t cfg_;
+  nve_key_type_t key_type_;
+  uint32_t num_sets_ = 0;
+  SetHash hash_{};
+  CacheStorage cs_{};
+  std::shared_ptr<ContextRegistry> contexts_;
+  std::mutex modify_mu_;   // one cache modification is assembled at a time
+  std::mutex order_mu_;    // guards invalidate_done_
+  cudaEvent_t invalidate_done_ = nullptr;
+  cudaEvent_t modify_done_ = nullptr;
+  int64_t global_ts_ = 0;
+
+
+ public:
+  const float* counters() const { return cs_.counters; }
+  const int64_t* set_timestamps() const { return cs_.set_ts; }
+};
+
+}  // namespace
+
+// ---- cached layer over a linear backing table ------------------------------------------------
+// Reference LinearUVMEmbeddingLayer<KeyType> (src/linear_embedding_layer.cu:30-316).  Automatic
+// cache population (insert heuristics) is not part of the lookup path: callers insert explicitly.
+class LinearUVMEmbeddingLayer : public EmbeddingLayer {
+ public:
+  LinearUVMEmbeddingLayer(const nve_linear_uvm_layer_config_t& cfg, nve_key_type_t key_type,
+                          std::shared_ptr<GpuTable> table)
+      : default_row_(cfg.default_row_index), key_type_(key_type), table_(std::move(table)) {
+    NVE_B200_CHECK(table_ != nullptr, "Invalid GPU table");
+    NVE_B200_CHECK(table_->config().uvm_table != nullptr, "GPU Table must be backed by a UVM buffer");
+    NVE_B200_CHECK(table_->config().uvm_num_rows > 0, "uvm_num_rows must be >0");
+    const uint64_t key_max = key_type == NVE_KEY_INT32 ? uint64_t(INT32_MAX) : uint64_t(INT64_MAX);
+    NVE_B200_CHECK(uint64_t(table_->config().uvm_num_rows) <= key_max,
+                   "Number of UVM rows cannot be represented by the layer key type");
+    NVE_B200_CHECK(default_row_ < table_->config().uvm_num_rows,
+                   "Default row index must be less than uvm_num_rows");
+  }
+
+  void lookup(context_ptr_t& ctx, int64_t num_keys, const void* keys, void* output,
+              int64_t output_stride, uint64_t* hitmask, const PoolingParams* pool_params,
+              float* hitrates) override {
+    const nve_gpu_table_config_t& tc = table_->config();
+    ScopedDevice sd(tc.device_id);
+    NVE_B200_ARG(num_keys >= 0, "Invalid num_keys");
+    NVE_B200_ARG(keys != nullptr, "Invalid keys buffer");
+    NVE_B200_ARG(output != nullptr, "Invalid output buffer");
+    NVE_B200_ARG(hitmask == nullptr, "Hitmask is not supported for the UVM layer");
+    NVE_B200_ARG(ctx != nullptr, "Invalid layer context");
+    if (pool_params) validate_pool_params(*pool_params);
+    const bool raw_concat = is_pooling_raw_concat(pool_params, tc.value_dtype);
+    if (raw_concat) {
+      NVE_B200_ARG(output_stride >= tc.row_size_in_bytes,
+                   "Raw Concatenate output stride is smaller than the stored row width");
+    }
+    const int64_t out_rows = get_lookup_output_rows(num_keys, pool_params);
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.lookup_stream();
+    const int kb = key_bytes(key_type_);
+    const Staged d_keys = stage_in(c, "keys", keys, size_t(num_keys) * kb, true, s);
+    const Staged d_out = stage_in(c, "output", output, size_t(out_rows) * output_stride, false, s);
+    if (hitrates) {
+      NVE_B200_CHECK(tc.count_misses, "GPU table was not configured to report hit counts");
+      table_->reset_lookup_counter(ctx);
+    }
+
+    if (pool_params && !raw_concat) {
+      const bool concat = pool_params->pooling_type == NVE_POOL_CONCATENATE;
+      const bool quant = is_quant_rowwise(tc.value_dtype);
+      const nve_data_type_t out_dtype = pool_params->output_type;
+      // same type rules as the reference's validate_find_and_pool_data_types
+      // (cuda_ops/find_and_pool.cuh:29-51): float tables pool to fp32/fp16, quantised tables to
+      // the precision of their metadata
+      NVE_B200_ARG(out_dtype == NVE_DTYPE_FLOAT32 || out_dtype == NVE_DTYPE_FLOAT16,
+                   "Unsupported pooled output type");
+      if (quant) {
+        NVE_B200_ARG(out_dtype == quant_output_dtype(tc.value_dtype),
+                     "Quantized output type must match the quantization metadata precision");
+      }
+      const int64_t out_elem = dtype_size(out_dtype);
+      NVE_B200_ARG(output_stride > 0 && output_stride % out_elem == 0, "Invalid pooled output stride");
+      const int64_t row_width = output_stride / out_elem;  // reference derives it the same way
+      const int64_t value_bytes = row_width * (quant ? 1 : dtype_size(tc.value_dtype));
+      NVE_B200_ARG(value_bytes + (quant ? quant_meta_bytes(tc.value_dtype) : 0) <= tc.row_size_in_bytes,
+                   "Pooled output stride does not match the stored row width");
+      nve_b200_cache_data_t view = table_->cache_view(c);
+      if (concat) {
+        nve_b200_gather_args_t g{};
+        g.table = tc.uvm_table;
+        g.num_rows = tc.uvm_num_rows;
+        g.row_stride = tc.row_size_in_bytes;
+        g.value_dtype = tc.value_dtype;
+        g.row_width = row_width;
+        g.default_row_index = default_row_;
+        g.cache = &view;
+        g.key_type = key_type_;
+        g.keys = d_keys.device;
+        g.num_keys = num_keys;
+        g.output = d_out.device;
+        g.output_stride = output_stride;
+        g.output_dtype = out_dtype;
+        table_->order_lookup(s);
+        gather_rows(g, tc.invalid_key, s);
+      } else {
+        nve_b200_pool_args_t a{};
+        a.table = tc.uvm_table;
+        a.num_rows = tc.uvm_num_rows;
+        a.row_stride = tc.row_size_in_bytes;
+        a.value_dtype = tc.value_dtype;
+        a.row_width = row_width;
+        a.default_row_index = default_row_;
+        a.cache = &view;
+        a.key_type = key_type_;
+        a.keys = d_keys.device;
+        a.num_keys = num_keys;
+        a.pooling_type = pool_params->pooling_type;
+        a.sparse_type = pool_params->sparse_type;
+        a.offset_bytes = kb;
+        a.fixed_hotness = pool_params->fixed_hotness;
+        a.num_bags = out_rows;
+        if (pool_params->sparse_type == NVE_SPARSE_CSR) {
+          a.csr_offsets = stage_in(c, "offsets", pool_params->csr_offsets,
+                                   size_t(pool_params->num_csr_offsets) * kb, true, s).device;
+        }
+        if (pool_params->weights) {
+          a.weights = stage_in(c, "weights", pool_params->weights,
+                               size_t(num_keys) * dtype_size(pool_params->weight_type), true, s).device;
+          a.weight_dtype = pool_params->weight_type;
+        }
+        a.output = d_out.device;
+        a.output_stride = output_stride;
+        a.output_dtype = out_dtype;
+        table_->order_lookup(s);
+        lookup_pool(a, tc.invalid_key, s);
+      }
+    } else {
+      table_->find_device(c, num_keys, d_keys.device, nullptr, output_stride, d_out.device,
+                          default_row_, s);
+    }
+    d_out.copy_back(s);
+
+    if (hitrates) {
+      int64_t* host_misses = static_cast<int64_t*>(c.scratch("miss_readback", 64, true));
+      table_->get_lookup_counter(ctx, host_misses);
+      NVE_B200_CUDA(cudaStreamSynchronize(s));  // the count is only known once the lookup ran
+      hitrates[0] = num_keys > 0
+                        ? 1.f - static_cast<float>(*host_misses) / static_cast<float>(num_keys)
+                        : 1.f;
+    }
+  }
+
+  void insert(context_ptr_t& ctx, int64_t num_keys, const void* keys, int64_t value_stride,
+              int64_t value_size, const void* values, int64_t table_id) override {
+    NVE_B200_CHECK(table_id < get_num_tables(), "Invalid table_id");
+    NVE_B200_CHECK(num_keys >= 0, "Invalid num_keys");
+    NVE_B200_CHECK(keys != nullptr, "Invalid keys buffer");
+    NVE_B200_CHECK(values != nullptr, "Invalid values buffer");
+    NVE_B200_CHECK(value_size == table_->config().row_size_in_bytes, "Invalid value size");
+    table_->insert(ctx, num_keys, keys, value_stride, value_size, values);
+  }
+  void update(context_ptr_t& ctx, int64_t num_keys, const void* keys, int64_t value_stride,
+              int64_t value_size, const void* values, int64_t table_id) override {
+    NVE_B200_CHECK(table_id < get_num_tables(), "Invalid table_id");
+    NVE_B200_CHECK(num_keys >= 0, "Invalid num_keys");
+    NVE_B200_CHECK(keys != nullptr, "Invalid keys buffer");
+    NVE_B200_CHECK(values != nullptr, "Invalid values buffer");
+    NVE_B200_CHECK(value_size == table_->config().row_size_in_bytes, "Invalid value size");
+    table_->update(ctx, num_keys, keys, value_stride, value_size, values);
+  }
+  void accumulate(context_ptr_t& ctx, int64_t num_keys, const void* keys, int64_t value_stride,
+                  int64_t value_size, const void* values, nve_data_type_t value_type,
+                  int64_t table_id) override {
+    NVE_B200_CHECK(table_id < get_num_tables(), "Invalid table_id");
+    NVE_B200_CHECK(num_keys >= 0, "Invalid num_keys");
+    NVE_B200_CHECK(keys != nullptr, "Invalid keys buffer");
+    NVE_B200_CHECK(values != nullptr, "Invalid values buffer");
+    NVE_B200_CHECK(value_size == table_->config().row_size_in_bytes, "Invalid value size");
+    table_->update_accumulate(ctx, num_keys, keys, value_stride, value_size, values, value_type);
+  }
+  void clear(context_ptr_t& ctx) override { table_->clear(ctx); }
+  void erase(context_ptr_t& ctx, int64_t num_keys, const void* keys, int64_t table_id) override {
+    NVE_B200_CHECK(table_id < get_num_tables(), "Invalid table_id");
+    NVE_B200_CHECK(num_keys >= 0, "Invalid num_keys");
+    NVE_B200_CHECK(keys != nullptr, "Invalid keys buffer");
+    table_->erase(ctx, num_keys, keys);
+  }
+  context_ptr_t create_execution_context(cudaStream_t lookup_stream,
+                                         cudaStream_t modify_stream) override {
+    return table_->create_execution_context(lookup_stream, modify_stream);
+  }
+  int64_t get_num_tables() const override { return 1; }
+
+ private:
+  int64_t default_row_;
+  nve_key_type_t key_type_;
+  std::shared_ptr<GpuTable> table_;
+};
+
+std::shared_ptr<Table> make_gpu_table(const nve_gpu_table_config_t& config, nve_key_type_t key_type) {
+  return std::make_shared<GpuTable>(config, key_type);
 }
-std::shared_ptr<EmbeddingLayer> make_linear_uvm_layer(const nve_linear_uvm_layer_config_t&,
-                                                      nve_key_type_t, std::shared_ptr<Table>) {
-  throw NotImplemented("Linear UVM layer: not built yet");
+
+std::shared_ptr<EmbeddingLayer> make_linear_uvm_layer(const nve_linear_uvm_layer_config_t& config,
+                                                      nve_key_type_t key_type,
+                                                      std::shared_ptr<Table> gpu_table) {
+  auto typed = std::dynamic_pointer_cast<GpuTable>(gpu_table);
+  if (!typed) throw InvalidArgument("gpu_table is not a GPU cache table");
+  return std::make_shared<LinearUVMEmbeddingLayer>(config, key_type, std::move(typed));
+}
+
+// Extension entry point used by the kernel-level ABI: insert rows read from the backing table.
+void gpu_table_insert_from_backing(Table& table, context_ptr_t& ctx, int64_t n, const void* keys) {
+  auto* t = dynamic_cast<GpuTable*>(&table);
+  if (!t) throw InvalidArgument("not a GPU cache table");
+  t->insert_from_table(ctx, n, keys);
+}
+
+void gpu_table_cache_data(Table& table, ExecutionContext& ctx, nve_b200_cache_data_t* out) {
+  auto* t = dynamic_cast<GpuTable*>(&table);
+  if (!t) throw InvalidArgument("not a GPU cache table");
+  *out = t->cache_view(ctx);
+}
+
+void gpu_table_policy_state(Table& table, const float** counters, const int64_t** set_ts) {
+  auto* t = dynamic_cast<GpuTable*>(&table);
+  if (!t) throw InvalidArgument("not a GPU cache table");
+  if (counters) *counters = t->counters();
+  if (set_ts) *set_ts = t->set_timestamps();
 }
 
 }  // namespace nve_b200

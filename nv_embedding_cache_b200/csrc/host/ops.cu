@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "../kernels/lookup_pool.cuh"
+#include "../kernels/pool_dense.cuh"
 #include "../kernels/lookup_rows.cuh"
 #include "../kernels/update_rows.cuh"
 
@@ -163,6 +164,17 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
   p.out_vec_ok = (reinterpret_cast<uint64_t>(a.output) % store_bytes == 0) &&
                  (static_cast<uint64_t>(a.output_stride) % store_bytes == 0);
 
+  static const bool dense_off = std::getenv("NVE_B200_NO_DENSE") != nullptr;
+  if (!dense_off && pool_dense_eligible(p, vb)) {
+    switch (in) {
+      case In::F32: launch_pool_dense<In::F32>(p, stream); break;
+      case In::F16: launch_pool_dense<In::F16>(p, stream); break;
+      case In::I8: launch_pool_dense<In::I8>(p, stream); break;
+      case In::U8: launch_pool_dense<In::U8>(p, stream); break;
+    }
+    NVE_B200_CUDA(cudaGetLastError());
+    return;
+  }
   switch (in) {
     case In::F32: launch_lookup_pool<In::F32>(p, vb, stream); break;
     case In::F16: launch_lookup_pool<In::F16>(p, vb, stream); break;

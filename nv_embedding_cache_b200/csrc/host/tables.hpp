@@ -29,6 +29,9 @@ class Table {
 };
 
 // Implemented in gpu_table.cu.
+void gpu_table_insert_from_backing(Table& table, context_ptr_t& ctx, int64_t n, const void* keys);
+void gpu_table_cache_data(Table& table, ExecutionContext& ctx, nve_b200_cache_data_t* out);
+void gpu_table_policy_state(Table& table, const float** counters, const int64_t** set_ts);
 std::shared_ptr<Table> make_gpu_table(const nve_gpu_table_config_t& config, nve_key_type_t key_type);
 // Implemented in linear_uvm_layer.cu.
 class EmbeddingLayer;

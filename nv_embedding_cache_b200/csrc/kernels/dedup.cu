@@ -1,0 +1,379 @@
+// Key de-duplication and per-unique-key gradient reduction.
+//
+// Deduper (reference cuda_ops/deduper.cuh:113-333): from a batch of keys produce
+//   unique[u]      distinct keys in ascending order,
+//   counts[u]      occurrences of unique[u],
+//   inverse[]      positions of the batch grouped by key, ascending position inside a group,
+//   offsets[c]     start of chunk c in inverse[] (a chunk is a whole group, or at most
+//                  max_run consecutive entries of a group when max_run > 0), offsets[C] = n,
+//   loc_map[c]     index u of the unique key chunk c belongs to (max_run > 0 only),
+//   num_runs       {U, C} on the host.
+// The ordering step is a radix sort of (key, position) pairs (cub::DeviceRadixSort, a library
+// primitive, over `end_bit` key bits); run detection, counting, chunk splitting and the maps are
+// fused into two kernels around one prefix scan, and the only host synchronisation is the final
+// read-back of {U, C}.
+//
+// dedup_grads (reference cuda_ops/dedup_grads_kernel.cuh:56-253): unique_grad[u] = sum of the
+// gradient rows at the positions of group u.  Here every chunk is summed by one lane group in
+// position order; groups of several chunks are combined in chunk order by a second kernel, so the
+// result does not depend on scheduling (the reference combines chunks with float atomics).
+// Optionally the sum is applied straight to a table row: table[unique[u]] += alpha * sum.
+//
+// Bytes: dedup reads n keys and writes U*(key + count) + (n + C) positions/offsets; the reduction
+// reads n gradient rows and writes U rows (fused form: reads and writes U table rows instead).
+// Bound: HBM bandwidth.
+#include "dedup.cuh"
+
+#include <cub/cub.cuh>
+
+#include "device_common.cuh"
+
+namespace nve_b200 {
+
+namespace {
+
+inline unsigned blocks_for(int64_t n, int per_block) {
+  return static_cast<unsigned>((n + per_block - 1) / per_block);
+}
+
+template <typename T>
+__global__ void iota_kernel(T* out, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = static_cast<T>(i);
+}
+
+// head[i] = 1 at the first entry of every group; chunk_head[i] = 1 additionally every max_run
+// entries inside a group needs the group start, which is only known after the scan of `head`,
+// so chunk heads are derived in the second kernel from (i - group_start) % max_run.
+template <typename KeyT>
+__global__ void mark_group_heads_kernel(const KeyT* sorted, uint32_t* head, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) head[i] = (i == 0 || sorted[i] != sorted[i - 1]) ? 1u : 0u;
+}
+
+// After rank = exclusive_scan(head): every group head publishes its key and start.
+template <typename KeyT>
+__global__ void emit_groups_kernel(const KeyT* sorted, const uint32_t* head, const uint32_t* rank,
+                                   int64_t n, KeyT* unique, KeyT* group_start, KeyT* num_out) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (head[i]) {
+    unique[rank[i]] = sorted[i];
+    group_start[rank[i]] = static_cast<KeyT>(i);
+  }
+  if (i == n - 1) {
+    const uint32_t total = rank[i] + head[i];
+    group_start[total] = static_cast<KeyT>(n);
+    num_out[0] = static_cast<KeyT>(total);
+  }
+}
+
+// counts and number of chunks per group
+template <typename KeyT>
+__global__ void group_counts_kernel(const KeyT* group_start, const KeyT* num_groups, int64_t n,
+                                    int64_t max_run, KeyT* counts, uint32_t* chunks) {
+  const int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (u >= n) return;
+  if (u < num_groups[0]) {
+    const KeyT c = group_start[u + 1] - group_start[u];
+    counts[u] = c;
+    chunks[u] = max_run > 0 ? static_cast<uint32_t>((c + max_run - 1) / max_run) : 1u;
+  } else {
+    chunks[u] = 0u;
+  }
+}
+
+// chunk_base = exclusive_scan(chunks): chunk offsets and chunk -> group map.
+template <typename KeyT>
+__global__ void emit_chunks_kernel(const KeyT* group_start, const KeyT* num_groups,
+                                   const uint32_t* chunks, const uint32_t* chunk_base, int64_t n,
+                                   int64_t max_run, KeyT* offsets, KeyT* loc_map, KeyT* num_out) {
+  const int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t groups = num_groups[0];
+  if (u >= groups) return;
+  const uint32_t base = chunk_base[u];
+  const uint32_t m = chunks[u];
+  for (uint32_t k = 0; k < m; k++) {
+    offsets[base + k] = group_start[u] + static_cast<KeyT>(k) * static_cast<KeyT>(max_run > 0 ? max_run : 0);
+    if (loc_map) loc_map[base + k] = static_cast<KeyT>(u);
+  }
+  if (u == groups - 1) {
+    offsets[base + m] = static_cast<KeyT>(n);
+    num_out[1] = static_cast<KeyT>(base + m);
+  }
+}
+
+template <typename KeyT>
+struct Workspace {
+  KeyT *sorted, *pos, *group_start, *num_out;
+  uint32_t *head, *rank, *chunks, *chunk_base;
+  void* cub_tmp;
+  size_t cub_bytes;
+  size_t total;
+};
+
+template <typename KeyT>
+Workspace<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
+  Workspace<KeyT> w{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    off = (off + 255) & ~static_cast<size_t>(255);
+    void* p = base ? static_cast<char*>(base) + off : nullptr;
+    off += bytes;
+    return p;
+  };
+  const size_t N = static_cast<size_t>(n) + 1;
+  w.sorted = static_cast<KeyT*>(take(N * sizeof(KeyT)));
+  w.pos = static_cast<KeyT*>(take(N * sizeof(KeyT)));
+  w.group_start = static_cast<KeyT*>(take(N * sizeof(KeyT)));
+  w.num_out = static_cast<KeyT*>(take(2 * sizeof(KeyT)));
+  w.head = static_cast<uint32_t*>(take(N * 4));
+  w.rank = static_cast<uint32_t*>(take(N * 4));
+  w.chunks = static_cast<uint32_t*>(take(N * 4));
+  w.chunk_base = static_cast<uint32_t*>(take(N * 4));
+  w.cub_tmp = take(cub_bytes);
+  w.cub_bytes = cub_bytes;
+  w.total = off + 256;
+  return w;
+}
+
+template <typename KeyT>
+size_t cub_bytes_for(int64_t n) {
+  size_t a = 0, b = 0;
+  KeyT* k = nullptr;
+  uint32_t* u = nullptr;
+  cub::DeviceRadixSort::SortPairs(nullptr, a, k, k, k, k, static_cast<int>(n));
+  cub::DeviceScan::ExclusiveSum(nullptr, b, u, u, static_cast<int>(n));
+  return std::max(a, b);
+}
+
+template <typename KeyT>
+void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t n, void* unique_v,
+                 void* counts_v, void* loc_map_v, void* inverse_v, void* offsets_v,
+                 int64_t max_run, int end_bit, void* pinned_num_runs, cudaStream_t s) {
+  Workspace<KeyT> w = carve<KeyT>(workspace, capacity, cub_bytes_for<KeyT>(capacity));
+  const KeyT* keys = static_cast<const KeyT*>(keys_v);
+  KeyT* unique = static_cast<KeyT*>(unique_v);
+  KeyT* counts = static_cast<KeyT*>(counts_v);
+  KeyT* loc_map = static_cast<KeyT*>(loc_map_v);
+  KeyT* inverse = static_cast<KeyT*>(inverse_v);
+  KeyT* offsets = static_cast<KeyT*>(offsets_v);
+  const int T = 256;
+  const int N = static_cast<int>(n);
+  size_t tmp = w.cub_bytes;
+  iota_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.pos, n);
+  NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, keys, w.sorted, w.pos, inverse, N,
+                                                0, end_bit, s));
+  mark_group_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, n);
+  tmp = w.cub_bytes;
+  NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.head, w.rank, N, s));
+  emit_groups_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, w.rank, n, unique,
+                                                           w.group_start, w.num_out);
+  group_counts_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, n, max_run,
+                                                            counts, w.chunks);
+  tmp = w.cub_bytes;
+  NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.chunks, w.chunk_base, N, s));
+  emit_chunks_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, w.chunks,
+                                                           w.chunk_base, n, max_run, offsets,
+                                                           max_run > 0 ? loc_map : nullptr,
+                                                           w.num_out);
+  NVE_B200_CUDA(cudaGetLastError());
+  NVE_B200_CUDA(cudaMemcpyAsync(pinned_num_runs, w.num_out, 2 * sizeof(KeyT),
+                                cudaMemcpyDeviceToHost, s));
+}
+
+// ---- gradient reduction ------------------------------------------------------------------
+struct GradParams {
+  const uint8_t* grads;      // [n] rows
+  int64_t grad_stride;
+  const void* inverse;       // positions grouped by key
+  const void* offsets;       // chunk starts (C + 1)
+  const void* loc_map;       // chunk -> group, or null (one chunk per group)
+  const void* unique;        // group keys (fused form)
+  const void* num_runs_dev;  // {U, C} on the device (key type)
+  int64_t max_chunks;        // launch bound on C
+  uint8_t* dst;              // [U] rows, or the table in the fused form
+  int64_t dst_stride;
+  int64_t table_rows;        // fused form: keys outside [0, table_rows) are skipped
+  float* partial;            // scratch rows for groups split into several chunks
+  int64_t partial_rows;
+  float alpha;
+  int32_t nvec;              // float4 vectors per row
+  bool idx64;
+  bool fused;
+};
+
+__device__ __forceinline__ int64_t ld_idx(const void* p, bool is64, int64_t i) {
+  return is64 ? reinterpret_cast<const int64_t*>(p)[i]
+              : static_cast<int64_t>(reinterpret_cast<const int32_t*>(p)[i]);
+}
+
+// PASS 0: one lane group per chunk sums its gradient rows in position order.  Groups made of a
+// single chunk finish here; chunks of split groups go to `partial`.
+// PASS 1: one lane group per split group adds its partial rows in chunk order and finishes.
+template <int GROUP, int PASS>
+__global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int gl = lane & (GROUP - 1);
+  const int64_t c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP;
+  const int64_t num_groups = ld_idx(p.num_runs_dev, p.idx64, 0);
+  const int64_t num_chunks = ld_idx(p.num_runs_dev, p.idx64, 1);
+  if (c >= num_chunks) return;
+  const int64_t u = p.loc_map ? ld_idx(p.loc_map, p.idx64, c) : c;
+  // chunks of group u are consecutive; find the first one
+  bool first_of_group = true, last_of_group = true;
+  if (p.loc_map) {
+    first_of_group = (c == 0) || ld_idx(p.loc_map, p.idx64, c - 1) != u;
+    last_of_group = (c == num_chunks - 1) || ld_idx(p.loc_map, p.idx64, c + 1) != u;
+  }
+  const bool single = first_of_group && last_of_group;
+  (void)num_groups;
+
+  int64_t slot_base = 0;   // partial rows of a split group start at 2 * (first_chunk - u)
+  int64_t chunks_in_group = 1;
+  if constexpr (PASS == 1) {
+    if (single || !first_of_group) return;
+    int64_t e = c;
+    while (e + 1 < num_chunks && ld_idx(p.loc_map, p.idx64, e + 1) == u) e++;
+    chunks_in_group = e - c + 1;
+    slot_base = 2 * (c - u);
+  }
+
+  for (int v0 = gl; v0 < p.nvec; v0 += GROUP) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (PASS == 0) {
+      const int64_t b = ld_idx(p.offsets, p.idx64, c);
+      const int64_t e = ld_idx(p.offsets, p.idx64, c + 1);
+      for (int64_t i = b; i < e; i += U) {
+        float4 r[U];
+#pragma unroll
+        for (int k = 0; k < U; k++) {
+          const int64_t at = min(i + k, e - 1);
+          const int64_t row = ld_idx(p.inverse, p.idx64, at);
+          r[k] = __ldg(reinterpret_cast<const float4*>(p.grads + row * p.grad_stride) + v0);
+        }
+#pragma unroll
+        for (int k = 0; k < U; k++) {
+          if (i + k < e) {
+            acc.x = __fadd_rn(acc.x, r[k].x);
+            acc.y = __fadd_rn(acc.y, r[k].y);
+            acc.z = __fadd_rn(acc.z, r[k].z);
+            acc.w = __fadd_rn(acc.w, r[k].w);
+          }
+        }
+      }
+      if (!single) {
+        // k-th chunk of its group
+        int64_t first = c;
+        while (first > 0 && ld_idx(p.loc_map, p.idx64, first - 1) == u) first--;
+        const int64_t slot = 2 * (first - u) + (c - first);
+        if (slot < p.partial_rows) {
+          reinterpret_cast<float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0] = acc;
+        }
+        continue;
+      }
+    } else {
+      for (int64_t k = 0; k < chunks_in_group; k++) {
+        const int64_t slot = slot_base + k;
+        if (slot < p.partial_rows) {
+          const float4 r = reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
+          acc.x = __fadd_rn(acc.x, r.x);
+          acc.y = __fadd_rn(acc.y, r.y);
+          acc.z = __fadd_rn(acc.z, r.z);
+          acc.w = __fadd_rn(acc.w, r.w);
+        }
+      }
+    }
+    if (p.fused) {
+      const int64_t key = ld_idx(p.unique, p.idx64, u);
+      if (static_cast<uint64_t>(key) < static_cast<uint64_t>(p.table_rows)) {
+        float4* d = reinterpret_cast<float4*>(p.dst + key * p.dst_stride) + v0;
+        float4 t = *d;
+        t.x = __fadd_rn(t.x, __fmul_rn(p.alpha, acc.x));
+        t.y = __fadd_rn(t.y, __fmul_rn(p.alpha, acc.y));
+        t.z = __fadd_rn(t.z, __fmul_rn(p.alpha, acc.z));
+        t.w = __fadd_rn(t.w, __fmul_rn(p.alpha, acc.w));
+        *d = t;
+      }
+    } else {
+      reinterpret_cast<float4*>(p.dst + u * p.dst_stride)[v0] = acc;
+    }
+  }
+}
+
+template <int PASS>
+void launch_grad(const GradParams& p, cudaStream_t s) {
+  if (p.max_chunks <= 0) return;
+  if (p.nvec <= 8) {
+    grad_reduce_kernel<8, PASS><<<blocks_for(p.max_chunks * 8, 128), 128, 0, s>>>(p);
+  } else if (p.nvec <= 16) {
+    grad_reduce_kernel<16, PASS><<<blocks_for(p.max_chunks * 16, 128), 128, 0, s>>>(p);
+  } else {
+    grad_reduce_kernel<32, PASS><<<blocks_for(p.max_chunks * 32, 128), 128, 0, s>>>(p);
+  }
+}
+
+}  // namespace
+
+size_t dedup_workspace_bytes(nve_key_type_t key_type, int64_t capacity) {
+  if (key_type == NVE_KEY_INT64) {
+    return carve<int64_t>(nullptr, capacity, cub_bytes_for<int64_t>(capacity)).total;
+  }
+  return carve<int32_t>(nullptr, capacity, cub_bytes_for<int32_t>(capacity)).total;
+}
+
+void dedup_run(nve_key_type_t key_type, void* workspace, int64_t capacity, const void* keys,
+               int64_t n, void* unique, void* counts, void* loc_map, void* inverse, void* offsets,
+               int64_t max_run, int end_bit, void* pinned_num_runs, cudaStream_t stream) {
+  if (key_type == NVE_KEY_INT64) {
+    dedup_typed<int64_t>(workspace, capacity, keys, n, unique, counts, loc_map, inverse, offsets,
+                         max_run, end_bit, pinned_num_runs, stream);
+  } else {
+    dedup_typed<int32_t>(workspace, capacity, keys, n, unique, counts, loc_map, inverse, offsets,
+                         max_run, end_bit, pinned_num_runs, stream);
+  }
+}
+
+const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int64_t capacity) {
+  if (key_type == NVE_KEY_INT64) {
+    return carve<int64_t>(workspace, capacity, cub_bytes_for<int64_t>(capacity)).num_out;
+  }
+  return carve<int32_t>(workspace, capacity, cub_bytes_for<int32_t>(capacity)).num_out;
+}
+
+void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
+                     int64_t row_bytes, const void* inverse, const void* offsets,
+                     const void* loc_map, const void* unique, const void* num_runs_dev,
+                     int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
+                     int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
+                     cudaStream_t stream) {
+  NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
+  NVE_B200_ARG(grad_stride % 16 == 0 && dst_stride % 16 == 0 &&
+                   reinterpret_cast<uint64_t>(grads) % 16 == 0 &&
+                   reinterpret_cast<uint64_t>(dst) % 16 == 0,
+               "dedup_grads: gradient and destination rows must be 16-byte aligned");
+  GradParams p{};
+  p.grads = static_cast<const uint8_t*>(grads);
+  p.grad_stride = grad_stride;
+  p.inverse = inverse;
+  p.offsets = offsets;
+  p.loc_map = loc_map;
+  p.unique = unique;
+  p.num_runs_dev = num_runs_dev;
+  p.max_chunks = max_chunks;
+  p.dst = static_cast<uint8_t*>(dst);
+  p.dst_stride = dst_stride;
+  p.table_rows = table_rows;
+  p.partial = partial;
+  p.partial_rows = partial_rows;
+  p.alpha = alpha;
+  p.nvec = static_cast<int32_t>(row_bytes / 16);
+  p.idx64 = key_type == NVE_KEY_INT64;
+  p.fused = fused;
+  launch_grad<0>(p, stream);
+  if (loc_map != nullptr) launch_grad<1>(p, stream);
+  NVE_B200_CUDA(cudaGetLastError());
+}
+
+}  // namespace nve_b200

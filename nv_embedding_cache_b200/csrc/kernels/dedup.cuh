@@ -1,0 +1,29 @@
+// Key de-duplication and gradient reduction (declarations; see dedup.cu).
+#pragma once
+
+#include "../common.hpp"
+
+namespace nve_b200 {
+
+size_t dedup_workspace_bytes(nve_key_type_t key_type, int64_t capacity);
+
+// All index arrays (unique, counts, loc_map, inverse, offsets) have the key type.
+// pinned_num_runs: 2 host-pinned elements of the key type, valid after the stream is synchronised.
+void dedup_run(nve_key_type_t key_type, void* workspace, int64_t capacity, const void* keys,
+               int64_t n, void* unique, void* counts, void* loc_map, void* inverse, void* offsets,
+               int64_t max_run, int end_bit, void* pinned_num_runs, cudaStream_t stream);
+
+// Device copy of {U, C} inside the workspace, for kernels that follow without a host round trip.
+const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int64_t capacity);
+
+// dst[u] = sum of grads rows of group u (fused == false), or
+// table[unique[u]] += alpha * sum (fused == true; dst is the table, keys outside
+// [0, table_rows) are skipped).  fp32 rows, 16-byte aligned.
+void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
+                     int64_t row_bytes, const void* inverse, const void* offsets,
+                     const void* loc_map, const void* unique, const void* num_runs_dev,
+                     int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
+                     int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
+                     cudaStream_t stream);
+
+}  // namespace nve_b200

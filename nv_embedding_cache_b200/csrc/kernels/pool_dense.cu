@@ -1,0 +1,54 @@
+// Instantiates the lean dense pooled lookup and picks the lane group from the row size.
+#include "pool_dense.cuh"
+
+namespace nve_b200 {
+
+namespace {
+
+// NVE_B200_DENSE_U (4 or 8) and NVE_B200_POOL_BLOCK (32..128) are tuning knobs.
+int dense_unroll() {
+  static const int value = [] {
+    const char* e = std::getenv("NVE_B200_DENSE_U");
+    const int v = e ? std::atoi(e) : 0;
+    return (v == 4 || v == 8) ? v : 4;
+  }();
+  return value;
+}
+
+template <In IN, int GROUP, int U>
+void launch_flags(const PoolKernelParams& p, cudaStream_t stream) {
+  const int block = pool_block_threads();
+  const unsigned grid = static_cast<unsigned>((p.num_bags * GROUP + block - 1) / block);
+  const bool weighted = p.weights != nullptr;
+  const bool sanitize = p.default_row >= 0;
+  if (weighted) {
+    if (sanitize) pool_dense_kernel<IN, GROUP, U, true, true><<<grid, block, 0, stream>>>(p);
+    else pool_dense_kernel<IN, GROUP, U, true, false><<<grid, block, 0, stream>>>(p);
+  } else {
+    if (sanitize) pool_dense_kernel<IN, GROUP, U, false, true><<<grid, block, 0, stream>>>(p);
+    else pool_dense_kernel<IN, GROUP, U, false, false><<<grid, block, 0, stream>>>(p);
+  }
+}
+
+template <In IN, int U>
+void launch_group(const PoolKernelParams& p, cudaStream_t stream) {
+  if (p.nvec <= 4) launch_flags<IN, 4, U>(p, stream);
+  else if (p.nvec <= 8) launch_flags<IN, 8, U>(p, stream);
+  else if (p.nvec <= 16) launch_flags<IN, 16, U>(p, stream);
+  else launch_flags<IN, 32, U>(p, stream);
+}
+
+template <In IN>
+void launch_any(const PoolKernelParams& p, cudaStream_t stream) {
+  if (dense_unroll() == 8) launch_group<IN, 8>(p, stream);
+  else launch_group<IN, 4>(p, stream);
+}
+
+}  // namespace
+
+template <> void launch_pool_dense<In::F32>(const PoolKernelParams& p, cudaStream_t s) { launch_any<In::F32>(p, s); }
+template <> void launch_pool_dense<In::F16>(const PoolKernelParams& p, cudaStream_t s) { launch_any<In::F16>(p, s); }
+template <> void launch_pool_dense<In::I8>(const PoolKernelParams& p, cudaStream_t s) { launch_any<In::I8>(p, s); }
+template <> void launch_pool_dense<In::U8>(const PoolKernelParams& p, cudaStream_t s) { launch_any<In::U8>(p, s); }
+
+}  // namespace nve_b200

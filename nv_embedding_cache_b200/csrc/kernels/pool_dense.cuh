@@ -1,0 +1,148 @@
+// Lean variant of the fused gather -> (dequantise) -> pool kernel for the common dense case:
+// plain table in HBM (no cache probe), 16-byte vectors, one vector per lane (row <= 512 bytes),
+// fewer than 2^32 rows.  Same arithmetic and order as the general kernel (lookup_pool.cuh), so
+// results are bit-identical; only the bookkeeping is trimmed:
+//   * the owner lane keeps a 32-bit row index, the row address is one wide multiply-add,
+//   * U row loads are always issued together (slots past the end re-read the last row),
+//   * fp16 rows are accumulated with the mixed-precision add (fp16 operand, fp32 accumulator),
+//     which is the same value as convert-then-add.
+//
+// Bytes per bag: len * (key + row) read, two offsets read, one pooled row written.
+// Bound: HBM bandwidth (L2 bandwidth when the key skew keeps the hot rows on chip).
+#pragma once
+
+#include "lookup_pool.cuh"
+
+namespace nve_b200 {
+
+// acc += value of one stored element.  For fp16 the hardware adds the half operand into the fp32
+// accumulator directly: exact conversion followed by one fp32 rounding.
+__device__ __forceinline__ void add_half_pair(float& a0, float& a1, uint32_t packed) {
+  unsigned short lo = static_cast<unsigned short>(packed & 0xffffu);
+  unsigned short hi = static_cast<unsigned short>(packed >> 16);
+  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(a0) : "h"(lo));
+  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(a1) : "h"(hi));
+}
+
+template <In IN, bool WEIGHTED>
+__device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, float w, float scale,
+                                                 float qoff) {
+  if constexpr (IN == In::F16 && !WEIGHTED) {
+    add_half_pair(acc[0], acc[1], raw.x);
+    add_half_pair(acc[2], acc[3], raw.y);
+    add_half_pair(acc[4], acc[5], raw.z);
+    add_half_pair(acc[6], acc[7], raw.w);
+  } else {
+    constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
+    float v[EPV];
+    RawVec<16> r;
+    r.v = raw;
+    decode_vec<IN, 16>(r, scale, qoff, v);
+#pragma unroll
+    for (int e = 0; e < EPV; e++) {
+      const float x = WEIGHTED ? __fmul_rn(v[e], w) : v[e];
+      acc[e] = __fadd_rn(acc[e], x);
+    }
+  }
+}
+
+template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE>
+__global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams p) {
+  constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
+  constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
+  const int lane = threadIdx.x & 31;
+  const int gl = lane & (GROUP - 1);
+  const uint32_t gmask = group_mask<GROUP>(lane);
+  const int64_t bag = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP;
+  if (bag >= p.num_bags) return;
+
+  int64_t start, end;
+  if (p.offsets != nullptr) {
+    start = load_index(p.offsets, p.off64, bag);
+    end = load_index(p.offsets, p.off64, bag + 1);
+  } else {
+    start = bag * p.hotness;
+    end = start + p.hotness;
+  }
+  const int len = static_cast<int>(end - start);
+  const bool lane_on = gl < p.nvec;
+  const uint8_t* lane_base = p.table + gl * 16;
+  const uint32_t stride = static_cast<uint32_t>(p.row_stride);
+
+  float acc[EPV];
+#pragma unroll
+  for (int e = 0; e < EPV; e++) acc[e] = 0.f;
+  float wsum = 0.f;
+
+#pragma unroll 1
+  for (int c = 0; c < len; c += GROUP) {
+    const int n = min(GROUP, len - c);
+    uint32_t my_key = 0;
+    float my_w = 1.f, my_scale = 1.f, my_qoff = 0.f;
+    if (gl < n) {
+      const int64_t k = start + c + gl;
+      int64_t key = p.keys ? load_index(p.keys, p.key64, k) : k;
+      if (SANITIZE && static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
+        key = p.default_row;
+      }
+      my_key = static_cast<uint32_t>(key);
+      if (WEIGHTED) my_w = load_weight(p.weights, p.w16, k);
+      if constexpr (QUANT) {
+        const uint8_t* meta = p.table + static_cast<uint64_t>(my_key) * stride + p.row_width;
+        my_scale = load_meta(meta, p.meta_bytes);
+        if (p.has_qoffset) my_qoff = load_meta(meta + p.meta_bytes, p.meta_bytes);
+      }
+    }
+    // ---- U rows at a time.  Row slots past the end of the chunk re-read the chunk's last row
+    // (an L1 hit) instead of being predicated off, and are skipped when accumulating.
+#pragma unroll 1
+    for (int s = 0; s < n; s += U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
+        if (lane_on) {
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(lane_base + static_cast<uint64_t>(k) * stride));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        float w = 1.f, scale = 1.f, qoff = 0.f;
+        if (WEIGHTED) w = __shfl_sync(gmask, my_w, min(s + u, n - 1), GROUP);
+        if constexpr (QUANT) {
+          scale = __shfl_sync(gmask, my_scale, min(s + u, n - 1), GROUP);
+          qoff = __shfl_sync(gmask, my_qoff, min(s + u, n - 1), GROUP);
+        }
+        if (s + u < n) {
+          if (WEIGHTED) wsum = __fadd_rn(wsum, w);
+          if (lane_on) accumulate_vec16<IN, WEIGHTED>(acc, raw[u], w, scale, qoff);
+        }
+      }
+    }
+  }
+
+  float inv = 1.f;
+  if (p.mean) {
+    const float denom = WEIGHTED ? wsum : static_cast<float>(len);
+    inv = (denom != 0.f) ? __fdiv_rn(1.f, denom) : 0.f;
+  }
+  if (lane_on) {
+    float v[EPV];
+#pragma unroll
+    for (int e = 0; e < EPV; e++) v[e] = __fmul_rn(acc[e], inv);
+    uint8_t* dst = p.out + bag * p.out_stride + static_cast<int64_t>(gl) * EPV * (p.out_f16 ? 2 : 4);
+    store_values<EPV>(dst, v, p.out_f16, p.out_vec_ok);
+  }
+}
+
+// The lean kernel covers: no cache, 16-byte vectors, at most 32 vectors per row, rows addressable
+// with 32 bits, non-negative bag lengths below 2^31.
+inline bool pool_dense_eligible(const PoolKernelParams& p, int vb) {
+  return !p.cache.enabled && p.table != nullptr && vb == 16 && p.nvec >= 1 && p.nvec <= 32 &&
+         p.num_rows > 0 && p.num_rows <= 0xffffffffll && p.row_stride <= 0x7fffffffll;
+}
+
+template <In IN>
+void launch_pool_dense(const PoolKernelParams& p, cudaStream_t stream);
+
+}  // namespace nve_b200

@@ -55,12 +55,12 @@ def build_oracle(verbose: bool = False) -> Path:
     """Compile the C restatement with gcc.  -ffp-contract=off keeps a*b+c unfused so that the
     arithmetic is the same on every host the library is rebuilt on."""
     OUT.mkdir(exist_ok=True)
-    src = HERE / "nve_oracle.c"
+    srcs = [HERE / "nve_oracle.c", HERE / "nve_oracle_cache.c"]
     out = OUT / "libnve_oracle.so"
-    if _newer(out, [src]):
+    if _newer(out, srcs):
         return out
     cmd = ["gcc", "-std=c11", "-O2", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
-           "-Wall", "-Wextra", "-o", str(out), str(src), "-lm"]
+           "-Wall", "-Wextra", "-o", str(out), *map(str, srcs), "-lm"]
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)

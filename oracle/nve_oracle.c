@@ -6,7 +6,7 @@
  * tree).  Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may load this
  * library; the CUDA product never calls it.
  *
- * Parity pin: tests/test_oracle_vs_reference.py checks these functions bit-for-bit against the
+ * Parity pin: tests/test_oracle_pin.py checks these functions bit-for-bit against the
  * unmodified reference CPU build (oracle/_ref/libnve_ref.so, see oracle/build.py) and against the
  * committed golden vectors in tests/golden/.
  *
@@ -213,9 +213,92 @@ NVE_EXPORT int nve_oracle_update_accumulate(void* table, int64_t num_rows, int64
         a = a + b; memcpy(dst + 4 * j, &a, 4);
       } else {
         f16 a, b; memcpy(&a, dst + 2 * j, 2); memcpy(&b, src + 2 * j, 2);
-        a = (f16)((float)a + (float)b); memcpy(dst + 2 * j, &a, 2);
+        a = (f16)((double)a + (double)b); memcpy(dst + 2 * j, &a, 2);
       }
     }
   }
   return 0;
+}
+
+/* ---- Deduper ------------------------------------------------------------------------------- */
+typedef struct { int64_t key; int64_t pos; } KeyPos;
+static int cmp_key_pos(const void* a, const void* b) {
+  const KeyPos* x = (const KeyPos*)a; const KeyPos* y = (const KeyPos*)b;
+  if (x->key != y->key) return x->key < y->key ? -1 : 1;
+  return x->pos < y->pos ? -1 : (x->pos > y->pos);
+}
+
+/*
+ * cuda_ops/deduper.cuh:136-221: stable sort of (key, position) by the low `end_bit` bits of the
+ * key (signed order when all bits take part, as the device radix sort orders signed keys), then
+ * run-length encoding.  Outputs (all int64 here): unique ascending, counts, inverse = positions
+ * grouped by key with ascending position inside a group, offsets = chunk starts (+ total), loc_map
+ * = group of each chunk, where a group is split into chunks of at most max_run positions when
+ * max_run > 0 (:39-81).  num_runs[0] = groups, num_runs[1] = chunks.
+ */
+NVE_EXPORT void nve_oracle_dedup(const void* keys, int key_bytes, int64_t n, int64_t max_run,
+                                 int end_bit, int64_t* unique, int64_t* counts, int64_t* inverse,
+                                 int64_t* offsets, int64_t* loc_map, int64_t* num_runs) {
+  num_runs[0] = num_runs[1] = 0;
+  if (n <= 0) { offsets[0] = 0; return; }
+  const int full = end_bit <= 0 || end_bit >= key_bytes * 8;
+  KeyPos* kp = (KeyPos*)malloc(sizeof(KeyPos) * (size_t)n);
+  int64_t* orig = (int64_t*)malloc(sizeof(int64_t) * (size_t)n);
+  for (int64_t i = 0; i < n; i++) {
+    const int64_t k = load_index(keys, key_bytes, i);
+    orig[i] = k;
+    kp[i].key = full ? k : (int64_t)((uint64_t)k & (((uint64_t)1 << end_bit) - 1));
+    kp[i].pos = i;
+  }
+  qsort(kp, (size_t)n, sizeof(KeyPos), cmp_key_pos);
+  int64_t groups = 0, chunks = 0;
+  for (int64_t i = 0; i < n;) {
+    int64_t j = i;
+    while (j < n && kp[j].key == kp[i].key) j++;
+    unique[groups] = orig[kp[i].pos];
+    counts[groups] = j - i;
+    if (max_run > 0) {
+      for (int64_t b = i; b < j; b += max_run) { offsets[chunks] = b; loc_map[chunks] = groups; chunks++; }
+    } else {
+      offsets[chunks++] = i;
+    }
+    groups++;
+    i = j;
+  }
+  offsets[chunks] = n;
+  for (int64_t i = 0; i < n; i++) inverse[i] = kp[i].pos;
+  num_runs[0] = groups; num_runs[1] = chunks;
+  free(orig); free(kp);
+}
+
+/*
+ * Per-group gradient sum (cuda_ops/dedup_grads_kernel.cuh:56-109): every chunk is summed in fp32
+ * in position order; the chunk sums of a group are added in chunk order (the device reference
+ * adds them with float atomics, i.e. in no fixed order; any order is within its tolerance).
+ * dst[group] = sum, fp32 rows of `width` values.
+ */
+NVE_EXPORT void nve_oracle_dedup_grads(const float* grads, int64_t grad_stride_elems, int64_t width,
+                                       const int64_t* inverse, const int64_t* offsets,
+                                       const int64_t* loc_map, int64_t num_chunks, float* dst,
+                                       int64_t dst_stride_elems) {
+  float* part = (float*)malloc(sizeof(float) * (size_t)width);
+  for (int64_t c = 0; c < num_chunks;) {
+    const int64_t g = loc_map ? loc_map[c] : c;
+    int64_t ce = c;
+    while (ce < num_chunks && (loc_map ? loc_map[ce] : ce) == g) ce++;
+    float* out = dst + g * dst_stride_elems;
+    const int single = (ce - c) == 1;
+    for (int64_t e = 0; e < width; e++) out[e] = 0.f;
+    for (int64_t k = c; k < ce; k++) {
+      for (int64_t e = 0; e < width; e++) part[e] = 0.f;
+      for (int64_t i = offsets[k]; i < offsets[k + 1]; i++) {
+        const float* row = grads + inverse[i] * grad_stride_elems;
+        for (int64_t e = 0; e < width; e++) part[e] = part[e] + row[e];
+      }
+      if (single) { for (int64_t e = 0; e < width; e++) out[e] = part[e]; }
+      else { for (int64_t e = 0; e < width; e++) out[e] = out[e] + part[e]; }
+    }
+    c = ce;
+  }
+  free(part);
 }

@@ -39,6 +39,35 @@ class Oracle:
         L.nve_oracle_update_accumulate.restype = _i32
         L.nve_oracle_update_accumulate.argtypes = [_vp, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i64]
 
+    def dedup(self, keys: np.ndarray, max_run: int = -1, end_bit: int = 0):
+        """Returns dict(unique, counts, inverse, offsets, loc_map, num_unique, num_chunks)."""
+        L = self.lib
+        L.nve_oracle_dedup.restype = None
+        L.nve_oracle_dedup.argtypes = [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp]
+        n = keys.size
+        cap = n + (n // max_run if max_run > 0 else 0) + 2
+        unique = np.zeros(n + 1, np.int64)
+        counts = np.zeros(n + 1, np.int64)
+        inverse = np.zeros(n + 1, np.int64)
+        offsets = np.zeros(cap + 1, np.int64)
+        loc_map = np.zeros(cap + 1, np.int64)
+        runs = np.zeros(2, np.int64)
+        L.nve_oracle_dedup(_ptr(keys), keys.dtype.itemsize, n, max_run, end_bit, _ptr(unique),
+                           _ptr(counts), _ptr(inverse), _ptr(offsets), _ptr(loc_map), _ptr(runs))
+        u, c = int(runs[0]), int(runs[1])
+        return dict(unique=unique[:u], counts=counts[:u], inverse=inverse[:n], offsets=offsets[:c + 1],
+                    loc_map=loc_map[:c] if max_run > 0 else None, num_unique=u, num_chunks=c)
+
+    def dedup_grads(self, grads: np.ndarray, d: dict) -> np.ndarray:
+        L = self.lib
+        L.nve_oracle_dedup_grads.restype = None
+        L.nve_oracle_dedup_grads.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _i64]
+        out = np.zeros((d["num_unique"], grads.shape[1]), np.float32)
+        L.nve_oracle_dedup_grads(_ptr(grads), grads.strides[0] // 4, grads.shape[1],
+                                 _ptr(d["inverse"]), _ptr(d["offsets"]), _ptr(d["loc_map"]),
+                                 d["num_chunks"], _ptr(out), grads.shape[1])
+        return out
+
     def gather(self, table2d: np.ndarray, keys: np.ndarray, out: np.ndarray, hit_mask=None) -> int:
         rows = table2d.reshape(table2d.shape[0], -1).view(np.uint8)
         return self.lib.nve_oracle_gather(_ptr(rows), rows.shape[0], rows.shape[1], _ptr(keys),
@@ -83,6 +112,121 @@ class Oracle:
                                                    dt, _ptr(keys), keys.dtype.itemsize, keys.size,
                                                    _ptr(updates), updates.strides[0])
         assert rc == 0
+
+
+class OracleCache:
+    """The C restatement of the set-associative cache with the device-side modify policy."""
+
+    def __init__(self, oracle: Oracle, cache_bytes: int, row_bytes: int, key_dtype=np.int64,
+                 decay_rate: float = 0.95, sentinel: int = -1):
+        L = self.lib = oracle.lib
+        u64 = C.c_uint64
+        L.nve_oracle_cache_num_sets.restype = u64
+        L.nve_oracle_cache_num_sets.argtypes = [u64, _i64, _i32]
+        L.nve_oracle_cache_create.restype = _vp
+        L.nve_oracle_cache_create.argtypes = [u64, _i64, _i32, C.c_float, _i64]
+        L.nve_oracle_cache_destroy.argtypes = [_vp]
+        L.nve_oracle_cache_sets.restype = u64
+        L.nve_oracle_cache_sets.argtypes = [_vp]
+        for name in ("get_tags", "get_counters", "get_data"):
+            getattr(L, "nve_oracle_cache_" + name).argtypes = [_vp, _vp]
+        L.nve_oracle_cache_misses.restype = _i64
+        L.nve_oracle_cache_misses.argtypes = [_vp]
+        L.nve_oracle_cache_reset_misses.argtypes = [_vp]
+        L.nve_oracle_cache_lookup.restype = _i64
+        L.nve_oracle_cache_lookup.argtypes = [_vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp]
+        L.nve_oracle_cache_insert.restype = _i64
+        L.nve_oracle_cache_insert.argtypes = [_vp, _vp, _i64, _vp, _i64, _i32, _i64]
+        L.nve_oracle_cache_update.argtypes = [_vp, _vp, _i64, _vp, _i64]
+        L.nve_oracle_cache_update_accumulate.argtypes = [_vp, _vp, _i64, _vp, _i64, _i32]
+        L.nve_oracle_cache_invalidate.argtypes = [_vp, _vp, _i64]
+        L.nve_oracle_cache_clear.argtypes = [_vp]
+        self.key_dtype = np.dtype(key_dtype)
+        self.row_bytes = row_bytes
+        self.h = L.nve_oracle_cache_create(cache_bytes, row_bytes, self.key_dtype.itemsize,
+                                           decay_rate, sentinel)
+        if not self.h:
+            raise ValueError("cache too small for one set")
+        self.num_sets = int(L.nve_oracle_cache_sets(self.h))
+        self.sentinel = sentinel
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.nve_oracle_cache_destroy(self.h)
+            self.h = None
+
+    def _keys(self, keys):
+        return np.ascontiguousarray(keys, dtype=self.key_dtype)
+
+    def tags(self) -> np.ndarray:
+        out = np.zeros((self.num_sets, 8), dtype=np.int64)
+        self.lib.nve_oracle_cache_get_tags(self.h, _ptr(out))
+        return out
+
+    def counters(self) -> np.ndarray:
+        out = np.zeros((self.num_sets, 8), dtype=np.float32)
+        self.lib.nve_oracle_cache_get_counters(self.h, _ptr(out))
+        return out
+
+    def data(self) -> np.ndarray:
+        out = np.zeros((self.num_sets, 8, self.row_bytes), dtype=np.uint8)
+        self.lib.nve_oracle_cache_get_data(self.h, _ptr(out))
+        return out
+
+    def resident_keys(self) -> np.ndarray:
+        """Keys held by the cache, in (set, way) order (get_keys_stored_in_cache)."""
+        t = self.tags()
+        sets = np.repeat(np.arange(self.num_sets, dtype=np.uint64), 8).reshape(t.shape)
+        valid = t != self.sentinel
+        if self.key_dtype.itemsize == 4:
+            keys = (t.astype(np.uint32).astype(np.uint64) * np.uint64(self.num_sets) + sets).astype(np.uint32).view(np.int32)
+        else:
+            keys = (t.view(np.uint64) * np.uint64(self.num_sets) + sets).view(np.int64)
+        return keys[valid]
+
+    @property
+    def misses(self) -> int:
+        return int(self.lib.nve_oracle_cache_misses(self.h))
+
+    def reset_misses(self):
+        self.lib.nve_oracle_cache_reset_misses(self.h)
+
+    def lookup(self, keys, out=None, hit_mask=None, table=None, default_row=-1, want_miss_list=False):
+        keys = self._keys(keys)
+        n = keys.size
+        mp = np.zeros(n, dtype=np.int64) if want_miss_list else None
+        mk = np.zeros(n, dtype=np.int64) if want_miss_list else None
+        trows = 0 if table is None else table.shape[0]
+        unresolved = self.lib.nve_oracle_cache_lookup(
+            self.h, _ptr(keys), n, _ptr(out), out.strides[0] if out is not None else 0,
+            _ptr(hit_mask), _ptr(table), trows, default_row, _ptr(mp), _ptr(mk))
+        if want_miss_list:
+            return unresolved, mp[:unresolved], mk[:unresolved]
+        return unresolved
+
+    def insert(self, keys, values=None, table=None, max_modify=1 << 20) -> int:
+        keys = self._keys(keys)
+        if table is not None:
+            return self.lib.nve_oracle_cache_insert(self.h, _ptr(keys), keys.size, _ptr(table),
+                                                    table.strides[0], 1, max_modify)
+        return self.lib.nve_oracle_cache_insert(self.h, _ptr(keys), keys.size, _ptr(values),
+                                                values.strides[0], 0, max_modify)
+
+    def update(self, keys, values):
+        keys = self._keys(keys)
+        self.lib.nve_oracle_cache_update(self.h, _ptr(keys), keys.size, _ptr(values), values.strides[0])
+
+    def update_accumulate(self, keys, updates):
+        keys = self._keys(keys)
+        self.lib.nve_oracle_cache_update_accumulate(self.h, _ptr(keys), keys.size, _ptr(updates),
+                                                    updates.strides[0], int(updates.dtype == np.float16))
+
+    def invalidate(self, keys):
+        keys = self._keys(keys)
+        self.lib.nve_oracle_cache_invalidate(self.h, _ptr(keys), keys.size)
+
+    def clear(self):
+        self.lib.nve_oracle_cache_clear(self.h)
 
 
 class Reference:

@@ -108,3 +108,103 @@ def rel_err(a: np.ndarray, b: np.ndarray) -> float:
     a = a.astype(np.float64)
     b = b.astype(np.float64)
     return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-30))) if a.size else 0.0
+
+
+# ---- GPU cache table helpers --------------------------------------------------------------------
+def device_read(ptr_value: int, nbytes: int) -> np.ndarray:
+    """Copy nbytes from a raw device address to a numpy buffer (UVA memcpy through cuda-python)."""
+    from cuda import cudart
+    out = np.empty(nbytes, dtype=np.uint8)
+    (err,) = cudart.cudaDeviceSynchronize()
+    assert int(err) == 0, err
+    (err,) = cudart.cudaMemcpy(out.ctypes.data, ptr_value, nbytes, cudart.cudaMemcpyKind.cudaMemcpyDefault)
+    assert int(err) == 0, err
+    return out
+
+
+class CacheTable:
+    """nve_gpu_table_create + one execution context; state readers for parity checks."""
+
+    def __init__(self, cache_bytes, row_bytes, value_dtype="f16", key_dtype=np.int64, backing=None,
+                 backing_rows=0, max_modify=1 << 20, sentinel=-1):
+        from nv_embedding_cache_b200.layers import GpuTable
+        self.key_dtype = np.dtype(key_dtype)
+        self.row_bytes = row_bytes
+        kt = capi.KEY_INT64 if self.key_dtype.itemsize == 8 else capi.KEY_INT32
+        self.table = GpuTable(cache_bytes, row_bytes, DT[value_dtype], key_type=kt, uvm_table=backing,
+                              uvm_num_rows=backing_rows, max_modify_size=max_modify,
+                              invalid_key=sentinel)
+        self.ctx = self.table.create_execution_context()
+        view = capi.CacheData()
+        capi.check(capi.lib.nve_b200_gpu_table_get_cache_data(self.table.handle, self.ctx.handle,
+                                                              C.byref(view)))
+        self.view = view
+        self.num_sets = view.num_sets
+        self.sentinel = sentinel
+
+    def tags(self) -> np.ndarray:
+        raw = device_read(self.view.tags_ptr, self.num_sets * 8 * self.key_dtype.itemsize)
+        return raw.view(self.key_dtype).astype(np.int64).reshape(self.num_sets, 8)
+
+    def data(self) -> np.ndarray:
+        raw = device_read(self.view.cache_ptr, self.num_sets * 8 * self.row_bytes)
+        return raw.reshape(self.num_sets, 8, self.row_bytes)
+
+    def counters(self) -> np.ndarray:
+        p, q = C.c_void_p(), C.c_void_p()
+        capi.check(capi.lib.nve_b200_gpu_table_get_policy_state(self.table.handle, C.byref(p), C.byref(q)))
+        return device_read(p.value, self.num_sets * 8 * 4).view(np.float32).reshape(self.num_sets, 8)
+
+    def keys_of(self, a):
+        return np.ascontiguousarray(a, dtype=self.key_dtype)
+
+    def insert(self, keys, values):
+        keys = self.keys_of(keys)
+        self.table.insert(self.ctx, keys.size, keys, values.strides[0], self.row_bytes, values)
+        self.ctx.wait()
+
+    def insert_from_backing(self, keys):
+        keys = self.keys_of(keys)
+        capi.check(capi.lib.nve_b200_gpu_table_insert_from_backing(self.table.handle, self.ctx.handle,
+                                                                   keys.size, keys.ctypes.data))
+        self.ctx.wait()
+
+    def find(self, keys, out, hit_mask=None):
+        keys = self.keys_of(keys)
+        self.table.reset_lookup_counter(self.ctx)
+        self.table.find(self.ctx, keys.size, keys, hit_mask, out.strides[0] if out is not None else 0, out)
+        self.ctx.wait()
+        v = self.table.get_lookup_counter(self.ctx)
+        self.ctx.wait()
+        return self.table_counter()
+
+    def table_counter(self) -> int:
+        v = C.c_int64(-1)
+        capi.check(capi.lib.nve_table_get_lookup_counter(self.table.handle, self.ctx.handle, C.byref(v)))
+        self.ctx.wait()
+        return v.value
+
+    def update(self, keys, values):
+        keys = self.keys_of(keys)
+        self.table.update(self.ctx, keys.size, keys, values.strides[0], self.row_bytes, values)
+        self.ctx.wait()
+
+    def update_accumulate(self, keys, updates, dtype):
+        keys = self.keys_of(keys)
+        self.table.update_accumulate(self.ctx, keys.size, keys, updates.strides[0], self.row_bytes,
+                                     updates, DT[dtype])
+        self.ctx.wait()
+
+    def erase(self, keys):
+        keys = self.keys_of(keys)
+        self.table.erase(self.ctx, keys.size, keys)
+        self.ctx.wait()
+
+    def clear(self):
+        self.table.clear(self.ctx)
+        self.ctx.wait()
+
+    def close(self):
+        self.ctx.wait()
+        self.ctx.destroy()
+        self.table.destroy()

@@ -1,0 +1,140 @@
+"""GPU parity of the Deduper and the per-key gradient reduction through the C ABI: unique sets,
+counts, offsets, inverse and chunk maps bit-exact; gradient sums exact on dyadic data and within
+1e-6 relative error on random data; the fused reduce-and-apply form within 1e-6 of the reference
+CPU update (cpu_kernel_update_accumulate on -lr * gradient)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from nv_embedding_cache_b200 import capi, datagen as dg
+from nve_helpers import ptr, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+class Deduper:
+    def __init__(self, key_dtype, max_run, max_keys):
+        self.kd = np.dtype(key_dtype)
+        self.max_run = max_run
+        self.h = C.c_void_p()
+        kt = capi.KEY_INT64 if self.kd.itemsize == 8 else capi.KEY_INT32
+        capi.check(capi.lib.nve_b200_deduper_create(C.byref(self.h), kt, max_run, max_keys))
+
+    def dedup(self, torch, keys, end_bit=0):
+        n = keys.size
+        cap = n + (n // self.max_run if self.max_run > 0 else 0) + 2
+        td = torch.int64 if self.kd.itemsize == 8 else torch.int32
+        self.d_keys = to_dev(torch, keys.astype(self.kd))
+        self.unique = torch.full((n + 1,), -7, dtype=td, device="cuda")
+        self.counts = torch.full((n + 1,), -7, dtype=td, device="cuda")
+        self.inverse = torch.full((n + 1,), -7, dtype=td, device="cuda")
+        self.offsets = torch.full((cap + 1,), -7, dtype=td, device="cuda")
+        self.loc_map = torch.full((cap + 1,), -7, dtype=td, device="cuda")
+        runs = np.zeros(2, dtype=self.kd)
+        capi.check(capi.lib.nve_b200_deduper_dedup(
+            self.h, ptr(self.d_keys), n, ptr(self.unique), ptr(self.counts), ptr(self.loc_map),
+            runs.ctypes.data, ptr(self.inverse), ptr(self.offsets), None, end_bit))
+        u, c = int(runs[0]), int(runs[1])
+        return dict(unique=self.unique[:u].cpu().numpy().astype(np.int64),
+                    counts=self.counts[:u].cpu().numpy().astype(np.int64),
+                    inverse=self.inverse[:n].cpu().numpy().astype(np.int64),
+                    offsets=self.offsets[:c + 1].cpu().numpy().astype(np.int64),
+                    loc_map=self.loc_map[:c].cpu().numpy().astype(np.int64) if self.max_run > 0 else None,
+                    num_unique=u, num_chunks=c)
+
+    def grads(self, torch, grads_np, n, dst, apply_to_table=False, table_rows=0, alpha=1.0):
+        g = to_dev(torch, grads_np)
+        capi.check(capi.lib.nve_b200_dedup_grads(
+            self.h, ptr(g), g.stride(0) * 4, grads_np.shape[1] * 4, n, ptr(self.unique),
+            ptr(self.inverse), ptr(self.offsets), ptr(self.loc_map), ptr(dst), dst.stride(0) * 4,
+            int(apply_to_table), table_rows, alpha, None))
+        torch.cuda.synchronize()
+
+    def close(self):
+        capi.check(capi.lib.nve_b200_deduper_destroy(self.h))
+
+
+def same(a, b):
+    for k in ("unique", "counts", "inverse", "offsets"):
+        assert np.array_equal(a[k], b[k]), k
+    assert (a["num_unique"], a["num_chunks"]) == (b["num_unique"], b["num_chunks"])
+    if b["loc_map"] is not None:
+        assert np.array_equal(a["loc_map"], b["loc_map"])
+
+
+@pytest.mark.parametrize("key_dtype", [np.int32, np.int64])
+@pytest.mark.parametrize("max_run", [-1, 8, 1024])
+def test_dedup_kats(torch_cuda, oracle, key_dtype, max_run):
+    d = Deduper(key_dtype, max_run, 1 << 16)
+    cases = [np.array([9, 3, 7, 1]), np.full(6, 42), np.array([5]), np.zeros(0, dtype=np.int64),
+             np.array([100] * 20 + [1, 2, 3, 4, 5]), np.array([-5, 3, -5, -1, 3, 0]),
+             dg.zipf_keys(5000, 800, 1.05, 3, dg.permutation(800)),
+             dg.zipf_keys(60000, 50000, 1.05, 4, dg.permutation(50000)),
+             np.arange(3000)[::-1].copy()]
+    for keys in cases:
+        keys = keys.astype(key_dtype)
+        same(d.dedup(torch_cuda, keys), oracle.dedup(keys, max_run=max_run))
+    k = np.array([0x105, 0x005, 0x203, 0x003], dtype=key_dtype)
+    same(d.dedup(torch_cuda, k, end_bit=8), oracle.dedup(k, max_run=max_run, end_bit=8))
+    d.close()
+
+
+def test_dedup_rejects_oversized_batch(torch_cuda):
+    d = Deduper(np.int64, -1, 100)
+    with pytest.raises(capi.NveError) as e:
+        d.dedup(torch_cuda, np.arange(101))
+    assert e.value.status == capi.NVE_ERROR_INVALID_ARGUMENT
+    d.close()
+
+
+@pytest.mark.parametrize("max_run", [-1, 16, 1024])
+@pytest.mark.parametrize("width", [4, 32, 128, 212])
+def test_grad_sums(torch_cuda, oracle, max_run, width):
+    torch = torch_cuda
+    n, rows = 20000, 3000
+    keys = dg.zipf_keys(n, rows, 1.05, 5, dg.permutation(rows))
+    keys[::7] = keys[0]          # one heavily repeated key, as in the reference's dedup-grad test
+    d = Deduper(np.int64, max_run, n)
+    g = d.dedup(torch, keys)
+    o = oracle.dedup(keys, max_run=max_run)
+    same(g, o)
+    exact = dg.dyadic_table(n, width, 6, np.float32)
+    dst = torch.full((g["num_unique"], width), 9.0, device="cuda")
+    d.grads(torch, exact, n, dst)
+    want = np.zeros((g["num_unique"], width), np.float64)
+    np.add.at(want, np.searchsorted(g["unique"], keys), exact.astype(np.float64))
+    assert np.array_equal(dst.cpu().numpy().astype(np.float64), want)
+    rnd = np.random.default_rng(7).normal(0, 1e-2, (n, width)).astype(np.float32)
+    d.grads(torch, rnd, n, dst)
+    got = dst.cpu().numpy()
+    assert np.array_equal(got, oracle.dedup_grads(rnd, o))      # same order of additions
+    want = np.zeros((g["num_unique"], width), np.float64)
+    np.add.at(want, np.searchsorted(g["unique"], keys), rnd.astype(np.float64))
+    assert np.max(np.abs(got - want)) <= 1e-6 * max(1.0, np.abs(want).max()) * 50
+    d.close()
+
+
+def test_fused_reduce_and_update_matches_cpu_update(torch_cuda, oracle):
+    """dedup_grads + update_accumulate with SGD lr = 0.01: table[key] += -lr * sum(grad)."""
+    torch = torch_cuda
+    rows, width, n = 5000, 128, 40000
+    table = dg.normal_table(rows, width, 0.02, 8, np.float32)
+    keys = dg.zipf_keys(n, rows, 1.05, 9, dg.permutation(rows))
+    keys[:5] = [-1, rows, rows + 7, -9, 1 << 40]     # out-of-range keys are ignored
+    grads = np.random.default_rng(10).normal(0, 1e-2, (n, width)).astype(np.float32)
+    d = Deduper(np.int64, 1024, n)
+    g = d.dedup(torch, keys)
+    t_dev = to_dev(torch, table)
+    d.grads(torch, grads, n, t_dev, apply_to_table=True, table_rows=rows, alpha=-0.01)
+    got = t_dev.cpu().numpy()
+    o = oracle.dedup(keys, max_run=1024)
+    upd = (np.float32(-0.01) * oracle.dedup_grads(grads, o)).astype(np.float32)
+    want = table.copy()
+    oracle.update_accumulate(want, o["unique"], upd)
+    assert np.array_equal(got, want)
+    exact = table.astype(np.float64)
+    ok = (keys >= 0) & (keys < rows)
+    np.add.at(exact, keys[ok], -0.01 * grads[ok].astype(np.float64))
+    assert np.max(np.abs(got - exact) / np.maximum(np.abs(exact), 1e-3)) <= 1e-6 * 10
+    d.close()
