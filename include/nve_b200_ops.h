@@ -187,6 +187,46 @@ NVE_C_API nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t deduper, const vo
                                             int32_t apply_to_table, int64_t table_rows, float alpha,
                                             void* stream);
 
+/* Device copy of {U, C} of the deduper's last dedup() (two elements of the key type), for
+ * kernels that follow without a host round trip. */
+NVE_C_API nve_status_t nve_b200_deduper_device_num_runs(nve_b200_deduper_t deduper,
+                                                        const void** out);
+
+/* ---- row-sharded table: routing around the all-to-all exchanges --------------------------------
+ * Row r of a table sharded over `world` ranks lives on rank r mod world at local index r / world.
+ * The reference shards a table by mapping every GPU's shard into one virtual address range and
+ * letting the gather kernel read peers over NVLink (src/distributed.cpp:155-256,
+ * src/memblock_nvl.cpp:40-119); here each rank deduplicates its keys, sends every unique key to
+ * its owner, and gets one row per unique key back.  The two all-to-all exchanges are issued by the
+ * caller (torch.distributed / NCCL); these launchers do the bucketing and index maps. */
+
+NVE_C_API nve_status_t nve_b200_shard_route_scratch_bytes(int64_t capacity, uint64_t* out);
+
+/*
+ * Buckets the deduplicated keys by owner.  d_unique[U] ascending (dedup output), d_num_unique =
+ * device pointer to U (key type), capacity >= U.  Outputs: d_send_keys[U] grouped by owner
+ * (ascending key inside a group), d_slot_of_unique[U] = position of unique[u] in d_send_keys,
+ * d_send_counts[0..world) keys per owner (the array must hold 2*world int64; the upper half is
+ * scratch).
+ */
+NVE_C_API nve_status_t nve_b200_shard_route(nve_key_type_t key_type, const void* d_unique,
+                                            const void* d_num_unique, int64_t capacity,
+                                            int32_t world, void* d_send_keys,
+                                            void* d_slot_of_unique, int64_t* d_send_counts,
+                                            void* d_scratch, uint64_t scratch_bytes, void* stream);
+
+/* Received global keys -> local row indices (key / world), in place. */
+NVE_C_API nve_status_t nve_b200_shard_localise(nve_key_type_t key_type, void* d_keys, int64_t n,
+                                               int32_t world, void* stream);
+
+/* d_slot_of_position[i] = d_slot_of_unique[group of original position i] for the n positions of
+ * the batch (dedup without run splitting: d_offsets has U+1 entries). */
+NVE_C_API nve_status_t nve_b200_shard_expand_slots(nve_key_type_t key_type, const void* d_inverse,
+                                                   const void* d_offsets,
+                                                   const void* d_slot_of_unique,
+                                                   const void* d_num_unique, int64_t n,
+                                                   void* d_slot_of_position, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -152,6 +152,11 @@ PROTOTYPES = {
     "nve_b200_deduper_dedup": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32]),
     "nve_b200_dedup_grads": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
                                      _i32, _i64, C.c_float, _vp]),
+    "nve_b200_deduper_device_num_runs": (_i32, [_vp, C.POINTER(_vp)]),
+    "nve_b200_shard_route_scratch_bytes": (_i32, [_i64, C.POINTER(_u64)]),
+    "nve_b200_shard_route": (_i32, [C.c_int, _vp, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "nve_b200_shard_localise": (_i32, [C.c_int, _vp, _i64, _i32, _vp]),
+    "nve_b200_shard_expand_slots": (_i32, [C.c_int, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "nve_b200_update_rows": (_i32, [_vp, _i64, _i64, _i32, _i64, C.c_int, _vp, _i64, _vp, _i64,
                                      C.c_int, C.c_int, _vp]),
 }

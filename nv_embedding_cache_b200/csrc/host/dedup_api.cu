@@ -3,6 +3,7 @@
 #include <cstring>
 
 #include "../kernels/dedup.cuh"
+#include "../kernels/shard_route.cuh"
 #include "context.hpp"
 
 struct nve_b200_deduper_s {
@@ -126,6 +127,51 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0,
         static_cast<cudaStream_t>(stream));
+  });
+}
+
+nve_status_t nve_b200_deduper_device_num_runs(nve_b200_deduper_t d, const void** out) {
+  if (!d || !out) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper and out must not be NULL");
+  *out = nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity);
+  return NVE_SUCCESS;
+}
+
+// ---- row-sharded table routing ----
+nve_status_t nve_b200_shard_route_scratch_bytes(int64_t capacity, uint64_t* out) {
+  if (!out || capacity <= 0) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "bad arguments");
+  return guarded([&] { *out = nve_b200::shard_route_scratch_bytes(capacity); });
+}
+nve_status_t nve_b200_shard_route(nve_key_type_t key_type, const void* d_unique,
+                                  const void* d_num_unique, int64_t capacity, int32_t world,
+                                  void* d_send_keys, void* d_slot_of_unique, int64_t* d_send_counts,
+                                  void* d_scratch, uint64_t scratch_bytes, void* stream) {
+  return guarded([&] {
+    NVE_B200_ARG(d_unique && d_num_unique && d_send_keys && d_slot_of_unique && d_send_counts &&
+                     d_scratch, "shard_route: NULL buffer");
+    NVE_B200_ARG(scratch_bytes >= nve_b200::shard_route_scratch_bytes(capacity),
+                 "shard_route: scratch too small");
+    nve_b200::shard_route(key_type, d_unique, d_num_unique, capacity, world, d_send_keys,
+                          d_slot_of_unique, d_send_counts, d_scratch,
+                          static_cast<cudaStream_t>(stream));
+  });
+}
+nve_status_t nve_b200_shard_localise(nve_key_type_t key_type, void* d_keys, int64_t n,
+                                     int32_t world, void* stream) {
+  return guarded([&] {
+    NVE_B200_ARG(n <= 0 || d_keys != nullptr, "shard_localise: NULL keys");
+    NVE_B200_ARG(world >= 1, "shard_localise: bad world size");
+    nve_b200::shard_localise(key_type, d_keys, n, world, static_cast<cudaStream_t>(stream));
+  });
+}
+nve_status_t nve_b200_shard_expand_slots(nve_key_type_t key_type, const void* d_inverse,
+                                         const void* d_offsets, const void* d_slot_of_unique,
+                                         const void* d_num_unique, int64_t n,
+                                         void* d_slot_of_position, void* stream) {
+  return guarded([&] {
+    NVE_B200_ARG(n <= 0 || (d_inverse && d_offsets && d_slot_of_unique && d_num_unique &&
+                            d_slot_of_position), "shard_expand_slots: NULL buffer");
+    nve_b200::shard_expand_slots(key_type, d_inverse, d_offsets, d_slot_of_unique, d_num_unique, n,
+                                 d_slot_of_position, static_cast<cudaStream_t>(stream));
   });
 }
 

@@ -118,7 +118,9 @@ class GpuTable : public Table {
     Staged d_mask;
     if (hit_mask && !cfg_.uvm_table) d_mask = stage_in(c, "hit_mask", hit_mask, mask_bytes, true, s);
     Staged d_vals;
-    if (values) d_vals = stage_in(c, "values", values, size_t(n) * value_stride, false, s);
+    // rows of keys that stay unresolved must keep the caller's bytes, so a staged (non-device)
+    // output buffer is copied in before the lookup and copied back whole after it
+    if (values) d_vals = stage_in(c, "values", values, size_t(n) * value_stride, true, s);
     find_device(c, n, d_keys.device, static_cast<uint64_t*>(d_mask.device), value_stride,
                 d_vals.device, -1, s);
     d_vals.copy_back(s);

@@ -67,7 +67,7 @@ __device__ __forceinline__ const uint8_t* resolve_row(const PoolKernelParams& p,
 template <In IN, int VB, int GROUP, int VPL>
 __global__ void __launch_bounds__(128) lookup_pool_kernel(const PoolKernelParams p) {
   constexpr int EPV = VB / InTraits<IN>::kElemBytes;
-  constexpr int U = (VPL == 1) ? 8 : (VPL == 2 ? 4 : 2);
+  constexpr int U = (VPL == 1) ? 4 : 2;   // row loads in flight per lane
   constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
 
   const int lane = threadIdx.x & 31;
@@ -202,7 +202,7 @@ inline int pool_block_threads() {
   static const int value = [] {
     const char* e = std::getenv("NVE_B200_POOL_BLOCK");
     const int v = e ? std::atoi(e) : 0;
-    return (v >= 32 && v <= 128 && v % 32 == 0) ? v : 128;
+    return (v >= 32 && v <= 128 && v % 32 == 0) ? v : 64;
   }();
   return value;
 }

@@ -1,0 +1,187 @@
+"""Python edge with the class and method names of the reference's pynve bindings
+(python/pynve/bindings/python_binding.cu:150-391, binding_layers.hpp:72-440), served by the C ABI
+of libnve_b200.  Arguments are raw addresses and raw ``cudaStream_t`` values, exactly as in the
+pybind layer, so ``pynve.torch.nve_layers`` style callers pass ``tensor.data_ptr()`` and
+``torch.cuda.current_stream().cuda_stream``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+
+from . import capi
+from .layers import ExecutionContext, GpuTable, GPUEmbeddingLayer, LinearUVMEmbeddingLayer, _Layer
+
+
+class DataType_t(enum.IntEnum):
+    Unknown = capi.DTYPE_UNKNOWN
+    Float32 = capi.DTYPE_FLOAT32
+    Float16 = capi.DTYPE_FLOAT16
+
+
+class PoolingType_t(enum.IntEnum):
+    Concatenate = capi.POOL_CONCATENATE
+    Sum = capi.POOL_SUM
+    Mean = capi.POOL_MEAN
+    WeightedSum = capi.POOL_WEIGHTED_SUM
+    WeightedMean = capi.POOL_WEIGHTED_MEAN
+
+
+class EmbedLayerConfig:
+    """reference binding_layers.hpp:50-65"""
+
+    def __init__(self):
+        self.logging_interval = -1
+        self.kernel_mode = 0
+        self.kernel_mode_value_1 = 0
+        self.kernel_mode_value_2 = 0
+        self.max_modify_size = 1 << 20
+        self.default_row_index = -1
+
+
+_POOL_NAME = {PoolingType_t.Concatenate: "concatenate", PoolingType_t.Sum: "sum",
+              PoolingType_t.Mean: "mean", PoolingType_t.WeightedSum: "weighted_sum",
+              PoolingType_t.WeightedMean: "weighted_mean"}
+MAX_RUN_SIZE = 1024  # reference binding_layers.hpp:390
+
+
+class NVEmbedBinding:
+    """Common lookup / modify / backward surface (reference NVEmbedBinding<int64_t>)."""
+
+    def __init__(self, layer: _Layer, row_size: int, data_type: DataType_t, device_id: int):
+        self._layer = layer
+        self._dtype = DataType_t(data_type)
+        self._row_elems = row_size
+        self._row_bytes = row_size * (4 if self._dtype == DataType_t.Float32 else 2)
+        self._device = device_id
+        self._ctx: dict[int, ExecutionContext] = {}
+        self._deduper = None
+        self._dedup_capacity = 0
+        self._runs = (C.c_int64 * 2)()
+
+    # one execution context per caller stream, created on first use (binding_layers.hpp:352-367)
+    def _context(self, stream: int) -> ExecutionContext:
+        ctx = self._ctx.get(stream)
+        if ctx is None:
+            ctx = self._layer.create_execution_context(stream or None, stream or None)
+            self._ctx[stream] = ctx
+        return ctx
+
+    def get_embedding_dim(self) -> int:
+        return self._row_elems
+
+    def get_data_type(self) -> DataType_t:
+        return self._dtype
+
+    def lookup(self, num_keys: int, keys: int, output: int, stream: int = 0) -> None:
+        self._layer.lookup(self._context(stream), num_keys, keys, output, self._row_bytes)
+
+    def lookup_with_pooling(self, num_keys: int, keys: int, output: int, pooling_type: int,
+                            num_offsets: int, offsets: int, weight_data_type: int, weights: int,
+                            stream: int = 0) -> None:
+        self._layer.lookup_pooled(self._context(stream), num_keys, keys, output, self._row_bytes,
+                                  _POOL_NAME[PoolingType_t(pooling_type)], int(self._dtype),
+                                  csr_offsets=offsets, num_csr_offsets=num_offsets,
+                                  weights=weights or None, weight_type=int(weight_data_type))
+
+    def accumulate(self, num_keys: int, keys: int, updates: int, stream: int = 0) -> None:
+        self._layer.accumulate(self._context(stream), num_keys, keys, self._row_bytes,
+                               self._row_bytes, updates, int(self._dtype), -1)
+
+    def update(self, num_keys: int, keys: int, updates: int, stream: int = 0) -> None:
+        self._layer.update(self._context(stream), num_keys, keys, self._row_bytes, self._row_bytes,
+                           updates, -1)
+
+    def insert(self, num_keys: int, keys: int, values: int, table_id: int = 0, stream: int = 0) -> None:
+        self._layer.insert(self._context(stream), num_keys, keys, self._row_bytes, self._row_bytes,
+                           values, table_id)
+
+    def clear(self, stream: int = 0) -> None:
+        self._layer.clear(self._context(stream))
+
+    def erase(self, num_keys: int, keys: int, table_id: int = 0, stream: int = 0) -> None:
+        self._layer.erase(self._context(stream), num_keys, keys, table_id)
+
+    def concat_backprop(self, num_keys: int, keys: int, grads: int, unique_keys: int,
+                        output_grads: int, stream: int = 0) -> int:
+        """Backward of an un-pooled lookup: unique keys and the per-key sum of the incoming
+        gradient rows.  Returns the number of unique keys (binding_layers.hpp:131-189).
+        Scratch (inverse map, offsets, chunk map) is owned by this object and grows on demand."""
+        if self._dtype != DataType_t.Float32:
+            raise NotImplementedError("concat_backprop is provided for Float32 gradients")
+        import torch
+        if num_keys > self._dedup_capacity:
+            if self._deduper:
+                capi.check(capi.lib.nve_b200_deduper_destroy(self._deduper))
+            self._deduper = C.c_void_p()
+            capi.check(capi.lib.nve_b200_deduper_create(C.byref(self._deduper), capi.KEY_INT64,
+                                                        MAX_RUN_SIZE, num_keys))
+            dev = torch.device("cuda", self._device)
+            cap = num_keys + num_keys // MAX_RUN_SIZE + 2
+            self._counts = torch.empty(num_keys + 1, dtype=torch.int64, device=dev)
+            self._inverse = torch.empty(num_keys + 1, dtype=torch.int64, device=dev)
+            self._offsets = torch.empty(cap + 1, dtype=torch.int64, device=dev)
+            self._loc_map = torch.empty(cap + 1, dtype=torch.int64, device=dev)
+            self._dedup_capacity = num_keys
+        s = stream or None
+        capi.check(capi.lib.nve_b200_deduper_dedup(
+            self._deduper, keys, num_keys, unique_keys, self._counts.data_ptr(),
+            self._loc_map.data_ptr(), self._runs, self._inverse.data_ptr(), self._offsets.data_ptr(),
+            s, 0))
+        capi.check(capi.lib.nve_b200_dedup_grads(
+            self._deduper, grads, self._row_bytes, self._row_bytes, num_keys, unique_keys,
+            self._inverse.data_ptr(), self._offsets.data_ptr(), self._loc_map.data_ptr(),
+            output_grads, self._row_bytes, 0, 0, 1.0, s))
+        return int(self._runs[0])
+
+    def pooling_backprop(self, *args, **kwargs):
+        raise NotImplementedError("pooled backward is outside the lookup hot path")
+
+    def close(self) -> None:
+        for ctx in self._ctx.values():
+            ctx.wait()
+            ctx.destroy()
+        self._ctx.clear()
+        if self._deduper:
+            capi.check(capi.lib.nve_b200_deduper_destroy(self._deduper))
+            self._deduper = None
+        self._layer.destroy()
+
+
+def _address(memblock) -> int:
+    return memblock if isinstance(memblock, int) else memblock.data_ptr()
+
+
+class GPUEmbedding(NVEmbedBinding):
+    """Dense table in HBM (reference GPUEmbedding, binding_layers.hpp:665-690).  ``memblock`` is the
+    table: a torch tensor (kept alive here) or a raw device address."""
+
+    def __init__(self, row_size: int, num_embeddings: int, data_type: DataType_t, memblock,
+                 device_id: int = 0, config: EmbedLayerConfig | None = None):
+        config = config or EmbedLayerConfig()
+        elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
+        self._memblock = memblock
+        layer = GPUEmbeddingLayer(_address(memblock), num_embeddings, row_size * elem, int(data_type),
+                                  device_id=device_id, default_row_index=config.default_row_index)
+        super().__init__(layer, row_size, data_type, device_id)
+
+
+class LinearUVMEmbedding(NVEmbedBinding):
+    """GPU cache in front of a linear table in host / managed / device memory (reference
+    LinearUVMEmbedding, binding_layers.hpp:534-640)."""
+
+    def __init__(self, row_size: int, num_embeddings: int, data_type: DataType_t, memblock,
+                 gpu_cache_size: int, optimize_for_training: bool = True, device_id: int = 0,
+                 config: EmbedLayerConfig | None = None):
+        config = config or EmbedLayerConfig()
+        elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
+        self._memblock = memblock
+        self._table = GpuTable(gpu_cache_size, row_size * elem, int(data_type), device_id=device_id,
+                               uvm_table=_address(memblock), uvm_num_rows=num_embeddings,
+                               max_modify_size=config.max_modify_size)
+        layer = LinearUVMEmbeddingLayer(self._table, default_row_index=config.default_row_index)
+        super().__init__(layer, row_size, data_type, device_id)
+
+    def close(self) -> None:
+        super().close()
+        self._table.destroy()

@@ -1,0 +1,184 @@
+"""Row-sharded embedding table over several GPUs: one process per GPU, NCCL all-to-all over NVLink.
+
+Row ``r`` of the global table lives on rank ``r mod W`` at local index ``r // W``.  A pooled lookup
+on a rank runs
+
+    dedup keys -> bucket unique keys by owner -> all-to-all (counts, keys)
+    -> owners gather their rows -> all-to-all (rows) -> pool from the received rows
+
+so every distinct row crosses NVLink once per rank and batch, whatever its multiplicity.  The
+device stages are the kernels of libnve_b200 (``nve_b200_deduper_dedup``, ``nve_b200_shard_route``,
+``nve_b200_shard_localise``, ``nve_b200_gather_rows``, ``nve_b200_shard_expand_slots``,
+``nve_b200_lookup_pool``); torch.distributed supplies the collectives.  The reference instead maps
+all shards into one address range and lets its gather kernel read peers directly
+(src/distributed.cpp:155-256, src/memblock_nvl.cpp:40-119); results are the same as a lookup in
+the unsharded table.
+
+``stages`` is the object that runs the device stages.  The product uses :class:`CudaStages`; the
+exchange protocol itself (split sizes, ordering) is backend-agnostic, which is what the
+multi-process CPU tests exercise with a host implementation of the same stage interface.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+def _split_list(t: torch.Tensor):
+    return [int(x) for x in t.cpu().tolist()]
+
+
+class CudaStages:
+    """Device stages on the current CUDA device / current stream, through the C ABI."""
+
+    def __init__(self, max_keys: int, world: int):
+        self.world = world
+        self.max_keys = max_keys
+        self.deduper = C.c_void_p()
+        capi.check(capi.lib.nve_b200_deduper_create(C.byref(self.deduper), capi.KEY_INT64, -1, max_keys))
+        nbytes = C.c_uint64()
+        capi.check(capi.lib.nve_b200_shard_route_scratch_bytes(max_keys, C.byref(nbytes)))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.route_scratch = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        i64 = dict(dtype=torch.int64, device=dev)
+        self.unique = torch.empty(max_keys + 1, **i64)
+        self.counts = torch.empty(max_keys + 1, **i64)
+        self.inverse = torch.empty(max_keys + 1, **i64)
+        self.offsets = torch.empty(max_keys + 2, **i64)
+        self.send_keys = torch.empty(max_keys + 1, **i64)
+        self.slot_of_unique = torch.empty(max_keys + 1, **i64)
+        self.slot_of_position = torch.empty(max_keys + 1, **i64)
+        self.send_counts = torch.zeros(2 * world, **i64)
+        p = C.c_void_p()
+        capi.check(capi.lib.nve_b200_deduper_device_num_runs(self.deduper, C.byref(p)))
+        self.num_unique_dev = p.value
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def dedup_and_route(self, keys: torch.Tensor):
+        """-> (num_unique, send_keys[:U], send_counts[W] device tensor)"""
+        n = keys.numel()
+        runs = (C.c_int64 * 2)()
+        capi.check(capi.lib.nve_b200_deduper_dedup(
+            self.deduper, keys.data_ptr(), n, self.unique.data_ptr(), self.counts.data_ptr(), None,
+            runs, self.inverse.data_ptr(), self.offsets.data_ptr(), self._stream(), 0))
+        u = int(runs[0])
+        capi.check(capi.lib.nve_b200_shard_route(
+            capi.KEY_INT64, self.unique.data_ptr(), self.num_unique_dev, max(u, 1), self.world,
+            self.send_keys.data_ptr(), self.slot_of_unique.data_ptr(), self.send_counts.data_ptr(),
+            self.route_scratch.data_ptr(), self.route_scratch.numel(), self._stream()))
+        return u, self.send_keys[:u], self.send_counts[:self.world]
+
+    def serve(self, shard: torch.Tensor, recv_keys: torch.Tensor) -> torch.Tensor:
+        """Rows of the local shard for the received GLOBAL keys (localised in place)."""
+        r = recv_keys.numel()
+        rows = torch.empty((r, shard.shape[1]), dtype=shard.dtype, device=shard.device)
+        if r == 0:
+            return rows
+        capi.check(capi.lib.nve_b200_shard_localise(capi.KEY_INT64, recv_keys.data_ptr(), r,
+                                                    self.world, self._stream()))
+        row_bytes = shard.shape[1] * shard.element_size()
+        g = capi.GatherArgs()
+        g.table = shard.data_ptr()
+        g.num_rows = shard.shape[0]
+        g.row_stride = shard.stride(0) * shard.element_size()
+        g.value_dtype = capi.DTYPE_FLOAT16 if shard.dtype == torch.float16 else capi.DTYPE_FLOAT32
+        g.default_row_index = -1
+        g.cache = None
+        g.key_type = capi.KEY_INT64
+        g.keys = recv_keys.data_ptr()
+        g.num_keys = r
+        g.output = rows.data_ptr()
+        g.output_stride = row_bytes
+        g.output_dtype = g.value_dtype
+        g.row_copy_bytes = row_bytes
+        capi.check(capi.lib.nve_b200_gather_rows(C.byref(g), self._stream()))
+        return rows
+
+    def pool(self, rows: torch.Tensor, n: int, pooling: int, hotness: int, offsets, out: torch.Tensor):
+        capi.check(capi.lib.nve_b200_shard_expand_slots(
+            capi.KEY_INT64, self.inverse.data_ptr(), self.offsets.data_ptr(),
+            self.slot_of_unique.data_ptr(), self.num_unique_dev, n,
+            self.slot_of_position.data_ptr(), self._stream()))
+        a = capi.PoolArgs()
+        a.table = rows.data_ptr()
+        a.num_rows = rows.shape[0]
+        a.row_stride = rows.shape[1] * rows.element_size()
+        a.value_dtype = capi.DTYPE_FLOAT16 if rows.dtype == torch.float16 else capi.DTYPE_FLOAT32
+        a.row_width = rows.shape[1]
+        a.default_row_index = -1
+        a.cache = None
+        a.key_type = capi.KEY_INT64
+        a.keys = self.slot_of_position.data_ptr()
+        a.num_keys = n
+        a.pooling_type = pooling
+        a.sparse_type = capi.SPARSE_CSR if offsets is not None else capi.SPARSE_FIXED
+        a.csr_offsets = offsets.data_ptr() if offsets is not None else None
+        a.offset_bytes = 8
+        a.num_bags = (offsets.numel() - 1) if offsets is not None else n // hotness
+        a.fixed_hotness = hotness
+        a.weights = None
+        a.output = out.data_ptr()
+        a.output_stride = out.stride(0) * out.element_size()
+        a.output_dtype = capi.DTYPE_FLOAT16 if out.dtype == torch.float16 else capi.DTYPE_FLOAT32
+        capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), self._stream()))
+
+    def close(self):
+        if self.deduper:
+            capi.check(capi.lib.nve_b200_deduper_destroy(self.deduper))
+            self.deduper = None
+
+
+class ShardedEmbeddingTable:
+    """A table of ``world * local_rows`` rows sharded round-robin over the ranks of a process group."""
+
+    POOLING = {"sum": capi.POOL_SUM, "mean": capi.POOL_MEAN}
+
+    def __init__(self, local_shard: torch.Tensor, *, max_keys: int, group=None, stages=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.shard = local_shard
+        self.stages = stages if stages is not None else CudaStages(max_keys, self.world)
+        self.last_exchange = {}
+
+    def lookup_pooled(self, keys: torch.Tensor, pooling: str = "sum", *, fixed_hotness: int = 0,
+                      csr_offsets: torch.Tensor | None = None, out: torch.Tensor | None = None):
+        n = keys.numel()
+        w = self.world
+        u, send_keys, send_counts = self.stages.dedup_and_route(keys)
+        if w > 1:
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+            send_splits, recv_splits = _split_list(send_counts), _split_list(recv_counts)
+            recv_keys = torch.empty(sum(recv_splits), dtype=send_keys.dtype, device=send_keys.device)
+            dist.all_to_all_single(recv_keys, send_keys.contiguous(), recv_splits, send_splits,
+                                   group=self.group)
+        else:
+            send_splits = recv_splits = [u]
+            recv_keys = send_keys.clone()
+        served = self.stages.serve(self.shard, recv_keys)
+        if w > 1:
+            rows = torch.empty((u, self.shard.shape[1]), dtype=self.shard.dtype, device=served.device)
+            dist.all_to_all_single(rows, served, send_splits, recv_splits, group=self.group)
+        else:
+            rows = served
+        num_bags = (csr_offsets.numel() - 1) if csr_offsets is not None else n // fixed_hotness
+        if out is None:
+            out = torch.empty((num_bags, self.shard.shape[1]), dtype=self.shard.dtype, device=rows.device)
+        self.stages.pool(rows, n, self.POOLING[pooling], fixed_hotness, csr_offsets, out)
+        row_bytes = self.shard.shape[1] * self.shard.element_size()
+        remote = u - send_splits[self.rank] if w > 1 else 0
+        self.last_exchange = {"unique": u, "served": int(recv_keys.numel()),
+                              "nvlink_bytes_out": remote * 8 + (int(recv_keys.numel()) - recv_splits[self.rank]) * row_bytes if w > 1 else 0}
+        return out
+
+    def close(self):
+        if hasattr(self.stages, "close"):
+            self.stages.close()

@@ -1,0 +1,225 @@
+"""Benchmark drivers for the other configurations of the lookup hot path (bench.py runs the
+headline one).  Each function builds seeded synthetic inputs of the configuration's shape on the
+current CUDA device, times the path with CUDA events and returns a dict (one JSON line).
+
+    python bench.py --workload c3|c4a|c4b|c5 [--steps K] [--warmup W]
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import time
+
+import numpy as np
+import torch
+
+from . import capi, datagen as dg
+from .layers import GpuTable, GPUEmbeddingLayer, LinearUVMEmbeddingLayer
+
+
+def _hbm_peak(root):
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _time_loop(stream, fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / steps
+
+
+def _fill_rows_fp16(dst: torch.Tensor, seed: int, std: float = 0.02, chunk: int = 1 << 22):
+    """dst: [rows, dim] fp16 tensor (device or pinned host), filled chunk-wise from a device RNG."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    for r0 in range(0, dst.shape[0], chunk):
+        r1 = min(dst.shape[0], r0 + chunk)
+        dst[r0:r1].copy_((torch.randn((r1 - r0, dst.shape[1]), generator=gen, device="cuda") * std).half())
+
+
+def h2d_probe_gbs(nbytes: int = 1 << 30, reps: int = 10) -> float:
+    """Host-link ceiling: pinned host -> device copy, best of `reps`."""
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    best = 1e9
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        d.copy_(h, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e-3)
+    return nbytes / best / 1e9
+
+
+def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, cache_frac=0.10):
+    """LinearUVM cached lookup, no pooling: table in pinned host memory, 10 % of rows cached."""
+    row_bytes = dim * 2
+    stream = torch.cuda.current_stream()
+    table = torch.empty((rows, dim), dtype=torch.float16).pin_memory()
+    _fill_rows_fp16(table, 30)
+    cache_bytes = int(rows * cache_frac) * row_bytes
+    gt = GpuTable(cache_bytes, row_bytes, "float16", uvm_table=table, uvm_num_rows=rows)
+    layer = LinearUVMEmbeddingLayer(gt)
+    ctx = layer.create_execution_context(stream.cuda_stream, stream.cuda_stream)
+    for b in range(20):                                    # explicit, deterministic warm-up
+        k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+        capi.check(capi.lib.nve_b200_gpu_table_insert_from_backing(gt.handle, ctx.handle, batch, k.data_ptr()))
+        ctx.wait()
+    out = torch.empty((batch, dim), dtype=torch.float16, device="cuda")
+    link = h2d_probe_gbs()
+    peak, kind = _hbm_peak(root)
+    res = {"workload": "C3 LinearUVM: 100M x 128 fp16 in pinned host memory, 10% GPU cache, 262144 keys, no pooling",
+           "host_link_probe_gbs": link, "runs": {}}
+    for name, keys_np in (("zipf1.2", dg.zipf_keys(batch, rows, 1.2, 320)),
+                          ("uniform", dg.uniform_keys(batch, rows, 321))):
+        keys = torch.from_numpy(keys_np).cuda()
+        hr = layer.lookup(ctx, batch, keys, out, row_bytes, want_hitrate=True)
+        ctx.wait()
+        ok = bool(torch.equal(out.cpu(), table[torch.from_numpy(keys_np)]))
+        sec = _time_loop(stream, lambda i: layer.lookup(ctx, batch, keys, out, row_bytes), steps, warmup)
+        misses = round((1.0 - hr) * batch)
+        res["runs"][name] = {
+            "keys_per_s": batch / sec, "us_per_lookup": sec * 1e6, "hit_rate": hr, "byte_exact": ok,
+            "algorithmic_gbs": batch * (8 + 2 * row_bytes) / sec / 1e9,
+            "hbm_gbs": ((batch - misses) * 2 * row_bytes + misses * row_bytes + batch * 8) / sec / 1e9,
+            "host_link_gbs": misses * row_bytes / sec / 1e9,
+            "host_link_frac_of_probe": misses * row_bytes / sec / 1e9 / link,
+            "frac_of_hbm_peak": batch * (8 + 2 * row_bytes) / sec / 1e9 / peak, "peak_kind": kind}
+    ctx.destroy(); layer.destroy(); gt.destroy()
+    return res
+
+
+def _quant_table(rows, width, stride, seed):
+    t = torch.zeros((rows, stride), dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    chunk = 1 << 21
+    for r0 in range(0, rows, chunk):
+        r1 = min(rows, r0 + chunk)
+        t[r0:r1, :width] = torch.randint(-127, 128, (r1 - r0, width), generator=gen, device="cuda",
+                                         dtype=torch.int8).view(torch.uint8)
+        scale = torch.rand((r1 - r0, 1), generator=gen, device="cuda") * 9e-3 + 1e-3
+        t[r0:r1, width:width + 4] = scale.view(torch.uint8)
+    return t
+
+
+def run_c4a(root, steps=50, warmup=5, rows=50_000_000, width=256, bags=32_768, hot=20):
+    """find_and_dequant + sum pooling: int8 rows with fp32 row scale -> fp16 sums."""
+    stream = torch.cuda.current_stream()
+    peak, kind = _hbm_peak(root)
+    keys_np = dg.zipf_keys(bags * hot, rows, 1.05, 400)
+    keys = torch.from_numpy(keys_np).cuda()
+    out = torch.empty((bags, width), dtype=torch.float16, device="cuda")
+    res = {"workload": "C4a: 50M x 256 int8 + fp32 scale, 32768 bags x 20 keys Zipf(1.05), dequant + sum -> fp16", "runs": {}}
+    for stride in (width + 4, 272):
+        t = _quant_table(rows, width, stride, 40)
+        a = capi.PoolArgs()
+        a.table, a.num_rows, a.row_stride = t.data_ptr(), rows, stride
+        a.value_dtype, a.row_width, a.default_row_index = capi.DTYPE_QINT8_F32, width, -1
+        a.cache, a.key_type, a.keys, a.num_keys = None, capi.KEY_INT64, keys.data_ptr(), keys.numel()
+        a.pooling_type, a.sparse_type, a.num_bags, a.fixed_hotness = capi.POOL_SUM, capi.SPARSE_FIXED, bags, hot
+        a.output, a.output_stride, a.output_dtype = out.data_ptr(), width * 2, capi.DTYPE_FLOAT16
+
+        def launch(i):
+            capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), stream.cuda_stream))
+        sec = _time_loop(stream, launch, steps, warmup)
+        alg = keys.numel() * (8 + width + 4) + bags * width * 2
+        res["runs"][f"stride{stride}"] = {"keys_per_s": keys.numel() / sec, "us_per_launch": sec * 1e6,
+                                          "algorithmic_gbs": alg / sec / 1e9,
+                                          "frac_of_hbm_peak": alg / sec / 1e9 / peak, "peak_kind": kind}
+        del t
+        torch.cuda.empty_cache()
+    return res
+
+
+def run_c4b(root, steps=30, warmup=5, rows=10_000_000, dim=128, n=1_048_576, lr=0.01):
+    """dedup_grads + update_accumulate: 1M (key, grad) pairs into a 10M x 128 fp32 table."""
+    stream = torch.cuda.current_stream()
+    peak, kind = _hbm_peak(root)
+    table = torch.empty((rows, dim), dtype=torch.float32, device="cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(50)
+    table.normal_(0, 0.02, generator=gen)
+    keys_np = dg.zipf_keys(n, rows, 1.05, 500)
+    keys = torch.from_numpy(keys_np).cuda()
+    grads = torch.empty((n, dim), dtype=torch.float32, device="cuda").normal_(0, 1e-2, generator=gen)
+    i64 = dict(dtype=torch.int64, device="cuda")
+    cap = n + n // 1024 + 2
+    uniq, counts, inverse = torch.empty(n + 1, **i64), torch.empty(n + 1, **i64), torch.empty(n + 1, **i64)
+    offsets, loc = torch.empty(cap + 1, **i64), torch.empty(cap + 1, **i64)
+    d = C.c_void_p()
+    capi.check(capi.lib.nve_b200_deduper_create(C.byref(d), capi.KEY_INT64, 1024, n))
+    runs = (C.c_int64 * 2)()
+    s = stream.cuda_stream
+
+    def dedup(i):
+        capi.check(capi.lib.nve_b200_deduper_dedup(d, keys.data_ptr(), n, uniq.data_ptr(), counts.data_ptr(),
+                                                   loc.data_ptr(), runs, inverse.data_ptr(), offsets.data_ptr(), s, 24))
+
+    def apply(i):
+        capi.check(capi.lib.nve_b200_dedup_grads(d, grads.data_ptr(), dim * 4, dim * 4, n, uniq.data_ptr(),
+                                                 inverse.data_ptr(), offsets.data_ptr(), loc.data_ptr(),
+                                                 table.data_ptr(), dim * 4, 1, rows, -lr, s))
+    t_dedup = _time_loop(stream, dedup, steps, warmup)
+    u = int(runs[0])
+    t_apply = _time_loop(stream, apply, steps, warmup)
+    t_both = _time_loop(stream, lambda i: (dedup(i), apply(i)), steps, warmup)
+    alg = n * (8 + dim * 4) + u * 2 * dim * 4
+    capi.check(capi.lib.nve_b200_deduper_destroy(d))
+    return {"workload": "C4b: dedup_grads + update_accumulate, 1048576 pairs Zipf(1.05), 10M x 128 fp32, SGD lr 0.01",
+            "unique": u, "keys_per_s": n / t_both, "us_dedup": t_dedup * 1e6, "us_reduce_apply": t_apply * 1e6,
+            "us_total": t_both * 1e6, "algorithmic_gbs": alg / t_both / 1e9,
+            "reduce_apply_gbs": alg / t_apply / 1e9, "frac_of_hbm_peak": alg / t_both / 1e9 / peak,
+            "peak_kind": kind}
+
+
+def run_c5(root, steps=30, warmup=5, rows_per_rank=250_000_000, dim=64, bags=131_072, hot=8):
+    """Row-sharded table, weak scaling: 32 GB of fp16 rows per rank, dedup + all-to-all each way."""
+    import torch.distributed as dist
+    from .sharded import ShardedEmbeddingTable
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    stream = torch.cuda.current_stream()
+    shard = torch.empty((rows_per_rank, dim), dtype=torch.float16, device="cuda")
+    _fill_rows_fp16(shard, 60 + rank)
+    total = rows_per_rank * world
+    n = bags * hot
+    t = ShardedEmbeddingTable(shard, max_keys=n)
+    batches = [torch.from_numpy(dg.zipf_keys(n, total, 1.05, 600 + 10 * b + rank)).cuda() for b in range(4)]
+    out = torch.empty((bags, dim), dtype=torch.float16, device="cuda")
+
+    def step(i):
+        t.lookup_pooled(batches[i % 4], "sum", fixed_hotness=hot, out=out)
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        step(warmup + i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sec = torch.tensor([e0.elapsed_time(e1) * 1e-3 / steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+    sec = float(sec.item())
+    ex = t.last_exchange
+    t.close()
+    return {"workload": "C5 sharded table: 250M x W rows x 64 fp16, 131072 bags x 8 per rank, Zipf(1.05), sum",
+            "n_gpus": world, "keys_per_s": n * world / sec, "ms_per_step": sec * 1e3,
+            "unique_per_rank": ex.get("unique"), "served_per_rank": ex.get("served"),
+            "nvlink_gbs_out_per_rank": ex.get("nvlink_bytes_out", 0) / sec / 1e9, "scaling": "weak"}

@@ -231,7 +231,8 @@ static int cmp_key_pos(const void* a, const void* b) {
 /*
  * cuda_ops/deduper.cuh:136-221: stable sort of (key, position) by the low `end_bit` bits of the
  * key (signed order when all bits take part, as the device radix sort orders signed keys), then
- * run-length encoding.  Outputs (all int64 here): unique ascending, counts, inverse = positions
+ * run-length encoding of the full keys in that order (so keys that differ above end_bit stay
+ * separate runs; callers pass an end_bit that covers their key range).  Outputs (all int64 here): unique ascending, counts, inverse = positions
  * grouped by key with ascending position inside a group, offsets = chunk starts (+ total), loc_map
  * = group of each chunk, where a group is split into chunks of at most max_run positions when
  * max_run > 0 (:39-81).  num_runs[0] = groups, num_runs[1] = chunks.
@@ -253,8 +254,8 @@ NVE_EXPORT void nve_oracle_dedup(const void* keys, int key_bytes, int64_t n, int
   qsort(kp, (size_t)n, sizeof(KeyPos), cmp_key_pos);
   int64_t groups = 0, chunks = 0;
   for (int64_t i = 0; i < n;) {
-    int64_t j = i;
-    while (j < n && kp[j].key == kp[i].key) j++;
+    int64_t j = i;   /* runs are runs of equal FULL keys in the (partially) sorted order */
+    while (j < n && orig[kp[j].pos] == orig[kp[i].pos]) j++;
     unique[groups] = orig[kp[i].pos];
     counts[groups] = j - i;
     if (max_run > 0) {

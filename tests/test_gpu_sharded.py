@@ -1,0 +1,118 @@
+"""GPU checks of the row-sharded table: the routing kernels against numpy, the full lookup at
+world size 1 against the oracle, and (when the box has at least 2 GPUs) a 2-rank NCCL run."""
+import ctypes as C
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from nv_embedding_cache_b200 import capi, datagen as dg
+from nve_helpers import to_dev
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_route_localise_expand_against_numpy(torch_cuda):
+    torch = torch_cuda
+    from nv_embedding_cache_b200.sharded import CudaStages
+    for world in (1, 2, 3, 8):
+        n, rows = 20000, 100000
+        st = CudaStages(n, world)
+        keys = dg.zipf_keys(n, rows, 1.05, world, dg.permutation(rows))
+        d_keys = to_dev(torch, keys)
+        u, send_keys, send_counts = st.dedup_and_route(d_keys)
+        uniq = np.unique(keys)
+        assert u == uniq.size
+        owner = uniq % world
+        order = np.argsort(owner, kind="stable")
+        assert np.array_equal(send_keys.cpu().numpy(), uniq[order])
+        assert np.array_equal(send_counts.cpu().numpy(), np.bincount(owner, minlength=world))
+        slot = np.empty(u, np.int64)
+        slot[order] = np.arange(u)
+        assert np.array_equal(st.slot_of_unique[:u].cpu().numpy(), slot)
+        # expand: position i -> slot of its unique key
+        capi.check(capi.lib.nve_b200_shard_expand_slots(
+            capi.KEY_INT64, st.inverse.data_ptr(), st.offsets.data_ptr(), st.slot_of_unique.data_ptr(),
+            st.num_unique_dev, n, st.slot_of_position.data_ptr(), None))
+        torch.cuda.synchronize()
+        assert np.array_equal(st.slot_of_position[:n].cpu().numpy(), slot[np.searchsorted(uniq, keys)])
+        k2 = d_keys.clone()
+        capi.check(capi.lib.nve_b200_shard_localise(capi.KEY_INT64, k2.data_ptr(), n, world, None))
+        torch.cuda.synchronize()
+        assert np.array_equal(k2.cpu().numpy(), keys // world)
+        st.close()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_world_size_one_matches_oracle(torch_cuda, oracle, dtype):
+    torch = torch_cuda
+    from nv_embedding_cache_b200.sharded import ShardedEmbeddingTable
+    rows, dim = 50000, 64
+    npdt = np.float16 if dtype == "f16" else np.float32
+    table = dg.normal_table(rows, dim, 0.02, 3, npdt)
+    t = ShardedEmbeddingTable(to_dev(torch, table), max_keys=1 << 16)
+    keys = dg.zipf_keys(4096 * 8, rows, 1.05, 5, dg.permutation(rows))
+    out = t.lookup_pooled(to_dev(torch, keys), "sum", fixed_hotness=8)
+    torch.cuda.synchronize()
+    want = oracle.lookup_pooled(table.view(np.uint8).reshape(rows, -1), dtype, dim, keys, "sum",
+                                hotness=8, out_dtype=dtype)
+    assert np.array_equal(out.cpu().numpy().view(np.uint8), want.view(np.uint8))
+    _, offs = dg.csr_bags(3000, 0, 20, 6)
+    keys = dg.uniform_keys(int(offs[-1]), rows, 7)
+    out = t.lookup_pooled(to_dev(torch, keys), "mean", csr_offsets=to_dev(torch, offs))
+    torch.cuda.synchronize()
+    want = oracle.lookup_pooled(table.view(np.uint8).reshape(rows, -1), dtype, dim, keys, "mean",
+                                offsets=offs, out_dtype=dtype)
+    assert np.array_equal(out.cpu().numpy().view(np.uint8), want.view(np.uint8))
+    t.close()
+
+
+WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["NVE_ROOT"])
+from nv_embedding_cache_b200 import datagen as dg
+from nv_embedding_cache_b200.sharded import ShardedEmbeddingTable
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+rows_per_rank, dim = 40000, 64
+total = rows_per_rank * world
+table = dg.dyadic_table(total, dim, 3, np.float16)
+shard = torch.from_numpy(table[rank::world].copy()).cuda()
+t = ShardedEmbeddingTable(shard, max_keys=1 << 16)
+ok = True
+for step in range(3):
+    keys = dg.zipf_keys(2048 * 8, total, 1.05, 100 + 10 * step + rank, dg.permutation(total))
+    out = t.lookup_pooled(torch.from_numpy(keys).cuda(), "sum", fixed_hotness=8)
+    torch.cuda.synchronize()
+    want = table[keys].astype(np.float32).reshape(2048, 8, dim).sum(1).astype(np.float16)
+    ok = ok and bool(np.array_equal(out.cpu().numpy(), want))
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+t.close()
+dist.barrier()
+dist.destroy_process_group()
+sys.exit(0 if int(flag.item()) == 1 else 3)
+'''
+
+
+def test_two_ranks_nccl(torch_cuda, tmp_path):
+    torch = torch_cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, NVE_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                          "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port",
+                          str(port), str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]

@@ -46,8 +46,13 @@ def test_split_long_run(oracle):
 
 def test_reduced_end_bit_and_random_round_trip(oracle):
     k = np.array([0x105, 0x005, 0x203, 0x003], dtype=np.int64)
-    d = oracle.dedup(k, end_bit=8)   # only the low byte orders and groups the keys
-    assert d["counts"].tolist() == [2, 2] and d["inverse"].tolist() == [2, 3, 0, 1]
+    d = oracle.dedup(k, end_bit=8)   # only the low byte orders the keys; runs compare full keys
+    assert d["unique"].tolist() == [0x203, 0x003, 0x105, 0x005] and d["counts"].tolist() == [1, 1, 1, 1]
+    assert d["inverse"].tolist() == [2, 3, 0, 1]
+    k = np.array([200, 7, 200, 3, 7, 255], dtype=np.int64)
+    d = oracle.dedup(k, end_bit=8)   # keys below 2^end_bit: identical to the full sort
+    full = oracle.dedup(k)
+    assert all(np.array_equal(d[x], full[x]) for x in ("unique", "counts", "inverse", "offsets"))
     keys = dg.zipf_keys(5000, 800, 1.05, 3, dg.permutation(800))
     d = oracle.dedup(keys, max_run=16)
     check_contract(keys, d)
