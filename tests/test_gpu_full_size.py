@@ -1,0 +1,115 @@
+"""Parity at the benchmark configurations' full sizes.  The tables are generated on the device;
+the oracle works on a host mirror of the rows a batch actually touches (rows are re-indexed, which
+does not change any result), so full-size batches are checked element for element."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from nv_embedding_cache_b200 import capi, datagen as dg
+from nve_helpers import ptr, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def touched_mirror(torch, table_dev, keys_np):
+    """(compact host table of the touched rows as bytes, keys re-indexed into it)"""
+    uniq, inv = np.unique(keys_np, return_inverse=True)
+    rows = table_dev[torch.from_numpy(uniq).cuda()].contiguous().cpu().numpy()
+    return rows.view(np.uint8).reshape(rows.shape[0], -1), inv.astype(np.int64)
+
+
+def test_c2_full_table_batch_matches_oracle(torch_cuda, oracle):
+    """One table of the headline config: 4M x 128 fp16, 65536 CSR bags of 1..32 keys, Zipf(1.1), mean."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+    rows, dim, bags = 4_000_000, 128, 65_536
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(20)
+    table = (torch.randn((rows, dim), generator=gen, device="cuda") * 0.02).half()
+    _, offs = dg.csr_bags(bags, 1, 32, 1200)
+    keys = dg.zipf_keys(int(offs[-1]), rows, 1.1, 6200, dg.permutation(rows))
+    layer = GPUEmbeddingLayer(table, rows, dim * 2, "float16")
+    ctx = layer.create_execution_context()
+    out = torch.zeros((bags, dim), dtype=torch.float16, device="cuda")
+    layer.lookup_pooled(ctx, keys.size, to_dev(torch, keys), out, dim * 2, "mean", "float16",
+                        csr_offsets=to_dev(torch, offs), num_csr_offsets=offs.size)
+    ctx.wait()
+    mirror, local = touched_mirror(torch, table, keys)
+    want = oracle.lookup_pooled(mirror, "f16", dim, local, "mean", offsets=offs, out_dtype="f16")
+    got = out.cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    # size-independent property: un-pooled rows of the same keys, summed in fp32 by torch, divided
+    rows_out = torch.zeros((keys.size, dim), dtype=torch.float16, device="cuda")
+    layer.lookup(ctx, keys.size, to_dev(torch, keys), rows_out, dim * 2)
+    ctx.wait()
+    seg = torch.repeat_interleave(torch.arange(bags, device="cuda"), torch.from_numpy(np.diff(offs)).cuda())
+    acc = torch.zeros((bags, dim), dtype=torch.float32, device="cuda").index_add_(0, seg, rows_out.float())
+    mean = (acc / torch.from_numpy(np.diff(offs)).cuda().float()[:, None]).cpu().numpy()
+    assert np.max(np.abs(got.astype(np.float32) - mean)) <= 1e-5 + 2 ** -11 * np.abs(mean).max()
+    ctx.destroy(); layer.destroy()
+
+
+def test_c4a_full_batch_dequant_sum_matches_oracle(torch_cuda, oracle):
+    """32768 bags x 20 keys over int8 rows with fp32 scale (tight 260-byte rows and padded 272),
+    table scaled to 5M rows to keep the test short; the batch has the full size."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.workloads import _quant_table
+    rows, width, bags, hot = 5_000_000, 256, 32_768, 20
+    keys = dg.zipf_keys(bags * hot, rows, 1.05, 400)
+    d_keys = to_dev(torch, keys)
+    for stride in (260, 272):
+        t = _quant_table(rows, width, stride, 40)
+        out = torch.zeros((bags, width), dtype=torch.float16, device="cuda")
+        a = capi.PoolArgs()
+        a.table, a.num_rows, a.row_stride = t.data_ptr(), rows, stride
+        a.value_dtype, a.row_width, a.default_row_index = capi.DTYPE_QINT8_F32, width, -1
+        a.cache, a.key_type, a.keys, a.num_keys = None, capi.KEY_INT64, d_keys.data_ptr(), keys.size
+        a.pooling_type, a.sparse_type, a.num_bags, a.fixed_hotness = capi.POOL_SUM, capi.SPARSE_FIXED, bags, hot
+        a.output, a.output_stride, a.output_dtype = out.data_ptr(), width * 2, capi.DTYPE_FLOAT16
+        capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), None))
+        torch.cuda.synchronize()
+        mirror, local = touched_mirror(torch, t, keys)
+        want = oracle.lookup_pooled(mirror, "qint8_f32", width, local, "sum", hotness=hot, out_dtype="f16")
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16)), stride
+        del t
+
+
+def test_c4b_full_batch_update_matches_oracle(torch_cuda, oracle):
+    """1,048,576 (key, grad) pairs, Zipf(1.05), fp32 x 128, SGD lr 0.01 through dedup + fused apply."""
+    torch = torch_cuda
+    rows, dim, n = 10_000_000, 128, 1_048_576
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(50)
+    table = torch.empty((rows, dim), dtype=torch.float32, device="cuda").normal_(0, 0.02, generator=gen)
+    keys = dg.zipf_keys(n, rows, 1.05, 500)
+    grads = torch.empty((n, dim), dtype=torch.float32, device="cuda").normal_(0, 1e-2, generator=gen)
+    mirror_before, local = touched_mirror(torch, table, keys)
+    d = C.c_void_p()
+    capi.check(capi.lib.nve_b200_deduper_create(C.byref(d), capi.KEY_INT64, 1024, n))
+    i64 = dict(dtype=torch.int64, device="cuda")
+    cap = n + n // 1024 + 2
+    uniq, counts, inverse = torch.zeros(n + 1, **i64), torch.zeros(n + 1, **i64), torch.zeros(n + 1, **i64)
+    offsets, loc = torch.zeros(cap + 1, **i64), torch.zeros(cap + 1, **i64)
+    runs = (C.c_int64 * 2)()
+    d_keys = to_dev(torch, keys)
+    capi.check(capi.lib.nve_b200_deduper_dedup(d, ptr(d_keys), n, ptr(uniq), ptr(counts), ptr(loc), runs,
+                                               ptr(inverse), ptr(offsets), None, 24))
+    u = int(runs[0])
+    o = oracle.dedup(keys, max_run=1024)
+    assert u == o["num_unique"] and int(runs[1]) == o["num_chunks"]
+    assert np.array_equal(uniq[:u].cpu().numpy(), o["unique"])
+    assert np.array_equal(counts[:u].cpu().numpy(), o["counts"])
+    assert np.array_equal(inverse[:n].cpu().numpy(), o["inverse"])
+    capi.check(capi.lib.nve_b200_dedup_grads(d, ptr(grads), dim * 4, dim * 4, n, ptr(uniq), ptr(inverse),
+                                             ptr(offsets), ptr(loc), ptr(table), dim * 4, 1, rows, -0.01, None))
+    torch.cuda.synchronize()
+    got = table[torch.from_numpy(o["unique"]).cuda()].cpu().numpy()
+    upd = (np.float32(-0.01) * oracle.dedup_grads(grads.cpu().numpy(), o)).astype(np.float32)
+    want = mirror_before.view(np.float32).reshape(u, dim).copy()
+    oracle.update_accumulate(want, np.arange(u, dtype=np.int64), upd)
+    assert np.array_equal(got, want)
+    exact = mirror_before.view(np.float32).reshape(u, dim).astype(np.float64)
+    np.add.at(exact, local, -0.01 * grads.cpu().numpy().astype(np.float64))
+    assert np.max(np.abs(got - exact) / np.maximum(np.abs(exact), 1e-2)) <= 1e-6 * 20
+    capi.check(capi.lib.nve_b200_deduper_destroy(d))
