@@ -187,6 +187,32 @@ NVE_C_API nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t deduper, const vo
                                             int32_t apply_to_table, int64_t table_rows, float alpha,
                                             void* stream);
 
+/*
+ * Same reduction as nve_b200_dedup_grads, for callers that must not allocate device memory at
+ * this point: a training step whose memory pool is fully planned, a plugin that owns only the
+ * buffers it was given, a thread that must stay out of the driver's allocator.  (No counterpart
+ * in the reference: its reduction combines chunks with atomics and needs no scratch.)
+ *
+ * It takes no deduper object.  The caller passes the arrays a dedup() produced and
+ * d_num_runs = device pointer to {U, C} (nve_b200_deduper_device_num_runs), plus the max_run_size
+ * that dedup() used.  The partial sums of split groups go to a 4 MiB array built into the library
+ * (held by every GPU that loads it, until the process exits); a call that would need more than
+ * that -- (2 * (num_keys / max_run_size + 1) + 2) * row_bytes bytes -- is rejected with
+ * NVE_ERROR_INVALID_ARGUMENT.  With max_run_size == -1 no scratch is used at all.
+ *
+ * The call never calls cudaMalloc / cudaFree or any allocating routine.  The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress, with that device current);
+ * make that first call before starting a stream capture.  All calls on a device share the one
+ * array: nothing in it has to be zero (every slot is written before it is read within a call),
+ * but two calls that overlap on the GPU would overwrite each other's partial sums, so keep them
+ * on one stream or otherwise ordered.
+ */
+NVE_C_API nve_status_t nve_b200_dedup_grads_static(
+    nve_key_type_t key_type, int64_t max_run_size, const void* d_grads, int64_t grad_stride,
+    int64_t row_bytes, int64_t num_keys, const void* d_unique, const void* d_inverse,
+    const void* d_offsets, const void* d_loc_map, const void* d_num_runs, void* d_dst,
+    int64_t dst_stride, int32_t apply_to_table, int64_t table_rows, float alpha, void* stream);
+
 /* Device copy of {U, C} of the deduper's last dedup() (two elements of the key type), for
  * kernels that follow without a host round trip. */
 NVE_C_API nve_status_t nve_b200_deduper_device_num_runs(nve_b200_deduper_t deduper,

@@ -26,6 +26,8 @@
 
 #include <cub/cub.cuh>
 
+#include <mutex>
+
 #include "device_common.cuh"
 
 namespace nve_b200 {
@@ -42,9 +44,7 @@ __global__ void iota_kernel(T* out, int64_t n) {
   if (i < n) out[i] = static_cast<T>(i);
 }
 
-// head[i] = 1 at the first entry of every group; chunk_head[i] = 1 additionally every max_run
-// entries inside a group needs the group start, which is only known after the scan of `head`,
-// so chunk heads are derived in the second kernel from (i - group_start) % max_run.
+// head[i] = 1 at the first entry of every group of equal keys in the sorted order.
 template <typename KeyT>
 __global__ void mark_group_heads_kernel(const KeyT* sorted, uint32_t* head, int64_t n) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -376,4 +376,73 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   NVE_B200_CUDA(cudaGetLastError());
 }
 
+// ---- allocation-free variant of the gradient reduction ---------------------------------------
+// The regular entry point takes the scratch for split groups from the deduper object, which
+// allocates it.  Some callers cannot allocate device memory where they reduce gradients: a
+// training step whose memory pool is already planned to the last byte, a plugin that is handed
+// nothing but its input and output buffers, a latency-critical thread that must not enter the
+// driver's allocator (that call can serialise against other threads' GPU work).  For them the
+// scratch lives here, in a fixed array inside the library's device image.  Every GPU that loads the
+// library holds these bytes until the process exits, hence the modest size.
+constexpr size_t kStaticPartialBytes = size_t(4) << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_partial[kStaticPartialBytes];
+
+namespace {
+std::mutex g_static_mu;
+float* g_static_partial_addr[64] = {nullptr};  // by device ordinal
+}  // namespace
+
+// Device address of g_static_partial on the CURRENT device.  In host code the array's name is a
+// handle the runtime understands, not a device pointer: handing it to a kernel would fault or,
+// where the GPU can reach host memory, quietly use the wrong bytes.  The runtime translates it per
+// device, so this is done once per device, with that device current, and kernels get the result.
+static float* static_partial_for_current_device() {
+  int dev = 0;
+  NVE_B200_CUDA(cudaGetDevice(&dev));
+  NVE_B200_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_partial_addr[dev] == nullptr) {
+    void* p = nullptr;
+    NVE_B200_CUDA(cudaGetSymbolAddress(&p, g_static_partial));
+    g_static_partial_addr[dev] = static_cast<float*>(p);
+  }
+  return g_static_partial_addr[dev];
+}
+
 }  // namespace nve_b200
+
+extern "C" nve_status_t nve_b200_dedup_grads_static(
+    nve_key_type_t key_type, int64_t max_run_size, const void* d_grads, int64_t grad_stride,
+    int64_t row_bytes, int64_t num_keys, const void* d_unique, const void* d_inverse,
+    const void* d_offsets, const void* d_loc_map, const void* d_num_runs, void* d_dst,
+    int64_t dst_stride, int32_t apply_to_table, int64_t table_rows, float alpha, void* stream) {
+  using namespace nve_b200;
+  return guarded([&] {
+    if (num_keys <= 0) return;
+    NVE_B200_ARG(key_type == NVE_KEY_INT32 || key_type == NVE_KEY_INT64, "Unsupported key type");
+    NVE_B200_ARG(max_run_size == -1 || max_run_size > 0, "max_run_size must be -1 or positive");
+    NVE_B200_ARG(d_grads && d_inverse && d_offsets && d_num_runs && d_dst,
+                 "dedup_grads_static: NULL buffer");
+    NVE_B200_ARG(!apply_to_table || d_unique != nullptr, "dedup_grads_static: unique keys are required");
+    NVE_B200_ARG(max_run_size <= 0 || d_loc_map != nullptr,
+                 "dedup_grads_static: the chunk map is required when runs are split");
+    int64_t partial_rows = 0;
+    float* partial = nullptr;
+    int64_t max_chunks = num_keys;
+    if (max_run_size > 0) {
+      // split groups park one partial row per chunk; at most 2 * (n / max_run + 1) + 2 rows
+      partial_rows = 2 * (num_keys / max_run_size + 1) + 2;
+      const uint64_t need = static_cast<uint64_t>(partial_rows) * static_cast<uint64_t>(row_bytes);
+      NVE_B200_ARG(need <= kStaticPartialBytes,
+                   "dedup_grads_static: ", num_keys, " keys with runs of ", max_run_size, " and rows of ",
+                   row_bytes, " bytes need ", need, " bytes of scratch; the built-in scratch holds ",
+                   kStaticPartialBytes, " (use nve_b200_dedup_grads, which allocates)");
+      partial = static_partial_for_current_device();
+      max_chunks = num_keys + num_keys / max_run_size + 1;
+    }
+    dedup_grads_run(key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
+                    max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
+                    dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
+                    static_cast<cudaStream_t>(stream));
+  });
+}
