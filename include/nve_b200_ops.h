@@ -57,6 +57,12 @@ typedef struct {
   void* output;                 /* [num_bags][row_width] */
   int64_t output_stride;        /* bytes */
   nve_data_type_t output_dtype; /* FLOAT32 or FLOAT16 */
+  /* Row-sharded table (optional): HOST array of num_shards device addresses, one per rank, each
+   * mapped into this GPU's address space (peer / symmetric memory).  Row r is read from
+   * shard_tables[r % num_shards] at local row r / num_shards; `table` is ignored, `num_rows` is
+   * the global row count.  num_shards == 0: plain table.  At most 32 shards. */
+  const void* const* shard_tables;
+  int32_t num_shards;
 } nve_b200_pool_args_t;
 
 /*

@@ -55,7 +55,8 @@ class PoolArgs(C.Structure):
                 ("pooling_type", C.c_int), ("sparse_type", C.c_int), ("csr_offsets", _vp),
                 ("offset_bytes", _i32), ("num_bags", _i64), ("fixed_hotness", _i64),
                 ("weights", _vp), ("weight_dtype", _i32), ("output", _vp),
-                ("output_stride", _i64), ("output_dtype", _i32)]
+                ("output_stride", _i64), ("output_dtype", _i32),
+                ("shard_tables", C.POINTER(_vp)), ("num_shards", _i32)]
 
 
 class GatherArgs(C.Structure):

@@ -1,5 +1,7 @@
 #include "context.hpp"
 
+#include "../kernels/gather_bulk_api.hpp"
+
 namespace nve_b200 {
 
 ScopedDevice::ScopedDevice(int device) {
@@ -70,6 +72,9 @@ void ExecutionContext::wait() {
   ScopedDevice sd(device_);
   NVE_B200_CUDA(cudaStreamSynchronize(lookup_stream_));
   NVE_B200_CUDA(cudaStreamSynchronize(modify_stream_));
+  if (gather_bulk_take_error()) {
+    throw RuntimeFailure("a bulk-copy wait in the gather kernel ran out; output rows are incomplete");
+  }
 }
 
 void ContextRegistry::add(ExecutionContext* ctx) {

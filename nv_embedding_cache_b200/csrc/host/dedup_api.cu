@@ -16,6 +16,8 @@ struct nve_b200_deduper_s {
   float* partial = nullptr;    // partial sums of split groups
   int64_t partial_rows = 0;
   int64_t partial_row_bytes = 0;
+  int64_t last_num_keys = -1;  // batch size and chunk count of the last dedup()
+  int64_t last_chunks = 0;
 };
 
 namespace nve_b200 {
@@ -101,6 +103,9 @@ nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, in
                         end_bit, d->pinned, s);
     NVE_B200_CUDA(cudaStreamSynchronize(s));  // the counts are part of the return value
     std::memcpy(h_num_runs_out, d->pinned, size_t(2) * kb);
+    d->last_num_keys = num_keys;
+    d->last_chunks = kb == 8 ? static_cast<const int64_t*>(d->pinned)[1]
+                             : static_cast<const int32_t*>(d->pinned)[1];
   });
 }
 
@@ -118,8 +123,10 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
     NVE_B200_ARG(d->max_run <= 0 || d_loc_map != nullptr,
                  "dedup_grads: the chunk map is required when runs are split");
     nve_b200::ensure_partial(d, num_keys, row_bytes);
-    // chunks <= unique + n / max_run <= n + n / max_run
-    const int64_t max_chunks = d->max_run > 0 ? num_keys + num_keys / d->max_run + 1 : num_keys;
+    // launch bound: the chunk count of the last dedup() (read back by that call); fall back to
+    // chunks <= n + n / max_run when this batch is not the one that was deduplicated last
+    int64_t max_chunks = d->max_run > 0 ? num_keys + num_keys / d->max_run + 1 : num_keys;
+    if (d->last_num_keys == num_keys && d->last_chunks > 0) max_chunks = d->last_chunks;
     nve_b200::dedup_grads_run(
         d->key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
         d->max_run > 0 ? d_loc_map : nullptr, d_unique,

@@ -7,6 +7,7 @@
 #include "../kernels/lookup_pool.cuh"
 #include "../kernels/pool_dense.cuh"
 #include "../kernels/lookup_rows.cuh"
+#include "../kernels/gather_bulk.cuh"
 #include "../kernels/update_rows.cuh"
 
 namespace nve_b200 {
@@ -94,7 +95,11 @@ int pick_vector_bytes(std::initializer_list<uint64_t> quantities, int floor_byte
 }  // namespace
 
 void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream_t stream) {
-  NVE_B200_ARG(a.table != nullptr || a.cache != nullptr, "lookup_pool: no table and no cache");
+  NVE_B200_ARG(a.table != nullptr || a.cache != nullptr || a.num_shards > 0,
+               "lookup_pool: no table and no cache");
+  NVE_B200_ARG(a.num_shards >= 0 && a.num_shards <= kMaxShards, "lookup_pool: at most 32 shards");
+  NVE_B200_ARG(a.num_shards == 0 || (a.shard_tables != nullptr && a.cache == nullptr),
+               "lookup_pool: a sharded table needs shard_tables and no cache");
   NVE_B200_ARG(a.output != nullptr, "lookup_pool: output is NULL");
   NVE_B200_ARG(a.pooling_type == NVE_POOL_SUM || a.pooling_type == NVE_POOL_MEAN ||
                    a.pooling_type == NVE_POOL_WEIGHTED_SUM ||
@@ -153,7 +158,19 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
     cache_base = reinterpret_cast<uint64_t>(p.cache.cache_ptr);
     cache_row = p.cache.row_size;
   }
-  const int vb = pick_vector_bytes({reinterpret_cast<uint64_t>(a.table),
+  uint64_t shard_align = 0;
+  p.num_shards = a.num_shards;
+  if (a.num_shards > 0) {
+    p.table = nullptr;
+    fast_div_params(static_cast<uint32_t>(a.num_shards), &p.shard_magic, &p.shard_shift);
+    for (int i = 0; i < a.num_shards; i++) {
+      NVE_B200_ARG(a.shard_tables[i] != nullptr, "lookup_pool: NULL shard address");
+      p.shard_base[i] = static_cast<const uint8_t*>(a.shard_tables[i]);
+      shard_align |= reinterpret_cast<uint64_t>(a.shard_tables[i]);
+    }
+  }
+  const int vb = pick_vector_bytes({a.num_shards > 0 ? shard_align & 15u
+                                                     : reinterpret_cast<uint64_t>(a.table),
                                     static_cast<uint64_t>(a.row_stride), value_bytes, cache_base,
                                     cache_row},
                                    eb);
@@ -247,7 +264,14 @@ void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStre
     p.out_vec_ok = (reinterpret_cast<uint64_t>(a.output) % store_bytes == 0) &&
                    (static_cast<uint64_t>(a.output_stride) % store_bytes == 0);
   }
-  launch_lookup_rows(p, mode, vb, stream);
+  // NVE_B200_GATHER_BULK=1 moves raw rows with the bulk-copy engine instead of lane vectors
+  static const bool bulk = std::getenv("NVE_B200_GATHER_BULK") != nullptr &&
+                           std::getenv("NVE_B200_GATHER_BULK")[0] == '1';
+  if (bulk && gather_bulk_eligible(p, mode, vb, a.row_copy_bytes)) {
+    launch_gather_bulk(p, a.row_copy_bytes, stream);
+  } else {
+    launch_lookup_rows(p, mode, vb, stream);
+  }
   NVE_B200_CUDA(cudaGetLastError());
 }
 

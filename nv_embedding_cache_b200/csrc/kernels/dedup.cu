@@ -213,7 +213,7 @@ __device__ __forceinline__ int64_t ld_idx(const void* p, bool is64, int64_t i) {
 // PASS 1: one lane group per split group adds its partial rows in chunk order and finishes.
 template <int GROUP, int PASS>
 __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
-  constexpr int U = 4;
+  constexpr int U = 8;
   const int lane = threadIdx.x & 31;
   const int gl = lane & (GROUP - 1);
   const int64_t c = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP;
@@ -240,26 +240,37 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
     slot_base = 2 * (c - u);
   }
 
-  for (int v0 = gl; v0 < p.nvec; v0 += GROUP) {
+  const uint32_t gmask = GROUP == 32 ? 0xffffffffu : ((1u << GROUP) - 1u) << (lane & ~(GROUP - 1));
+  // every lane of the group runs every column pass (the passes contain group shuffles); lanes
+  // past the end of the row only skip the memory accesses
+  for (int vbase = 0; vbase < p.nvec; vbase += GROUP) {
+    const int v0 = vbase + gl;
+    const bool on = v0 < p.nvec;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if constexpr (PASS == 0) {
       const int64_t b = ld_idx(p.offsets, p.idx64, c);
       const int64_t e = ld_idx(p.offsets, p.idx64, c + 1);
-      for (int64_t i = b; i < e; i += U) {
-        float4 r[U];
+      // GROUP positions per round: every lane fetches one position (coalesced), the rows are then
+      // streamed U at a time in position order; slots past the end re-read the last row
+      for (int64_t i = b; i < e; i += GROUP) {
+        const int n = static_cast<int>(min(static_cast<int64_t>(GROUP), e - i));
+        const int64_t my_row = ld_idx(p.inverse, p.idx64, min(i + gl, e - 1));
+#pragma unroll 1
+        for (int s = 0; s < n; s += U) {
+          float4 r[U];
 #pragma unroll
-        for (int k = 0; k < U; k++) {
-          const int64_t at = min(i + k, e - 1);
-          const int64_t row = ld_idx(p.inverse, p.idx64, at);
-          r[k] = __ldg(reinterpret_cast<const float4*>(p.grads + row * p.grad_stride) + v0);
-        }
+          for (int k = 0; k < U; k++) {
+            const int64_t row = __shfl_sync(gmask, my_row, min(s + k, n - 1), GROUP);
+            if (on) r[k] = __ldg(reinterpret_cast<const float4*>(p.grads + row * p.grad_stride) + v0);
+          }
 #pragma unroll
-        for (int k = 0; k < U; k++) {
-          if (i + k < e) {
-            acc.x = __fadd_rn(acc.x, r[k].x);
-            acc.y = __fadd_rn(acc.y, r[k].y);
-            acc.z = __fadd_rn(acc.z, r[k].z);
-            acc.w = __fadd_rn(acc.w, r[k].w);
+          for (int k = 0; k < U; k++) {
+            if (on && s + k < n) {
+              acc.x = __fadd_rn(acc.x, r[k].x);
+              acc.y = __fadd_rn(acc.y, r[k].y);
+              acc.z = __fadd_rn(acc.z, r[k].z);
+              acc.w = __fadd_rn(acc.w, r[k].w);
+            }
           }
         }
       }
@@ -268,7 +279,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
         int64_t first = c;
         while (first > 0 && ld_idx(p.loc_map, p.idx64, first - 1) == u) first--;
         const int64_t slot = 2 * (first - u) + (c - first);
-        if (slot < p.partial_rows) {
+        if (on && slot < p.partial_rows) {
           reinterpret_cast<float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0] = acc;
         }
         continue;
@@ -276,7 +287,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
     } else {
       for (int64_t k = 0; k < chunks_in_group; k++) {
         const int64_t slot = slot_base + k;
-        if (slot < p.partial_rows) {
+        if (on && slot < p.partial_rows) {
           const float4 r = reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
           acc.x = __fadd_rn(acc.x, r.x);
           acc.y = __fadd_rn(acc.y, r.y);
@@ -285,6 +296,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
         }
       }
     }
+    if (!on) continue;
     if (p.fused) {
       const int64_t key = ld_idx(p.unique, p.idx64, u);
       if (static_cast<uint64_t>(key) < static_cast<uint64_t>(p.table_rows)) {

@@ -51,6 +51,14 @@ __device__ __forceinline__ RawVec<VB> load_row_vec(const uint8_t* p) {
   return r;
 }
 
+// Ordinary (coherent) vector load, for memory that is not this GPU's own (peer mappings).
+template <int VB>
+__device__ __forceinline__ RawVec<VB> load_row_vec_plain(const uint8_t* p) {
+  RawVec<VB> r;
+  r.v = *reinterpret_cast<const decltype(r.v)*>(p);
+  return r;
+}
+
 template <int VB>
 __device__ __forceinline__ uint32_t raw_word(const RawVec<VB>& r, int i) {
   if constexpr (VB == 16) return i == 0 ? r.v.x : i == 1 ? r.v.y : i == 2 ? r.v.z : r.v.w;
@@ -60,8 +68,11 @@ __device__ __forceinline__ uint32_t raw_word(const RawVec<VB>& r, int i) {
 
 // Decode one raw vector into EPV = VB / elem_bytes fp32 values.  Quantised values become
 // float(q) * scale + offset with one rounding per operation (no fused multiply-add), which is
-// what a scalar CPU evaluation of the same expression gives.
-template <In IN, int VB>
+// what a scalar CPU evaluation of the same expression gives.  ADD_OFFSET = false drops the
+// "+ offset" of symmetric int8 rows (offset is 0 there): only for values that are then added to an
+// accumulator, where x + 0 and x give the same sum (the sign of a zero product cannot survive an
+// addition to a +0 or non-zero accumulator).
+template <In IN, int VB, bool ADD_OFFSET = true>
 __device__ __forceinline__ void decode_vec(const RawVec<VB>& r, float scale, float offset,
                                            float* out) {
   constexpr int EB = InTraits<IN>::kElemBytes;
@@ -89,7 +100,7 @@ __device__ __forceinline__ void decode_vec(const RawVec<VB>& r, float scale, flo
       const uint32_t b = (w >> (8 * (i % 4))) & 0xffu;
       const float q = (IN == In::I8) ? static_cast<float>(static_cast<int8_t>(b))
                                      : static_cast<float>(b);
-      out[i] = __fadd_rn(__fmul_rn(q, scale), offset);
+      out[i] = ADD_OFFSET ? __fadd_rn(__fmul_rn(q, scale), offset) : __fmul_rn(q, scale);
     }
   }
 }

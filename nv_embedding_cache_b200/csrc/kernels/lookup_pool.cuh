@@ -16,6 +16,8 @@
 
 namespace nve_b200 {
 
+constexpr int kMaxShards = 32;
+
 struct PoolKernelParams {
   const uint8_t* table;
   int64_t num_rows;
@@ -39,6 +41,12 @@ struct PoolKernelParams {
   bool mean;
   bool out_f16;
   bool out_vec_ok;
+  // row-sharded table read over peer mappings: row r lives in shard_base[r % num_shards] at local
+  // row r / num_shards (num_shards == 0: plain table)
+  const uint8_t* shard_base[kMaxShards];
+  uint64_t shard_magic;
+  uint32_t shard_shift;
+  int32_t num_shards;
 };
 
 template <int GROUP>
@@ -60,6 +68,11 @@ __device__ __forceinline__ const uint8_t* resolve_row(const PoolKernelParams& p,
   }
   if (p.default_row >= 0 && static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
     key = p.default_row;
+  }
+  if (p.num_shards > 0) {
+    const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
+    const uint32_t owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
+    return p.shard_base[owner] + local * p.row_stride;
   }
   return p.table == nullptr ? nullptr : p.table + key * p.row_stride;
 }
@@ -131,7 +144,13 @@ __global__ void __launch_bounds__(128) lookup_pool_kernel(const PoolKernelParams
 #pragma unroll
             for (int j = 0; j < VPL; j++) {
               const int idx = col0 + j * GROUP + gl;
-              if (idx < p.nvec) raw[u][j] = load_row_vec<VB>(row + static_cast<int64_t>(idx) * VB);
+              if (idx < p.nvec) {
+                // rows of a peer GPU are read with ordinary global loads, local rows through the
+                // read-only path
+                raw[u][j] = p.num_shards > 0
+                                ? load_row_vec_plain<VB>(row + static_cast<int64_t>(idx) * VB)
+                                : load_row_vec<VB>(row + static_cast<int64_t>(idx) * VB);
+              }
             }
           }
         }
@@ -152,7 +171,7 @@ __global__ void __launch_bounds__(128) lookup_pool_kernel(const PoolKernelParams
                 const int idx = col0 + j * GROUP + gl;
                 if (idx < p.nvec) {
                   float v[EPV];
-                  decode_vec<IN, VB>(raw[u][j], scale, qoff, v);
+                  decode_vec<IN, VB, IN != In::I8>(raw[u][j], scale, qoff, v);
 #pragma unroll
                   for (int e = 0; e < EPV; e++) {
                     const float x = weighted ? __fmul_rn(v[e], w) : v[e];

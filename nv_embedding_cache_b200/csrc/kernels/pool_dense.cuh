@@ -37,7 +37,7 @@ __device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, f
     float v[EPV];
     RawVec<16> r;
     r.v = raw;
-    decode_vec<IN, 16>(r, scale, qoff, v);
+    decode_vec<IN, 16, IN != In::I8>(r, scale, qoff, v);
 #pragma unroll
     for (int e = 0; e < EPV; e++) {
       const float x = WEIGHTED ? __fmul_rn(v[e], w) : v[e];
@@ -46,7 +46,9 @@ __device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, f
   }
 }
 
-template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE>
+// SHARDED: the table is split over peer-mapped shards (row r in shard r % W at local row r / W);
+// the owner lane then keeps the full 64-bit row address and rows are read with ordinary loads.
+template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool SHARDED = false>
 __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams p) {
   constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
   constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
@@ -78,17 +80,25 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   for (int c = 0; c < len; c += GROUP) {
     const int n = min(GROUP, len - c);
     uint32_t my_key = 0;
+    uint64_t my_addr = 0;   // SHARDED only: address of the row's first byte
     float my_w = 1.f, my_scale = 1.f, my_qoff = 0.f;
     if (gl < n) {
       const int64_t k = start + c + gl;
       int64_t key = p.keys ? load_index(p.keys, p.key64, k) : k;
-      if (SANITIZE && static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
+      if (SANITIZE && p.default_row >= 0 &&
+          static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
         key = p.default_row;
       }
       my_key = static_cast<uint32_t>(key);
+      if constexpr (SHARDED) {
+        const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
+        const uint32_t owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
+        my_addr = reinterpret_cast<uint64_t>(p.shard_base[owner]) + local * stride;
+      }
       if (WEIGHTED) my_w = load_weight(p.weights, p.w16, k);
       if constexpr (QUANT) {
-        const uint8_t* meta = p.table + static_cast<uint64_t>(my_key) * stride + p.row_width;
+        const uint8_t* meta = SHARDED ? reinterpret_cast<const uint8_t*>(my_addr) + p.row_width
+                                      : p.table + static_cast<uint64_t>(my_key) * stride + p.row_width;
         my_scale = load_meta(meta, p.meta_bytes);
         if (p.has_qoffset) my_qoff = load_meta(meta + p.meta_bytes, p.meta_bytes);
       }
@@ -100,9 +110,14 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
       uint4 raw[U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
-        if (lane_on) {
-          raw[u] = __ldg(reinterpret_cast<const uint4*>(lane_base + static_cast<uint64_t>(k) * stride));
+        if constexpr (SHARDED) {
+          const uint64_t a = __shfl_sync(gmask, my_addr, min(s + u, n - 1), GROUP);
+          if (lane_on) raw[u] = *reinterpret_cast<const uint4*>(a + gl * 16);
+        } else {
+          const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
+          if (lane_on) {
+            raw[u] = __ldg(reinterpret_cast<const uint4*>(lane_base + static_cast<uint64_t>(k) * stride));
+          }
         }
       }
 #pragma unroll
@@ -138,8 +153,9 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
 // The lean kernel covers: no cache, 16-byte vectors, at most 32 vectors per row, rows addressable
 // with 32 bits, non-negative bag lengths below 2^31.
 inline bool pool_dense_eligible(const PoolKernelParams& p, int vb) {
-  return !p.cache.enabled && p.table != nullptr && vb == 16 && p.nvec >= 1 && p.nvec <= 32 &&
-         p.num_rows > 0 && p.num_rows <= 0xffffffffll && p.row_stride <= 0x7fffffffll;
+  if (p.cache.enabled || vb != 16 || p.nvec < 1 || p.nvec > 32 || p.row_stride > 0x7fffffffll) return false;
+  if (p.num_shards > 0) return true;                      // peer-mapped shards: 64-bit addresses
+  return p.table != nullptr && p.num_rows > 0 && p.num_rows <= 0xffffffffll;
 }
 
 template <In IN>

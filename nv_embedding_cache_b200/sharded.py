@@ -135,21 +135,88 @@ class CudaStages:
             self.deduper = None
 
 
+def allocate_symmetric_shard(rows: int, dim: int, dtype: torch.dtype) -> torch.Tensor:
+    """Shard storage that every rank of the job can map (torch symmetric memory); required for
+    ``mode="peer"``.  Fill it, then hand it to :class:`ShardedEmbeddingTable`."""
+    import torch.distributed._symmetric_memory as symm_mem
+    return symm_mem.empty((rows, dim), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+
+
 class ShardedEmbeddingTable:
-    """A table of ``world * local_rows`` rows sharded round-robin over the ranks of a process group."""
+    """A table of ``world * local_rows`` rows sharded round-robin over the ranks of a process group.
+
+    mode="alltoall": dedup + two all-to-all exchanges (every distinct row crosses NVLink once).
+    mode="peer":     every rank maps all shards (symmetric memory) and ONE fused kernel probes,
+                     reads the rows straight from their owners over NVLink and pools them; no
+                     collective, no host synchronisation on the lookup path.
+    """
 
     POOLING = {"sum": capi.POOL_SUM, "mean": capi.POOL_MEAN}
 
-    def __init__(self, local_shard: torch.Tensor, *, max_keys: int, group=None, stages=None):
+    def __init__(self, local_shard: torch.Tensor, *, max_keys: int, group=None, stages=None,
+                 mode: str = "alltoall"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.shard = local_shard
-        self.stages = stages if stages is not None else CudaStages(max_keys, self.world)
+        self.mode = mode
         self.last_exchange = {}
+        self.stages = None
+        if mode == "peer":
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm_mem
+                handle = symm_mem.rendezvous(local_shard, group if group is not None else dist.group.WORLD)
+                self._symm = handle
+                ptrs = [int(p) for p in handle.buffer_ptrs]
+                torch.cuda.synchronize()
+                dist.barrier(group)          # every shard is filled before anyone reads it
+            else:
+                ptrs = [local_shard.data_ptr()]
+            self._shard_ptrs = (C.c_void_p * len(ptrs))(*ptrs)
+        else:
+            self.stages = stages if stages is not None else CudaStages(max_keys, self.world)
+
+    def _lookup_peer(self, keys, pooling, fixed_hotness, csr_offsets, out):
+        n = keys.numel()
+        num_bags = (csr_offsets.numel() - 1) if csr_offsets is not None else n // fixed_hotness
+        if out is None:
+            out = torch.empty((num_bags, self.shard.shape[1]), dtype=self.shard.dtype, device=keys.device)
+        a = capi.PoolArgs()
+        a.table = None
+        a.num_rows = self.shard.shape[0] * self.world
+        a.row_stride = self.shard.stride(0) * self.shard.element_size()
+        a.value_dtype = capi.DTYPE_FLOAT16 if self.shard.dtype == torch.float16 else capi.DTYPE_FLOAT32
+        a.row_width = self.shard.shape[1]
+        a.default_row_index = -1
+        a.cache = None
+        a.key_type = capi.KEY_INT64
+        a.keys = keys.data_ptr()
+        a.num_keys = n
+        a.pooling_type = self.POOLING[pooling]
+        a.sparse_type = capi.SPARSE_CSR if csr_offsets is not None else capi.SPARSE_FIXED
+        a.csr_offsets = csr_offsets.data_ptr() if csr_offsets is not None else None
+        a.offset_bytes = 8
+        a.num_bags = num_bags
+        a.fixed_hotness = fixed_hotness
+        a.weights = None
+        a.output = out.data_ptr()
+        a.output_stride = out.stride(0) * out.element_size()
+        a.output_dtype = capi.DTYPE_FLOAT16 if out.dtype == torch.float16 else capi.DTYPE_FLOAT32
+        if self.world > 1:
+            a.shard_tables = self._shard_ptrs
+            a.num_shards = self.world
+        else:                       # one rank: the shard is the table
+            a.table = self.shard.data_ptr()
+        capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), torch.cuda.current_stream().cuda_stream))
+        row_bytes = self.shard.shape[1] * self.shard.element_size()
+        self.last_exchange = {"unique": None, "served": None,
+                              "nvlink_bytes_in": n * row_bytes * (self.world - 1) // self.world}
+        return out
 
     def lookup_pooled(self, keys: torch.Tensor, pooling: str = "sum", *, fixed_hotness: int = 0,
                       csr_offsets: torch.Tensor | None = None, out: torch.Tensor | None = None):
+        if self.mode == "peer":
+            return self._lookup_peer(keys, pooling, fixed_hotness, csr_offsets, out)
         n = keys.numel()
         w = self.world
         u, send_keys, send_counts = self.stages.dedup_and_route(keys)
@@ -180,5 +247,5 @@ class ShardedEmbeddingTable:
         return out
 
     def close(self):
-        if hasattr(self.stages, "close"):
+        if self.stages is not None and hasattr(self.stages, "close"):
             self.stages.close()

@@ -84,8 +84,14 @@ dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 rows_per_rank, dim = 40000, 64
 total = rows_per_rank * world
 table = dg.dyadic_table(total, dim, 3, np.float16)
-shard = torch.from_numpy(table[rank::world].copy()).cuda()
-t = ShardedEmbeddingTable(shard, max_keys=1 << 16)
+mode = os.environ.get("NVE_TEST_SHARD_MODE", "alltoall")
+if mode == "peer":
+    from nv_embedding_cache_b200.sharded import allocate_symmetric_shard
+    shard = allocate_symmetric_shard(rows_per_rank, dim, torch.float16)
+    shard.copy_(torch.from_numpy(table[rank::world].copy()))
+else:
+    shard = torch.from_numpy(table[rank::world].copy()).cuda()
+t = ShardedEmbeddingTable(shard, max_keys=1 << 16, mode=mode)
 ok = True
 for step in range(3):
     keys = dg.zipf_keys(2048 * 8, total, 1.05, 100 + 10 * step + rank, dg.permutation(total))
@@ -102,7 +108,8 @@ sys.exit(0 if int(flag.item()) == 1 else 3)
 '''
 
 
-def test_two_ranks_nccl(torch_cuda, tmp_path):
+@pytest.mark.parametrize("mode", ["alltoall", "peer"])
+def test_two_ranks_nccl(torch_cuda, tmp_path, mode):
     torch = torch_cuda
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -111,7 +118,7 @@ def test_two_ranks_nccl(torch_cuda, tmp_path):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    env = dict(os.environ, NVE_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NVE_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0", NVE_TEST_SHARD_MODE=mode)
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                           "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port",
                           str(port), str(script)], env=env, capture_output=True, text=True, timeout=600)
