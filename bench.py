@@ -387,7 +387,10 @@ def run_other_workload(args):
     fn = {"c3": workloads.run_c3, "c4a": workloads.run_c4a, "c4b": workloads.run_c4b,
           "c5": workloads.run_c5}[args.workload]
     steps = min(args.steps, 50)
-    res = fn(str(ROOT), steps=steps, warmup=args.warmup)
+    kw = {}
+    if args.rows > 0:   # smaller table for profiling runs (the configuration's size is the default)
+        kw["rows_per_rank" if args.workload == "c5" else "rows"] = args.rows
+    res = fn(str(ROOT), steps=steps, warmup=args.warmup, **kw)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(res), flush=True)
     if world > 1:
@@ -405,6 +408,8 @@ def main():
     ap.add_argument("--workload", choices=["c2", "c3", "c4a", "c4b", "c5"], default="c2",
                     help="c2 is the headline benchmark; the others print one JSON line for that "
                          "configuration (see nv_embedding_cache_b200/workloads.py)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="table rows for --workload runs (0 = the configuration's own size)")
     ap.add_argument("--tables", type=int, default=NUM_TABLES,
                     help="tables per GPU (profiling runs use fewer; the benchmark config is 8)")
     args = ap.parse_args()
