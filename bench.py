@@ -142,6 +142,16 @@ def cpu_reference_run(table_host: np.ndarray, batches, seconds_budget: float, mi
     return total_keys / sum(times), workers, len(times), float(np.median(times))
 
 
+def load_reference_gpu():
+    """The unmodified reference GPU code built into oracle/_ref (a baseline timed beside this
+    library's kernels, never on their path); None when the library was not built."""
+    try:
+        from oracle.pyoracle import ReferenceGpu
+        return ReferenceGpu()
+    except (FileNotFoundError, OSError):
+        return None
+
+
 def run_reference_arm(args):
     """--impl reference: the reference's own CPU path on this box's host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -364,6 +374,24 @@ def run_ours(args):
             out["cpu_baseline"] = {"value": None, "unit": "keys/s", "cores": 0, "kind": "reference",
                                    "sample": f"unavailable: {e}"}
 
+    # ---- the reference's own GPU kernel for this lookup on the same GPU (rank 0, N=1 only):
+    # find_and_combine reading the table directly, timed on table 0's four batches
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ref_gpu = load_reference_gpu()
+        if ref_gpu is None:
+            out["reference_gpu_kernel"] = {"unavailable": "oracle/_ref/libnve_ref_gpu.so is not built"}
+        else:
+            torch.cuda.synchronize()
+            ks = [k.data_ptr() for k, _ in dev_batches[0]]
+            os_ = [o.data_ptr() for _, o in dev_batches[0]]
+            ms = ref_gpu.find_and_combine("f16_csr_mean", NUM_BAGS, tables[0].data_ptr(), ks, os_, 0, WIDTH,
+                                          dev_out[0].data_ptr(), warmup=10, iters=100)
+            nk = float(np.mean([k.numel() for k, _ in dev_batches[0]]))
+            out["reference_gpu_kernel"] = {
+                "kernel": "find_and_combine (fp16, CSR, mean, no cache in front), unmodified reference code",
+                "us_per_launch": ms * 1e3, "value": nk / (ms * 1e-3), "unit": "keys/s",
+                "sample": "table 0, 4 batches cycled, 100 launches"}
+
     for c in ctxs + ctxs_e2e:
         c.wait()
         c.destroy()
@@ -390,6 +418,8 @@ def run_other_workload(args):
     kw = {}
     if args.rows > 0:   # smaller table for profiling runs (the configuration's size is the default)
         kw["rows_per_rank" if args.workload == "c5" else "rows"] = args.rows
+    if args.workload in ("c3", "c4a", "c4b") and world == 1:
+        kw["ref_gpu"] = load_reference_gpu()
     res = fn(str(ROOT), steps=steps, warmup=args.warmup, **kw)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(res), flush=True)

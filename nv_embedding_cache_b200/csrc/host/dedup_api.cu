@@ -132,8 +132,8 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         d->max_run > 0 ? d_loc_map : nullptr, d_unique,
         nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
-        d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0,
-        static_cast<cudaStream_t>(stream));
+        d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
+        /*streamed=*/true, static_cast<cudaStream_t>(stream));
   });
 }
 

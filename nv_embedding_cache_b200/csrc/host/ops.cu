@@ -182,6 +182,19 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
                  (static_cast<uint64_t>(a.output_stride) % store_bytes == 0);
 
   static const bool dense_off = std::getenv("NVE_B200_NO_DENSE") != nullptr;
+  // One-byte rows that are only 4-byte aligned (quantised rows stored back to back) still take
+  // the dense kernel, reading each lane's 16 values as four 32-bit words.
+  if (vb == 4 && eb == 1 && value_bytes % 16 == 0 && a.num_shards == 0 && !p.cache.enabled) {
+    p.word_loads = true;
+    p.nvec = static_cast<int32_t>(value_bytes / 16);
+    const int sb = 4 * out_eb;
+    p.out_vec_ok = (reinterpret_cast<uint64_t>(a.output) % sb == 0) &&
+                   (static_cast<uint64_t>(a.output_stride) % sb == 0);
+    if (dense_off || !pool_dense_eligible(p, vb)) {
+      p.word_loads = false;
+      p.nvec = static_cast<int32_t>(value_bytes / vb);
+    }
+  }
   if (!dense_off && pool_dense_eligible(p, vb)) {
     switch (in) {
       case In::F32: launch_pool_dense<In::F32>(p, stream); break;

@@ -26,6 +26,7 @@
 
 #include <cub/cub.cuh>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "device_common.cuh"
@@ -208,10 +209,10 @@ __device__ __forceinline__ int64_t ld_idx(const void* p, bool is64, int64_t i) {
               : static_cast<int64_t>(reinterpret_cast<const int32_t*>(p)[i]);
 }
 
-// PASS 0: one lane group per chunk sums its gradient rows in position order.  Groups made of a
-// single chunk finish here; chunks of split groups go to `partial`.
-// PASS 1: one lane group per split group adds its partial rows in chunk order and finishes.
-template <int GROUP, int PASS>
+// First pass, register form: one lane group per chunk sums its gradient rows in position order.
+// Groups made of a single chunk finish here; chunks of split groups go to `partial`
+// (grad_finish_kernel completes them).
+template <int GROUP>
 __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
   constexpr int U = 8;
   const int lane = threadIdx.x & 31;
@@ -230,15 +231,6 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
   const bool single = first_of_group && last_of_group;
   (void)num_groups;
 
-  int64_t slot_base = 0;   // partial rows of a split group start at 2 * (first_chunk - u)
-  int64_t chunks_in_group = 1;
-  if constexpr (PASS == 1) {
-    if (single || !first_of_group) return;
-    int64_t e = c;
-    while (e + 1 < num_chunks && ld_idx(p.loc_map, p.idx64, e + 1) == u) e++;
-    chunks_in_group = e - c + 1;
-    slot_base = 2 * (c - u);
-  }
 
   const uint32_t gmask = GROUP == 32 ? 0xffffffffu : ((1u << GROUP) - 1u) << (lane & ~(GROUP - 1));
   // every lane of the group runs every column pass (the passes contain group shuffles); lanes
@@ -247,7 +239,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
     const int v0 = vbase + gl;
     const bool on = v0 < p.nvec;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if constexpr (PASS == 0) {
+    {
       const int64_t b = ld_idx(p.offsets, p.idx64, c);
       const int64_t e = ld_idx(p.offsets, p.idx64, c + 1);
       // GROUP positions per round: every lane fetches one position (coalesced), the rows are then
@@ -284,17 +276,6 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
         }
         continue;
       }
-    } else {
-      for (int64_t k = 0; k < chunks_in_group; k++) {
-        const int64_t slot = slot_base + k;
-        if (on && slot < p.partial_rows) {
-          const float4 r = reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
-          acc.x = __fadd_rn(acc.x, r.x);
-          acc.y = __fadd_rn(acc.y, r.y);
-          acc.z = __fadd_rn(acc.z, r.z);
-          acc.w = __fadd_rn(acc.w, r.w);
-        }
-      }
     }
     if (!on) continue;
     if (p.fused) {
@@ -314,16 +295,307 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
   }
 }
 
-template <int PASS>
-void launch_grad(const GradParams& p, cudaStream_t s) {
+// ---- streamed first pass -------------------------------------------------------------------
+// The register form above gives one lane group per chunk, so a chunk of 1024 rows is one dependent
+// chain of register loads (8 rows in flight) and a batch dominated by a few hot keys waits on those
+// chains, while the many single-row chunks each pay a chain of dependent metadata loads.  Here a
+// warp owns a window of consecutive positions of the inverse buffer (all chunks that START in the
+// window, so every chunk still belongs to exactly one warp and is summed in position order) and
+// streams the rows through a ring of 32 rows in shared memory filled by asynchronous 16-byte
+// copies (cp.async): lane L always copies and later reads columns [4L, 4L + 4) of a row, so no
+// barrier is needed between the copy and the read, only the copy-group wait.  The ring is split
+// into kGsStages groups of kGsBatch rows; three groups are in flight while one is summed, whatever
+// the chunk boundaries.  Chunk metadata is fetched for 32 chunks at a time (one per lane).
+// Single-chunk groups finish with one vector reduction to the destination (no read of the table
+// row); chunks of split groups park their sum in `partial` as in the register form.
+constexpr int kGsWarps = 2;
+constexpr int kGsStages = 4;
+constexpr int kGsBatch = 8;        // kGsStages * kGsBatch == 32 ring slots
+constexpr int kGsWindow = 256;     // positions per warp (default)
+constexpr int kGsMaxRowBytes = 512;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Smallest c in [0, C] with offsets[c] >= target, by 32-way narrowing.  Needs offsets[C] >= target.
+template <typename IdxT>
+__device__ __forceinline__ int64_t first_chunk_from(const IdxT* __restrict__ offsets, int64_t C,
+                                                    int64_t target, int lane) {
+  int64_t lo = 0, hi = C;
+  while (hi - lo >= 32) {
+    const int64_t stride = (hi - lo + 31) / 32;
+    const int64_t idx = min(lo + (lane + 1) * stride, hi);
+    const bool ge = static_cast<int64_t>(offsets[idx]) >= target;
+    const uint32_t m = __ballot_sync(0xffffffffu, ge);   // lane 31 probes hi, so m != 0
+    const int j = __ffs(m) - 1;
+    const int64_t new_hi = min(lo + (j + 1) * stride, hi);
+    if (j > 0) lo = min(lo + j * stride, hi) + 1;
+    hi = new_hi;
+  }
+  const int64_t idx = lo + lane;
+  const bool ge = idx <= hi && static_cast<int64_t>(offsets[idx]) >= target;
+  const uint32_t m = __ballot_sync(0xffffffffu, ge);
+  return lo + (__ffs(m) - 1);
+}
+
+template <typename IdxT>
+__global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradParams p, const int window) {
+  extern __shared__ __align__(128) uint8_t gs_ring[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const IdxT* __restrict__ offsets = static_cast<const IdxT*>(p.offsets);
+  const IdxT* __restrict__ inverse = static_cast<const IdxT*>(p.inverse);
+  const IdxT* __restrict__ loc_map = static_cast<const IdxT*>(p.loc_map);
+  const IdxT* __restrict__ unique = static_cast<const IdxT*>(p.unique);
+  const int64_t C = static_cast<const IdxT*>(p.num_runs_dev)[1];
+  if (C <= 0) return;
+  const int64_t n = offsets[C];
+  const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kGsWarps + warp) * window;
+  if (t0 >= n) return;
+  const int64_t cb = first_chunk_from(offsets, C, t0, lane);
+  const int64_t ce = first_chunk_from(offsets, C, min(t0 + window, n), lane);
+  if (cb >= ce) return;
+
+  const int64_t p0 = offsets[cb];
+  const int total = static_cast<int>(static_cast<int64_t>(offsets[ce]) - p0);
+  const uint32_t rb = static_cast<uint32_t>(p.nvec) * 16u;
+  const bool col = lane < p.nvec;
+  uint8_t* my_ring = gs_ring + static_cast<size_t>(warp) * 32u * rb + 16u * lane;   // this lane's column
+  const uint8_t* my_grads = p.grads + 16u * lane;
+
+  // metadata of 32 chunks at a time: lane j holds chunk cw + j
+  int64_t cw = cb;
+  int m_end = 0, m_u = -1, m_flags = 0;
+  int64_t m_key = 0;
+  auto load_window = [&]() {
+    const int64_t cj = cw + lane;
+    m_end = 0; m_u = -1; m_flags = 3; m_key = 0;
+    if (cj < ce) {
+      m_end = static_cast<int>(static_cast<int64_t>(offsets[cj + 1]) - p0);
+      if (loc_map) {
+        m_u = static_cast<int>(loc_map[cj]);
+        const int prev = cj > 0 ? static_cast<int>(loc_map[cj - 1]) : -1;
+        const int next = cj + 1 < C ? static_cast<int>(loc_map[cj + 1]) : -1;
+        m_flags = (prev != m_u ? 1 : 0) | (next != m_u ? 2 : 0);
+      } else {
+        m_u = static_cast<int>(cj);
+      }
+      if (p.fused) m_key = static_cast<int64_t>(unique[m_u]);
+    }
+  };
+
+  // `row` holds the gradient row of position 32 * cycle + lane for the cycle being issued
+  IdxT row = lane < total ? inverse[p0 + lane] : IdxT(0);
+  const int batches = (total + kGsBatch - 1) / kGsBatch;
+  // copies of batch b (positions 8b .. 8b + 7) into ring slots 8 * (b % 4) ..; always one commit
+  auto issue_batch = [&](int b) {
+    if (b < batches) {
+      const int q = b % kGsStages;
+      const int cnt = min(kGsBatch, total - b * kGsBatch);
+#pragma unroll
+      for (int i = 0; i < kGsBatch; i++) {
+        const int64_t r = static_cast<int64_t>(__shfl_sync(0xffffffffu, row, q * kGsBatch + i));
+        if (col && i < cnt) {
+          cp_async16(my_ring + static_cast<size_t>(q * kGsBatch + i) * rb, my_grads + r * p.grad_stride);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int b = 0; b < kGsStages; b++) issue_batch(b);
+  row = 32 + lane < total ? inverse[p0 + 32 + lane] : IdxT(0);   // positions of cycle 1
+  load_window();
+
+  int64_t c = cb;
+  int cur_end = __shfl_sync(0xffffffffu, m_end, 0);
+  int64_t group_first = -1;   // first chunk of the split group being walked, when known
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  // chunk c is complete: hand its sum on and move to the next chunk (warp-uniform)
+  auto finish_chunk = [&]() {
+    const int j = static_cast<int>(c - cw);
+    const int u = __shfl_sync(0xffffffffu, m_u, j);
+    const int flags = __shfl_sync(0xffffffffu, m_flags, j);
+    if (flags == 3) {
+      if (p.fused) {
+        const int64_t key = __shfl_sync(0xffffffffu, m_key, j);
+        if (col && static_cast<uint64_t>(key) < static_cast<uint64_t>(p.table_rows)) {
+          atomicAdd(reinterpret_cast<float4*>(p.dst + key * p.dst_stride) + lane,
+                    make_float4(__fmul_rn(p.alpha, acc.x), __fmul_rn(p.alpha, acc.y),
+                                __fmul_rn(p.alpha, acc.z), __fmul_rn(p.alpha, acc.w)));
+        }
+      } else if (col) {
+        reinterpret_cast<float4*>(p.dst + static_cast<int64_t>(u) * p.dst_stride)[lane] = acc;
+      }
+    } else {
+      if (flags & 1) {
+        group_first = c;
+      } else if (group_first < 0) {
+        group_first = c;
+        while (group_first > 0 && static_cast<int>(loc_map[group_first - 1]) == u) group_first--;
+      }
+      const int64_t slot = 2 * (group_first - u) + (c - group_first);
+      if (col && slot < p.partial_rows) {
+        reinterpret_cast<float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[lane] = acc;
+      }
+      if (flags & 2) group_first = -1;
+    }
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    c++;
+    if (c < ce) {
+      if (c - cw == 32) {
+        cw = c;
+        load_window();
+      }
+      cur_end = __shfl_sync(0xffffffffu, m_end, static_cast<int>(c - cw));
+    }
+  };
+
+  for (int b = 0; b < batches; b++) {
+    const int q = b % kGsStages;
+    if (q == 0 && b > 0) {
+      // entering a new cycle: its copies were all issued during the previous one; fetch the rows
+      // of the cycle after it
+      const int at = 32 * (b / kGsStages + 1) + lane;
+      row = at < total ? inverse[p0 + at] : IdxT(0);
+    }
+    cp_async_wait<kGsStages - 1>();   // the oldest of the four groups in flight has landed
+    const int first = b * kGsBatch;
+    const int cnt = min(kGsBatch, total - first);
+    const uint8_t* stage = my_ring + static_cast<size_t>(q * kGsBatch) * rb;
+    int s = 0;
+    if (cnt == kGsBatch && cur_end - first >= kGsBatch) {
+      // the whole batch lies inside the current chunk: eight independent loads, then the adds
+      if (col) {
+        float4 v[kGsBatch];
+#pragma unroll
+        for (int i = 0; i < kGsBatch; i++) {
+          v[i] = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(i) * rb);
+        }
+#pragma unroll
+        for (int i = 0; i < kGsBatch; i++) {
+          acc.x = __fadd_rn(acc.x, v[i].x);
+          acc.y = __fadd_rn(acc.y, v[i].y);
+          acc.z = __fadd_rn(acc.z, v[i].z);
+          acc.w = __fadd_rn(acc.w, v[i].w);
+        }
+      }
+      s = kGsBatch;
+      if (first + s == cur_end) finish_chunk();
+    }
+    for (; s < cnt; s++) {
+      if (col) {
+        const float4 v = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(s) * rb);
+        acc.x = __fadd_rn(acc.x, v.x);
+        acc.y = __fadd_rn(acc.y, v.y);
+        acc.z = __fadd_rn(acc.z, v.z);
+        acc.w = __fadd_rn(acc.w, v.w);
+      }
+      if (first + s + 1 == cur_end) finish_chunk();
+    }
+    issue_batch(b + kGsStages);   // refill the stage just read (this lane read only what it copied)
+  }
+  cp_async_wait<0>();
+}
+
+bool grad_stream_eligible(const GradParams& p, bool allow) {
+  static const bool off = std::getenv("NVE_B200_NO_GRAD_STREAM") != nullptr;
+  return !off && allow && p.nvec >= 1 && p.nvec <= 32 && p.nvec * 16 <= kGsMaxRowBytes;
+}
+
+template <typename IdxT>
+void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(kGsWarps) * 32u * static_cast<size_t>(p.nvec) * 16u;
+  static const int window = [] {
+    const char* e = std::getenv("NVE_B200_GRAD_WINDOW");   // tuning knob: positions per warp
+    const int v = e ? std::atoi(e) : 0;
+    return v >= 32 && v <= (1 << 20) ? v : kGsWindow;
+  }();
+  const int64_t warps = (n + window - 1) / window;
+  grad_stream_kernel<IdxT><<<blocks_for(warps, kGsWarps), kGsWarps * 32, smem, s>>>(p, window);
+}
+
+// Second pass: split groups.  A warp scans 32 chunks (one per lane) for first chunks of split
+// groups; for each one found the whole warp adds the group's partial rows in chunk order and
+// finishes the group (store, or read-modify-write of the table row in the fused form).
+__global__ void __launch_bounds__(128) grad_finish_kernel(const GradParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t num_chunks = ld_idx(p.num_runs_dev, p.idx64, 1);
+  const int64_t c = warp * 32 + lane;
+  if (warp * 32 >= num_chunks) return;
+  int64_t u = -1;
+  bool split_first = false;
+  if (c < num_chunks) {
+    u = ld_idx(p.loc_map, p.idx64, c);
+    const bool first = (c == 0) || ld_idx(p.loc_map, p.idx64, c - 1) != u;
+    const bool last = (c == num_chunks - 1) || ld_idx(p.loc_map, p.idx64, c + 1) != u;
+    split_first = first && !last;
+  }
+  uint32_t todo = __ballot_sync(0xffffffffu, split_first);
+  while (todo) {
+    const int j = __ffs(todo) - 1;
+    todo &= todo - 1;
+    const int64_t gu = __shfl_sync(0xffffffffu, u, j);
+    const int64_t first = warp * 32 + j;
+    int64_t chunks = 1;
+    while (first + chunks < num_chunks && ld_idx(p.loc_map, p.idx64, first + chunks) == gu) chunks++;
+    const int64_t slot_base = 2 * (first - gu);
+    for (int v0 = lane; v0 < p.nvec; v0 += 32) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int64_t k = 0; k < chunks; k++) {
+        const int64_t slot = slot_base + k;
+        if (slot < p.partial_rows) {
+          const float4 r =
+              reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
+          acc.x = __fadd_rn(acc.x, r.x);
+          acc.y = __fadd_rn(acc.y, r.y);
+          acc.z = __fadd_rn(acc.z, r.z);
+          acc.w = __fadd_rn(acc.w, r.w);
+        }
+      }
+      if (p.fused) {
+        const int64_t key = ld_idx(p.unique, p.idx64, gu);
+        if (static_cast<uint64_t>(key) < static_cast<uint64_t>(p.table_rows)) {
+          float4* d = reinterpret_cast<float4*>(p.dst + key * p.dst_stride) + v0;
+          float4 t = *d;
+          t.x = __fadd_rn(t.x, __fmul_rn(p.alpha, acc.x));
+          t.y = __fadd_rn(t.y, __fmul_rn(p.alpha, acc.y));
+          t.z = __fadd_rn(t.z, __fmul_rn(p.alpha, acc.z));
+          t.w = __fadd_rn(t.w, __fmul_rn(p.alpha, acc.w));
+          *d = t;
+        }
+      } else {
+        reinterpret_cast<float4*>(p.dst + gu * p.dst_stride)[v0] = acc;
+      }
+    }
+  }
+}
+
+void launch_grad_first(const GradParams& p, cudaStream_t s) {
   if (p.max_chunks <= 0) return;
   if (p.nvec <= 8) {
-    grad_reduce_kernel<8, PASS><<<blocks_for(p.max_chunks * 8, 128), 128, 0, s>>>(p);
+    grad_reduce_kernel<8><<<blocks_for(p.max_chunks * 8, 128), 128, 0, s>>>(p);
   } else if (p.nvec <= 16) {
-    grad_reduce_kernel<16, PASS><<<blocks_for(p.max_chunks * 16, 128), 128, 0, s>>>(p);
+    grad_reduce_kernel<16><<<blocks_for(p.max_chunks * 16, 128), 128, 0, s>>>(p);
   } else {
-    grad_reduce_kernel<32, PASS><<<blocks_for(p.max_chunks * 32, 128), 128, 0, s>>>(p);
+    grad_reduce_kernel<32><<<blocks_for(p.max_chunks * 32, 128), 128, 0, s>>>(p);
   }
+}
+
+void launch_grad_finish(const GradParams& p, cudaStream_t s) {
+  if (p.max_chunks <= 0) return;
+  grad_finish_kernel<<<blocks_for(p.max_chunks, 128), 128, 0, s>>>(p);
 }
 
 }  // namespace
@@ -359,7 +631,7 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     cudaStream_t stream) {
+                     int64_t num_keys, bool streamed, cudaStream_t stream) {
   NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
   NVE_B200_ARG(grad_stride % 16 == 0 && dst_stride % 16 == 0 &&
                    reinterpret_cast<uint64_t>(grads) % 16 == 0 &&
@@ -383,8 +655,13 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   p.nvec = static_cast<int32_t>(row_bytes / 16);
   p.idx64 = key_type == NVE_KEY_INT64;
   p.fused = fused;
-  launch_grad<0>(p, stream);
-  if (loc_map != nullptr) launch_grad<1>(p, stream);
+  if (grad_stream_eligible(p, streamed)) {
+    if (p.idx64) launch_grad_stream<int64_t>(p, num_keys, stream);
+    else launch_grad_stream<int32_t>(p, num_keys, stream);
+  } else {
+    launch_grad_first(p, stream);
+  }
+  if (loc_map != nullptr) launch_grad_finish(p, stream);
   NVE_B200_CUDA(cudaGetLastError());
 }
 
@@ -455,6 +732,6 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
     dedup_grads_run(key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
                     max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
                     dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
-                    static_cast<cudaStream_t>(stream));
+                    num_keys, /*streamed=*/false, static_cast<cudaStream_t>(stream));
   });
 }

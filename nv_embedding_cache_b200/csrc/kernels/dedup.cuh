@@ -19,11 +19,13 @@ const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int6
 // dst[u] = sum of grads rows of group u (fused == false), or
 // table[unique[u]] += alpha * sum (fused == true; dst is the table, keys outside
 // [0, table_rows) are skipped).  fp32 rows, 16-byte aligned.
+// streamed: let rows of up to 512 bytes take the first pass that streams them through shared
+// memory with asynchronous copies; false keeps the register form for every width.
 void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
                      int64_t row_bytes, const void* inverse, const void* offsets,
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     cudaStream_t stream);
+                     int64_t num_keys, bool streamed, cudaStream_t stream);
 
 }  // namespace nve_b200

@@ -94,12 +94,17 @@ __device__ __forceinline__ void decode_vec(const RawVec<VB>& r, float scale, flo
       out[0] = __half2float(__ushort_as_half(r.v));
     }
   } else {
+    // Integer -> float without the conversion unit (a quarter-rate pipe): place the byte in the
+    // low mantissa bits of 2^23, which is the float 2^23 + b exactly, and subtract 2^23 (exact).
+    // Signed bytes are biased by 128 first (b ^ 0x80 = b + 128 as unsigned) and the bias is taken
+    // off in the same subtraction.  One byte-permute and one full-rate add per value.
+    constexpr float kMagic = (IN == In::I8) ? 8388736.0f : 8388608.0f;   // 2^23 (+128)
 #pragma unroll
     for (int i = 0; i < EPV; i++) {
-      const uint32_t w = raw_word<VB>(r, i / 4);
-      const uint32_t b = (w >> (8 * (i % 4))) & 0xffu;
-      const float q = (IN == In::I8) ? static_cast<float>(static_cast<int8_t>(b))
-                                     : static_cast<float>(b);
+      uint32_t w = raw_word<VB>(r, i / 4);
+      if constexpr (IN == In::I8) w ^= 0x80808080u;
+      const uint32_t m = __byte_perm(w, 0x4B000000u, 0x7540u + (i % 4));
+      const float q = __fsub_rn(__uint_as_float(m), kMagic);
       out[i] = ADD_OFFSET ? __fadd_rn(__fmul_rn(q, scale), offset) : __fmul_rn(q, scale);
     }
   }

@@ -156,7 +156,6 @@ void launch_gather_bulk(const GatherKernelParams& p, int64_t row_copy_bytes, cud
   BulkGatherParams bp{};
   bp.g = p;
   bp.row_bytes = static_cast<uint32_t>(row_copy_bytes);
-  bp.error_flag = nullptr;
   const size_t smem = static_cast<size_t>(kBulkWarps) * 2 * kBulkRows * row_copy_bytes;
   static std::atomic<bool> attr_set{false};
   if (smem > 48 * 1024 && !attr_set.exchange(true)) {

@@ -41,6 +41,7 @@ struct PoolKernelParams {
   bool mean;
   bool out_f16;
   bool out_vec_ok;
+  bool word_loads;        // dense kernel only: 4-byte aligned one-byte rows read as 32-bit words
   // row-sharded table read over peer mappings: row r lives in shard_base[r % num_shards] at local
   // row r / num_shards (num_shards == 0: plain table)
   const uint8_t* shard_base[kMaxShards];

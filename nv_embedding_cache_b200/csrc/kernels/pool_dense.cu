@@ -26,6 +26,13 @@ void launch_flags(const PoolKernelParams& p, cudaStream_t stream) {
     else pool_dense_kernel<IN, GROUP, U, false, true, true><<<grid, block, 0, stream>>>(p);
     return;
   }
+  if constexpr (IN == In::I8 || IN == In::U8) {
+    if (p.word_loads) {
+      if (weighted) pool_dense_kernel<IN, GROUP, U, true, true, false, true><<<grid, block, 0, stream>>>(p);
+      else pool_dense_kernel<IN, GROUP, U, false, true, false, true><<<grid, block, 0, stream>>>(p);
+      return;
+    }
+  }
   if (weighted) {
     if (sanitize) pool_dense_kernel<IN, GROUP, U, true, true><<<grid, block, 0, stream>>>(p);
     else pool_dense_kernel<IN, GROUP, U, true, false><<<grid, block, 0, stream>>>(p);

@@ -48,8 +48,14 @@ __device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, f
 
 // SHARDED: the table is split over peer-mapped shards (row r in shard r % W at local row r / W);
 // the owner lane then keeps the full 64-bit row address and rows are read with ordinary loads.
-template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool SHARDED = false>
+// WORDS: rows that are only 4-byte aligned (quantised rows stored back to back: 256 values + a
+// 4-byte scale = 260 bytes).  A lane still owns 16 values, but fetches them as four 32-bit words,
+// word j of lane l being word j * nvec + l of the row, so that each of the four loads of a lane
+// group covers one contiguous run of the row.  Lane l then holds the columns
+// 4 * (j * nvec + l) .. + 3 for j = 0..3 and stores them as four short vectors.
+template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool SHARDED = false, bool WORDS = false>
 __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams p) {
+  static_assert(!(WORDS && SHARDED), "word loads are not combined with peer shards");
   constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
   constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
   const int lane = threadIdx.x & 31;
@@ -68,7 +74,7 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   }
   const int len = static_cast<int>(end - start);
   const bool lane_on = gl < p.nvec;
-  const uint8_t* lane_base = p.table + gl * 16;
+  const uint8_t* lane_base = p.table + gl * (WORDS ? 4 : 16);
   const uint32_t stride = static_cast<uint32_t>(p.row_stride);
 
   float acc[EPV];
@@ -116,7 +122,15 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
         } else {
           const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
           if (lane_on) {
-            raw[u] = __ldg(reinterpret_cast<const uint4*>(lane_base + static_cast<uint64_t>(k) * stride));
+            if constexpr (WORDS) {
+              const uint32_t* w = reinterpret_cast<const uint32_t*>(lane_base + static_cast<uint64_t>(k) * stride);
+              raw[u].x = __ldg(w);
+              raw[u].y = __ldg(w + p.nvec);
+              raw[u].z = __ldg(w + 2 * p.nvec);
+              raw[u].w = __ldg(w + 3 * p.nvec);
+            } else {
+              raw[u] = __ldg(reinterpret_cast<const uint4*>(lane_base + static_cast<uint64_t>(k) * stride));
+            }
           }
         }
       }
@@ -145,16 +159,27 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
     float v[EPV];
 #pragma unroll
     for (int e = 0; e < EPV; e++) v[e] = __fmul_rn(acc[e], inv);
-    uint8_t* dst = p.out + bag * p.out_stride + static_cast<int64_t>(gl) * EPV * (p.out_f16 ? 2 : 4);
-    store_values<EPV>(dst, v, p.out_f16, p.out_vec_ok);
+    const int out_eb = p.out_f16 ? 2 : 4;
+    if constexpr (WORDS) {
+      static_assert(!WORDS || EPV == 16, "word loads are for one-byte elements");
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint8_t* dst = p.out + bag * p.out_stride + static_cast<int64_t>(4 * (j * p.nvec + gl)) * out_eb;
+        store_values<4>(dst, v + 4 * j, p.out_f16, p.out_vec_ok);
+      }
+    } else {
+      uint8_t* dst = p.out + bag * p.out_stride + static_cast<int64_t>(gl) * EPV * out_eb;
+      store_values<EPV>(dst, v, p.out_f16, p.out_vec_ok);
+    }
   }
 }
 
 // The lean kernel covers: no cache, 16-byte vectors, at most 32 vectors per row, rows addressable
 // with 32 bits, non-negative bag lengths below 2^31.
+// `p.nvec` counts 16-byte groups of values here, also for the word-load form (vb == 4).
 inline bool pool_dense_eligible(const PoolKernelParams& p, int vb) {
-  if (p.cache.enabled || vb != 16 || p.nvec < 1 || p.nvec > 32 || p.row_stride > 0x7fffffffll) return false;
-  if (p.num_shards > 0) return true;                      // peer-mapped shards: 64-bit addresses
+  if (p.cache.enabled || (vb != 16 && !p.word_loads) || p.nvec < 1 || p.nvec > 32 || p.row_stride > 0x7fffffffll) return false;
+  if (p.num_shards > 0) return !p.word_loads;             // peer-mapped shards: 64-bit addresses
   return p.table != nullptr && p.num_rows > 0 && p.num_rows <= 0xffffffffll;
 }
 

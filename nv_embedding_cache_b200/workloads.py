@@ -62,7 +62,7 @@ def h2d_probe_gbs(nbytes: int = 1 << 30, reps: int = 10) -> float:
     return nbytes / best / 1e9
 
 
-def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, cache_frac=0.10):
+def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, cache_frac=0.10, ref_gpu=None):
     """LinearUVM cached lookup, no pooling: table in pinned host memory, 10 % of rows cached."""
     row_bytes = dim * 2
     stream = torch.cuda.current_stream()
@@ -103,6 +103,22 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
             "host_link_frac_of_probe": misses * row_bytes / sec / 1e9 / link,
             "frac_of_hbm_peak": batch * (8 + 2 * row_bytes) / sec / 1e9 / peak, "peak_kind": kind}
     ctx.destroy(); layer.destroy(); gt.destroy()
+    if ref_gpu is not None:
+        # the reference cache, warmed with the same insert sequence, serving the same batches
+        rc = ref_gpu.cache(cache_bytes, row_bytes, max_modify=batch)
+        for b in range(20):
+            k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+            rc.insert_from_table(k.data_ptr(), batch, table.data_ptr(), row_bytes)
+        res["reference_gpu"] = {}
+        for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(batch, rows, 1.2, 320 + 2 * b)),
+                               ("uniform", lambda b: dg.uniform_keys(batch, rows, 321 + 2 * b))):
+            batches = [torch.from_numpy(gen_keys(b)).cuda() for b in range(nb)]
+            misses = rc.lookup_table(batches[0].data_ptr(), batch, out.data_ptr(), row_bytes, table.data_ptr())
+            ms = rc.lookup_table_timed([k.data_ptr() for k in batches], batch, out.data_ptr(), row_bytes,
+                                       table.data_ptr(), warmup, steps)
+            res["reference_gpu"][name] = {"us_per_lookup": ms * 1e3, "keys_per_s": batch / (ms * 1e-3),
+                                          "hit_rate_first_batch": 1.0 - misses / batch}
+        rc.close()
     return res
 
 
@@ -120,12 +136,14 @@ def _quant_table(rows, width, stride, seed):
     return t
 
 
-def run_c4a(root, steps=50, warmup=5, rows=50_000_000, width=256, bags=32_768, hot=20):
-    """find_and_dequant + sum pooling: int8 rows with fp32 row scale -> fp16 sums."""
+def run_c4a(root, steps=50, warmup=5, rows=50_000_000, width=256, bags=32_768, hot=20, ref_gpu=None):
+    """find_and_dequant + sum pooling: int8 rows with fp32 row scale -> fp16 sums.  Four key batches
+    are cycled.  `ref_gpu`: optional handle of the reference GPU code, timed beside on the tight
+    layout (it writes fp32 sums: the reference has no fp16 output for fp32-scaled rows)."""
     stream = torch.cuda.current_stream()
     peak, kind = _hbm_peak(root)
-    keys_np = dg.zipf_keys(bags * hot, rows, 1.05, 400)
-    keys = torch.from_numpy(keys_np).cuda()
+    batches = [torch.from_numpy(dg.zipf_keys(bags * hot, rows, 1.05, 400 + b)).cuda() for b in range(4)]
+    keys = batches[0]
     out = torch.empty((bags, width), dtype=torch.float16, device="cuda")
     res = {"workload": "C4a: 50M x 256 int8 + fp32 scale, 32768 bags x 20 keys Zipf(1.05), dequant + sum -> fp16", "runs": {}}
     for stride in (width + 4, 272):
@@ -138,18 +156,28 @@ def run_c4a(root, steps=50, warmup=5, rows=50_000_000, width=256, bags=32_768, h
         a.output, a.output_stride, a.output_dtype = out.data_ptr(), width * 2, capi.DTYPE_FLOAT16
 
         def launch(i):
+            a.keys = batches[i % 4].data_ptr()
             capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), stream.cuda_stream))
         sec = _time_loop(stream, launch, steps, warmup)
         alg = keys.numel() * (8 + width + 4) + bags * width * 2
         res["runs"][f"stride{stride}"] = {"keys_per_s": keys.numel() / sec, "us_per_launch": sec * 1e6,
                                           "algorithmic_gbs": alg / sec / 1e9,
                                           "frac_of_hbm_peak": alg / sec / 1e9 / peak, "peak_kind": kind}
+        if ref_gpu is not None and stride == width + 4:
+            out32 = torch.empty((bags, width), dtype=torch.float32, device="cuda")
+            torch.cuda.synchronize()
+            ms = ref_gpu.find_and_combine("qint8_fixed_sum", bags, t.data_ptr(), [b.data_ptr() for b in batches],
+                                          None, hot, width, out32.data_ptr(), warmup=warmup, iters=steps)
+            res["reference_gpu_kernel"] = {"kernel": "find_and_combine (int8 + fp32 scale, fixed hotness, sum, fp32 out)",
+                                           "layout": f"stride{stride}", "us_per_launch": ms * 1e3,
+                                           "keys_per_s": keys.numel() / (ms * 1e-3)}
+            del out32
         del t
         torch.cuda.empty_cache()
     return res
 
 
-def run_c4b(root, steps=30, warmup=5, rows=10_000_000, dim=128, n=1_048_576, lr=0.01):
+def run_c4b(root, steps=30, warmup=5, rows=10_000_000, dim=128, n=1_048_576, lr=0.01, ref_gpu=None):
     """dedup_grads + update_accumulate: 1M (key, grad) pairs into a 10M x 128 fp32 table."""
     stream = torch.cuda.current_stream()
     peak, kind = _hbm_peak(root)
@@ -183,11 +211,32 @@ def run_c4b(root, steps=30, warmup=5, rows=10_000_000, dim=128, n=1_048_576, lr=
     t_both = _time_loop(stream, lambda i: (dedup(i), apply(i)), steps, warmup)
     alg = n * (8 + dim * 4) + u * 2 * dim * 4
     capi.check(capi.lib.nve_b200_deduper_destroy(d))
-    return {"workload": "C4b: dedup_grads + update_accumulate, 1048576 pairs Zipf(1.05), 10M x 128 fp32, SGD lr 0.01",
-            "unique": u, "keys_per_s": n / t_both, "us_dedup": t_dedup * 1e6, "us_reduce_apply": t_apply * 1e6,
-            "us_total": t_both * 1e6, "algorithmic_gbs": alg / t_both / 1e9,
-            "reduce_apply_gbs": alg / t_apply / 1e9, "frac_of_hbm_peak": alg / t_both / 1e9 / peak,
-            "peak_kind": kind}
+    res = {"workload": "C4b: dedup_grads + update_accumulate, 1048576 pairs Zipf(1.05), 10M x 128 fp32, SGD lr 0.01",
+           "unique": u, "keys_per_s": n / t_both, "us_dedup": t_dedup * 1e6, "us_reduce_apply": t_apply * 1e6,
+           "us_total": t_both * 1e6, "algorithmic_gbs": alg / t_both / 1e9,
+           "reduce_apply_gbs": alg / t_apply / 1e9, "frac_of_hbm_peak": alg / t_both / 1e9 / peak,
+           "peak_kind": kind}
+    if ref_gpu is not None:
+        # the reference's Deduper (sorting the same 24 key bits) and its gradient reduction into a
+        # [unique, dim] buffer; its table update (a further kernel) is not included
+        import time
+        rd = ref_gpu.deduper(1024, n)
+        ptrs = (keys.data_ptr(), n, uniq.data_ptr(), counts.data_ptr(), loc.data_ptr(), inverse.data_ptr(),
+                offsets.data_ptr(), 24)
+        for _ in range(warmup):
+            ru, rc = rd.dedup(*ptrs)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            ru, rc = rd.dedup(*ptrs)
+        ref_dedup = (time.perf_counter() - t0) / steps
+        sums = torch.empty((ru, dim), dtype=torch.float32, device="cuda")
+        ms = rd.grads(grads.data_ptr(), sums.data_ptr(), uniq.data_ptr(), inverse.data_ptr(), loc.data_ptr(),
+                      offsets.data_ptr(), ru, rc, dim, warmup=warmup, iters=steps)
+        rd.close()
+        res["reference_gpu"] = {"us_dedup": ref_dedup * 1e6, "us_reduce_only": ms * 1e3,
+                                "note": "reference Deduper (host-timed, includes its stream sync) and "
+                                        "GradientDedup; the update of the table is not included"}
+    return res
 
 
 def run_c5(root, steps=30, warmup=5, rows_per_rank=250_000_000, dim=64, bags=131_072, hot=8,

@@ -1,11 +1,15 @@
 """Build recipe for the parity checker (test infrastructure, not the product).
 
-Two artefacts, both written under ``oracle/_ref/`` (git-ignored, shipped to the GPU box as built):
+Three artefacts, all written under ``oracle/_ref/`` (git-ignored, shipped to the GPU box as built):
 
 * ``libnve_oracle.so``  – the plain-C restatement in ``oracle/nve_oracle.c`` (always built).
 * ``libnve_ref.so``     – the UNMODIFIED reference CPU path (HostEmbeddingLayer, LinearHostTable,
   cpu_ops) compiled straight from the reference checkout, wrapped by ``oracle/ref_driver.cpp``.
   Built only where the reference checkout is present; elsewhere the prebuilt file is used.
+* ``libnve_ref_gpu.so`` – the UNMODIFIED reference GPU code (set-associative cache with device-side
+  modify, GPU histogram, Deduper, gradient de-duplication, find_and_combine) compiled by nvcc for
+  sm_100a from the reference checkout, wrapped by ``oracle/ref_gpu_driver.cu``.  Same rule: built
+  only where the checkout is present.
 
 No reference source is copied: the compiler reads the files where they lie.
 """
@@ -95,12 +99,50 @@ def build_reference(verbose: bool = False) -> Path | None:
     return out
 
 
+def _shim_and_json():
+    nl = _find_nlohmann()
+    if nl is None:
+        raise RuntimeError("nlohmann/json.hpp not found in site-packages")
+    shim = OUT / "shim" / "nlohmann"
+    shim.mkdir(parents=True, exist_ok=True)
+    (shim / "json_fwd.hpp").write_text("#pragma once\n#include <nlohmann/json.hpp>\n")
+    return nl, shim.parent
+
+
+def build_reference_gpu(verbose: bool = False) -> Path | None:
+    """Compile the reference GPU code (header templates + two support sources) with nvcc for
+    sm_100a, with the reference's own fast-math setting and NDEBUG as in its release build (its
+    size self-check asserts otherwise abort on a cache sized to a whole number of sets).  About
+    half a minute."""
+    OUT.mkdir(exist_ok=True)
+    out = OUT / "libnve_ref_gpu.so"
+    if not (REFERENCE / "cuda_ops" / "deduper.cuh").exists():
+        return out if out.exists() else None
+    driver = HERE / "ref_gpu_driver.cu"
+    if _newer(out, [driver]):
+        return out
+    nl, shim = _shim_and_json()
+    nvcc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "bin" / "nvcc"
+    cmd = [str(nvcc), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+           "--expt-relaxed-constexpr", "--use_fast_math", "-w", "-Xcompiler", "-fPIC", "-shared",
+           "-cudart", "static", "-DNDEBUG", "-DNVE_CACHE_LINE_SIZE=64", "-DNVE_DISABLE_MPI",
+           f"-I{REFERENCE}", f"-I{REFERENCE / 'include'}", f"-I{REFERENCE / 'include' / 'ecache'}",
+           f"-I{nl}", f"-I{shim}", str(driver),
+           str(REFERENCE / "src" / "default_allocator.cpp"), str(REFERENCE / "src" / "common.cpp"),
+           "-o", str(out)]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return out
+
+
 def build_all(verbose: bool = False):
-    return build_oracle(verbose), build_reference(verbose)
+    return build_oracle(verbose), build_reference(verbose), build_reference_gpu(verbose)
 
 
 if __name__ == "__main__":
-    o, r = build_all(verbose=True)
+    o, r, g = build_all(verbose=True)
     print("oracle:", o)
     print("reference:", r)
+    print("reference (GPU):", g)
     sys.exit(0)

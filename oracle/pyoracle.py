@@ -1,5 +1,6 @@
-"""ctypes front-ends of the parity checker: the plain-C restatement (``libnve_oracle.so``) and the
-unmodified reference CPU build (``libnve_ref.so``).  TEST INFRASTRUCTURE: only tests/, the smoke
+"""ctypes front-ends of the parity checker: the plain-C restatement (``libnve_oracle.so``), the
+unmodified reference CPU build (``libnve_ref.so``) and the unmodified reference GPU code
+(``libnve_ref_gpu.so``).  TEST INFRASTRUCTURE: only tests/, the smoke
 entry and the benchmark's CPU-baseline legs may import this module.
 """
 from __future__ import annotations
@@ -332,3 +333,161 @@ class RefLayer:
             _ptr(gathered_bytes), gathered_bytes.strides[0], _ptr(out), out.strides[0], 1, 0,
             _ptr(offsets32), POOL[pooling], _ptr(weights)))
         return out
+
+
+class ReferenceGpu:
+    """The unmodified reference GPU code (``libnve_ref_gpu.so``): cache with device-side modify,
+    Deduper, gradient de-duplication and the pooled find_and_combine kernel.  All pointers are raw
+    device addresses (ints); every call synchronises the device before it returns."""
+
+    def __init__(self):
+        path = _build.build_reference_gpu()
+        if path is None or not Path(path).exists():
+            raise FileNotFoundError("libnve_ref_gpu.so is not built and the reference checkout is absent")
+        self.lib = L = C.CDLL(str(path))
+        f32 = C.c_float
+        pp = C.POINTER(_vp)
+        L.refgpu_last_error.restype = C.c_char_p
+        sigs = {
+            "refgpu_cache_create": [pp, _i64, _i64, _i64, f32, _i64],
+            "refgpu_cache_destroy": [_vp],
+            "refgpu_cache_view": [_vp, C.POINTER(_i64), pp, pp],
+            "refgpu_cache_insert": [_vp, _vp, _i64, _vp, _i64],
+            "refgpu_cache_insert_from_table": [_vp, _vp, _i64, _vp, _i64],
+            "refgpu_cache_lookup_mask": [_vp, _vp, _i64, _vp, _i64, _vp, C.POINTER(_i64)],
+            "refgpu_cache_lookup_table": [_vp, _vp, _i64, _vp, _i64, _vp, C.POINTER(_i64)],
+            "refgpu_cache_lookup_table_timed": [_vp, pp, _i32, _i64, _vp, _i64, _vp, _i32, _i32,
+                                                C.POINTER(f32)],
+            "refgpu_cache_update": [_vp, _vp, _i64, _vp, _i64],
+            "refgpu_cache_update_accumulate": [_vp, _vp, _i64, _vp, _i64, _i32],
+            "refgpu_cache_invalidate": [_vp, _vp, _i64],
+            "refgpu_cache_clear": [_vp],
+            "refgpu_deduper_create": [pp, _i32, _i64],
+            "refgpu_deduper_destroy": [_vp],
+            "refgpu_deduper_dedup": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
+            "refgpu_dedup_grads": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
+            "refgpu_dedup_grads_timed": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                         C.POINTER(f32)],
+            "refgpu_find_and_combine": [_i32, _i64, _vp, pp, pp, _i32, _i32, _i32, _vp, _i32, _i32,
+                                        C.POINTER(f32)],
+        }
+        for name, args in sigs.items():
+            fn = getattr(L, name)
+            fn.restype = _i32
+            fn.argtypes = args
+
+    def check(self, rc):
+        if rc != 0:
+            raise RuntimeError("reference GPU code: " + self.lib.refgpu_last_error().decode())
+
+    # ---- cache
+    def cache(self, cache_bytes, row_bytes, sentinel=-1, decay=0.95, max_modify=1 << 20):
+        return RefGpuCache(self, cache_bytes, row_bytes, sentinel, decay, max_modify)
+
+    def deduper(self, max_run, max_keys):
+        return RefGpuDeduper(self, max_run, max_keys)
+
+    # ---- pooled lookup (kind: "f16_csr_mean", "f16_fixed_sum", "qint8_fixed_sum")
+    KINDS = {"f16_csr_mean": 0, "f16_fixed_sum": 1, "qint8_fixed_sum": 2}
+
+    def find_and_combine(self, kind, bags, table_ptr, key_ptrs, offset_ptrs, hot, width, out_ptr,
+                         warmup=0, iters=0):
+        nb = len(key_ptrs)
+        keys = (_vp * nb)(*key_ptrs)
+        offs = (_vp * nb)(*offset_ptrs) if offset_ptrs else None
+        ms = C.c_float(0)
+        self.check(self.lib.refgpu_find_and_combine(self.KINDS[kind], bags, table_ptr, keys, offs, nb,
+                                                    hot, width, out_ptr, warmup, iters, C.byref(ms)))
+        return ms.value
+
+
+class RefGpuCache:
+    def __init__(self, ref: ReferenceGpu, cache_bytes, row_bytes, sentinel, decay, max_modify):
+        self.ref = ref
+        self.h = _vp()
+        ref.check(ref.lib.refgpu_cache_create(C.byref(self.h), cache_bytes, row_bytes, sentinel, decay,
+                                              max_modify))
+        self.row_bytes = row_bytes
+
+    def close(self):
+        if self.h:
+            self.ref.check(self.ref.lib.refgpu_cache_destroy(self.h))
+            self.h = _vp()
+
+    def view(self):
+        """(num_sets, device address of the tags [num_sets][8], device address of the rows)."""
+        n, tags, rows = _i64(0), _vp(), _vp()
+        self.ref.check(self.ref.lib.refgpu_cache_view(self.h, C.byref(n), C.byref(tags), C.byref(rows)))
+        return n.value, tags.value, rows.value
+
+    def insert(self, keys_ptr, n, values_ptr, stride):
+        self.ref.check(self.ref.lib.refgpu_cache_insert(self.h, keys_ptr, n, values_ptr, stride))
+
+    def insert_from_table(self, keys_ptr, n, table_ptr, stride):
+        self.ref.check(self.ref.lib.refgpu_cache_insert_from_table(self.h, keys_ptr, n, table_ptr, stride))
+
+    def lookup_mask(self, keys_ptr, n, out_ptr, stride, mask_ptr) -> int:
+        m = _i64(0)
+        self.ref.check(self.ref.lib.refgpu_cache_lookup_mask(self.h, keys_ptr, n, out_ptr, stride, mask_ptr,
+                                                             C.byref(m)))
+        return m.value
+
+    def lookup_table(self, keys_ptr, n, out_ptr, stride, table_ptr) -> int:
+        m = _i64(0)
+        self.ref.check(self.ref.lib.refgpu_cache_lookup_table(self.h, keys_ptr, n, out_ptr, stride, table_ptr,
+                                                              C.byref(m)))
+        return m.value
+
+    def lookup_table_timed(self, key_ptrs, n, out_ptr, stride, table_ptr, warmup, iters) -> float:
+        nb = len(key_ptrs)
+        ms = C.c_float(0)
+        self.ref.check(self.ref.lib.refgpu_cache_lookup_table_timed(
+            self.h, (_vp * nb)(*key_ptrs), nb, n, out_ptr, stride, table_ptr, warmup, iters, C.byref(ms)))
+        return ms.value
+
+    def update(self, keys_ptr, n, values_ptr, stride):
+        self.ref.check(self.ref.lib.refgpu_cache_update(self.h, keys_ptr, n, values_ptr, stride))
+
+    def update_accumulate(self, keys_ptr, n, values_ptr, stride, fp16=False):
+        self.ref.check(self.ref.lib.refgpu_cache_update_accumulate(self.h, keys_ptr, n, values_ptr, stride,
+                                                                   1 if fp16 else 0))
+
+    def invalidate(self, keys_ptr, n):
+        self.ref.check(self.ref.lib.refgpu_cache_invalidate(self.h, keys_ptr, n))
+
+    def clear(self):
+        self.ref.check(self.ref.lib.refgpu_cache_clear(self.h))
+
+
+class RefGpuDeduper:
+    """Reference Deduper<int64_t, MAX_RUN> (max_run in {-1, 8, 1024}) on device buffers."""
+
+    def __init__(self, ref: ReferenceGpu, max_run: int, max_keys: int):
+        self.ref = ref
+        self.h = _vp()
+        ref.check(ref.lib.refgpu_deduper_create(C.byref(self.h), max_run, max_keys))
+
+    def close(self):
+        if self.h:
+            self.ref.check(self.ref.lib.refgpu_deduper_destroy(self.h))
+            self.h = _vp()
+
+    def dedup(self, keys_ptr, n, unique_ptr, counts_ptr, loc_map_ptr, inverse_ptr, offsets_ptr, end_bit=0):
+        runs = np.zeros(2, np.int64)
+        self.ref.check(self.ref.lib.refgpu_deduper_dedup(self.h, keys_ptr, n, unique_ptr, counts_ptr,
+                                                         loc_map_ptr, runs.ctypes.data, inverse_ptr,
+                                                         offsets_ptr, end_bit))
+        return int(runs[0]), int(runs[1])
+
+    def grads(self, grads_ptr, out_ptr, unique_ptr, inverse_ptr, loc_map_ptr, offsets_ptr, num_unique,
+              num_chunks, width, warmup=0, iters=0):
+        runs = np.array([num_unique, num_chunks], np.int64)
+        if iters <= 0:
+            self.ref.check(self.ref.lib.refgpu_dedup_grads(grads_ptr, out_ptr, unique_ptr, inverse_ptr,
+                                                           loc_map_ptr, offsets_ptr, runs.ctypes.data, width))
+            return 0.0
+        ms = C.c_float(0)
+        self.ref.check(self.ref.lib.refgpu_dedup_grads_timed(grads_ptr, out_ptr, unique_ptr, inverse_ptr,
+                                                             loc_map_ptr, offsets_ptr, runs.ctypes.data,
+                                                             width, warmup, iters, C.byref(ms)))
+        return ms.value

@@ -30,6 +30,16 @@ def reference():
 
 
 @pytest.fixture(scope="session")
+def reference_gpu():
+    """The unmodified reference GPU code, prebuilt where the reference checkout was present."""
+    from oracle.pyoracle import ReferenceGpu
+    try:
+        return ReferenceGpu()
+    except FileNotFoundError as e:
+        pytest.skip(str(e))
+
+
+@pytest.fixture(scope="session")
 def capi():
     from nv_embedding_cache_b200 import capi as _capi
     return _capi

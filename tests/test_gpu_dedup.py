@@ -115,6 +115,24 @@ def test_grad_sums(torch_cuda, oracle, max_run, width):
     d.close()
 
 
+@pytest.mark.parametrize("max_run", [-1, 5])
+def test_grad_sums_int32_keys(torch_cuda, oracle, max_run):
+    """int32 index arrays; chunk length 5 makes chunks straddle the 8-row copy batches and the
+    256-position windows of the streamed reduction."""
+    torch = torch_cuda
+    n, rows, width = 30011, 700, 64
+    keys = dg.zipf_keys(n, rows, 1.2, 15, dg.permutation(rows)).astype(np.int32)
+    keys[::3] = keys[1]
+    d = Deduper(np.int32, max_run, n)
+    g = d.dedup(torch, keys)
+    o = oracle.dedup(keys.astype(np.int64), max_run=max_run)
+    rnd = np.random.default_rng(17).normal(0, 1e-2, (n, width)).astype(np.float32)
+    dst = torch.full((g["num_unique"], width), 3.0, device="cuda")
+    d.grads(torch, rnd, n, dst)
+    assert np.array_equal(dst.cpu().numpy(), oracle.dedup_grads(rnd, o))
+    d.close()
+
+
 def test_fused_reduce_and_update_matches_cpu_update(torch_cuda, oracle):
     """dedup_grads + update_accumulate with SGD lr = 0.01: table[key] += -lr * sum(grad)."""
     torch = torch_cuda
