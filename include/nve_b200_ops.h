@@ -194,6 +194,26 @@ NVE_C_API nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t deduper, const vo
                                             void* stream);
 
 /*
+ * Backward of a pooled lookup in one call (replaces GradientCalculator::compute_gradients, pooling
+ * branch, cuda_ops/gradient_calculator.cuh:85-180,254-286, which the Python binding exposes as
+ * pooling_backprop): de-duplicates the keys of the batch and writes, for unique key u,
+ *   d_grads_out[u] = sum over the positions i of u, in ascending i, of w(i) * d_bag_grads[bag(i)]
+ * with w(i) = 1 (Sum), 1 / len(bag) (Mean), weight[i] (WeightedSum) or weight[i] / sum of the bag's
+ * weights (WeightedMean).  fp32 gradients and weights; d_csr_offsets has the deduper's key type
+ * (num_bags + 1 entries) or is NULL with fixed_hotness.  d_unique_out needs room for num_keys keys,
+ * d_grads_out for num_keys rows.  *h_num_unique is valid on return (one stream synchronisation).
+ * Index scratch is owned by the deduper and allocated on the first call.
+ */
+NVE_C_API nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t deduper, int64_t num_keys,
+                                                 const void* d_keys, const void* d_bag_grads,
+                                                 int64_t grad_stride, int64_t row_bytes,
+                                                 nve_pooling_type_t pooling, nve_sparse_type_t sparse,
+                                                 const void* d_csr_offsets, int64_t num_bags,
+                                                 int64_t fixed_hotness, const float* d_weights,
+                                                 void* d_unique_out, void* d_grads_out, int64_t out_stride,
+                                                 int64_t* h_num_unique, void* stream);
+
+/*
  * Same reduction as nve_b200_dedup_grads, for callers that must not allocate device memory at
  * this point: a training step whose memory pool is fully planned, a plugin that owns only the
  * buffers it was given, a thread that must stay out of the driver's allocator.  (No counterpart
@@ -258,6 +278,18 @@ NVE_C_API nve_status_t nve_b200_shard_expand_slots(nve_key_type_t key_type, cons
                                                    const void* d_slot_of_unique,
                                                    const void* d_num_unique, int64_t n,
                                                    void* d_slot_of_position, void* stream);
+
+/*
+ * Host-resident table memory that GPU kernels read in place (the backing table of the cached
+ * layer).  Replaces ManagedMemBlock (src/memblock.cpp:108-135), same recipe: managed memory,
+ * preferred location = host, accessed-by = each GPU of `gpu_ids`.  The pointer is valid on the host
+ * and on those GPUs.  Prefer this over cudaHostAlloc for tables of more than a few GB: random row
+ * reads from it kept 91 % of the host link's copy rate over a 25.6 GB table, against 30 % from
+ * cudaHostAlloc'ed memory.
+ */
+NVE_C_API nve_status_t nve_b200_managed_block_create(void** out, uint64_t bytes, const int32_t* gpu_ids,
+                                                     int32_t num_gpus);
+NVE_C_API nve_status_t nve_b200_managed_block_destroy(void* block);
 
 #ifdef __cplusplus
 }

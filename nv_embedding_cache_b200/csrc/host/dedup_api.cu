@@ -18,6 +18,10 @@ struct nve_b200_deduper_s {
   int64_t partial_row_bytes = 0;
   int64_t last_num_keys = -1;  // batch size and chunk count of the last dedup()
   int64_t last_chunks = 0;
+  // pooled backward only: index arrays of its internal dedup and the per-position sources
+  void* bp_arrays = nullptr;
+  int64_t bp_bags = 0;
+  float* bp_bag_sum = nullptr;
 };
 
 namespace nve_b200 {
@@ -68,6 +72,8 @@ nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t d) {
   (void)cudaFree(d->workspace);
   (void)cudaFreeHost(d->pinned);
   if (d->partial) (void)cudaFree(d->partial);
+  if (d->bp_arrays) (void)cudaFree(d->bp_arrays);
+  if (d->bp_bag_sum) (void)cudaFree(d->bp_bag_sum);
   (void)cudaGetLastError();
   delete d;
   return NVE_SUCCESS;
@@ -133,7 +139,85 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, static_cast<cudaStream_t>(stream));
+        /*streamed=*/true, /*pos_weight=*/nullptr, static_cast<cudaStream_t>(stream));
+  });
+}
+
+// Pooled backward in one call: unique keys of the batch and, per unique key, the sum over its
+// occurrences of weight * (gradient of the bag the occurrence belongs to).
+nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, const void* d_keys,
+                                       const void* d_bag_grads, int64_t grad_stride, int64_t row_bytes,
+                                       nve_pooling_type_t pooling, nve_sparse_type_t sparse,
+                                       const void* d_csr_offsets, int64_t num_bags, int64_t fixed_hotness,
+                                       const float* d_weights, void* d_unique_out, void* d_grads_out,
+                                       int64_t out_stride, int64_t* h_num_unique, void* stream) {
+  if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
+  return guarded([&] {
+    NVE_B200_ARG(h_num_unique != nullptr, "pooling_backprop: h_num_unique must not be NULL");
+    *h_num_unique = 0;
+    if (num_keys <= 0) return;
+    NVE_B200_ARG(num_keys <= d->capacity, "pooling_backprop: more keys than the deduper was created for");
+    NVE_B200_ARG(d_keys && d_bag_grads && d_unique_out && d_grads_out, "pooling_backprop: NULL buffer");
+    NVE_B200_ARG(pooling == NVE_POOL_SUM || pooling == NVE_POOL_MEAN || pooling == NVE_POOL_WEIGHTED_SUM ||
+                     pooling == NVE_POOL_WEIGHTED_MEAN,
+                 "pooling_backprop: pooling must be Sum, Mean, WeightedSum or WeightedMean "
+                 "(Concatenate is nve_b200_dedup_grads)");
+    const bool weighted = pooling == NVE_POOL_WEIGHTED_SUM || pooling == NVE_POOL_WEIGHTED_MEAN;
+    const bool mean = pooling == NVE_POOL_MEAN || pooling == NVE_POOL_WEIGHTED_MEAN;
+    NVE_B200_ARG(!weighted || d_weights != nullptr, "pooling_backprop: weighted pooling needs weights");
+    NVE_B200_ARG(num_bags > 0, "pooling_backprop: num_bags must be positive");
+    if (sparse == NVE_SPARSE_CSR) {
+      NVE_B200_ARG(d_csr_offsets != nullptr, "pooling_backprop: CSR layout needs offsets");
+    } else {
+      NVE_B200_ARG(sparse == NVE_SPARSE_FIXED && fixed_hotness > 0 && num_bags * fixed_hotness == num_keys,
+                   "pooling_backprop: fixed hotness must divide the keys into num_bags bags");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int kb = nve_b200::key_bytes(d->key_type);
+    const int64_t cap = d->capacity;
+    const int64_t chunk_cap = cap + (d->max_run > 0 ? cap / d->max_run : 0) + 2;
+    // internal arrays: counts, inverse, src_row (cap + 1 each), offsets, loc_map (chunk_cap + 1), pos_w
+    auto align = [](size_t v) { return (v + 255) & ~size_t(255); };
+    const size_t a_idx = align(size_t(cap + 1) * kb), a_chunk = align(size_t(chunk_cap + 1) * kb);
+    if (!d->bp_arrays) {
+      NVE_B200_CUDA(cudaMalloc(&d->bp_arrays, 3 * a_idx + 2 * a_chunk + align(size_t(cap + 1) * 4)));
+    }
+    char* base = static_cast<char*>(d->bp_arrays);
+    void* counts = base;
+    void* inverse = base + a_idx;
+    void* src_row = base + 2 * a_idx;
+    void* offsets = base + 3 * a_idx;
+    void* loc_map = base + 3 * a_idx + a_chunk;
+    float* pos_w = reinterpret_cast<float*>(base + 3 * a_idx + 2 * a_chunk);
+    if (mean && num_bags > d->bp_bags) {
+      if (d->bp_bag_sum) {
+        NVE_B200_CUDA(cudaDeviceSynchronize());
+        NVE_B200_CUDA(cudaFree(d->bp_bag_sum));
+        d->bp_bag_sum = nullptr;
+      }
+      NVE_B200_CUDA(cudaMalloc(&d->bp_bag_sum, size_t(num_bags) * 4));
+      d->bp_bags = num_bags;
+    }
+    nve_b200::dedup_run(d->key_type, d->workspace, d->capacity, d_keys, num_keys, d_unique_out, counts,
+                        loc_map, inverse, offsets, d->max_run, kb * 8, d->pinned, s);
+    const void* num_runs = nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity);
+    const bool need_w = weighted || mean;
+    nve_b200::pooled_sources_run(d->key_type, inverse, num_runs, offsets,
+                                 sparse == NVE_SPARSE_CSR ? d_csr_offsets : nullptr, num_bags,
+                                 fixed_hotness, weighted ? d_weights : nullptr, mean, d->bp_bag_sum, src_row,
+                                 need_w ? pos_w : nullptr, num_keys, s);
+    nve_b200::ensure_partial(d, num_keys, row_bytes);
+    const int64_t max_chunks = d->max_run > 0 ? num_keys + num_keys / d->max_run + 1 : num_keys;
+    nve_b200::dedup_grads_run(
+        d->key_type, d_bag_grads, grad_stride, row_bytes, src_row, offsets,
+        d->max_run > 0 ? loc_map : nullptr, d_unique_out, num_runs, max_chunks, d_grads_out, out_stride,
+        /*fused=*/false, 0, 1.0f, d->partial,
+        d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
+        /*streamed=*/true, need_w ? pos_w : nullptr, s);
+    NVE_B200_CUDA(cudaStreamSynchronize(s));   // the number of unique keys is part of the return value
+    *h_num_unique = kb == 8 ? static_cast<const int64_t*>(d->pinned)[0]
+                            : static_cast<const int32_t*>(d->pinned)[0];
+    d->last_num_keys = -1;   // the caller's own dedup() arrays no longer match the workspace
   });
 }
 

@@ -187,7 +187,8 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
 struct GradParams {
   const uint8_t* grads;      // [n] rows
   int64_t grad_stride;
-  const void* inverse;       // positions grouped by key
+  const void* inverse;       // positions grouped by key (pooled backward: the bag of each position)
+  const float* pos_weight;   // per position of `inverse`, or null: rows are scaled before they are added
   const void* offsets;       // chunk starts (C + 1)
   const void* loc_map;       // chunk -> group, or null (one chunk per group)
   const void* unique;        // group keys (fused form)
@@ -247,17 +248,26 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
       for (int64_t i = b; i < e; i += GROUP) {
         const int n = static_cast<int>(min(static_cast<int64_t>(GROUP), e - i));
         const int64_t my_row = ld_idx(p.inverse, p.idx64, min(i + gl, e - 1));
+        const float my_w = p.pos_weight ? p.pos_weight[min(i + gl, e - 1)] : 1.f;
 #pragma unroll 1
         for (int s = 0; s < n; s += U) {
           float4 r[U];
+          float w[U];
 #pragma unroll
           for (int k = 0; k < U; k++) {
             const int64_t row = __shfl_sync(gmask, my_row, min(s + k, n - 1), GROUP);
+            w[k] = __shfl_sync(gmask, my_w, min(s + k, n - 1), GROUP);
             if (on) r[k] = __ldg(reinterpret_cast<const float4*>(p.grads + row * p.grad_stride) + v0);
           }
 #pragma unroll
           for (int k = 0; k < U; k++) {
             if (on && s + k < n) {
+              if (p.pos_weight) {
+                r[k].x = __fmul_rn(w[k], r[k].x);
+                r[k].y = __fmul_rn(w[k], r[k].y);
+                r[k].z = __fmul_rn(w[k], r[k].z);
+                r[k].w = __fmul_rn(w[k], r[k].w);
+              }
               acc.x = __fadd_rn(acc.x, r[k].x);
               acc.y = __fadd_rn(acc.y, r[k].y);
               acc.z = __fadd_rn(acc.z, r[k].z);
@@ -301,17 +311,17 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
 // chains, while the many single-row chunks each pay a chain of dependent metadata loads.  Here a
 // warp owns a window of consecutive positions of the inverse buffer (all chunks that START in the
 // window, so every chunk still belongs to exactly one warp and is summed in position order) and
-// streams the rows through a ring of 32 rows in shared memory filled by asynchronous 16-byte
+// streams the rows through a ring of 16 or 32 rows in shared memory filled by asynchronous 16-byte
 // copies (cp.async): lane L always copies and later reads columns [4L, 4L + 4) of a row, so no
 // barrier is needed between the copy and the read, only the copy-group wait.  The ring is split
-// into kGsStages groups of kGsBatch rows; three groups are in flight while one is summed, whatever
+// into kGsStages groups of BATCH rows; three groups are in flight while one is summed, whatever
 // the chunk boundaries.  Chunk metadata is fetched for 32 chunks at a time (one per lane).
 // Single-chunk groups finish with one vector reduction to the destination (no read of the table
 // row); chunks of split groups park their sum in `partial` as in the register form.
 constexpr int kGsWarps = 2;
 constexpr int kGsStages = 4;
-constexpr int kGsBatch = 8;        // kGsStages * kGsBatch == 32 ring slots
-constexpr int kGsWindow = 256;     // positions per warp (default)
+// rows per stage: a template parameter (4 or 8); the ring holds kGsStages * BATCH rows
+constexpr int kGsWindow = 128;     // positions per warp (default)
 constexpr int kGsMaxRowBytes = 512;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -347,8 +357,11 @@ __device__ __forceinline__ int64_t first_chunk_from(const IdxT* __restrict__ off
   return lo + (__ffs(m) - 1);
 }
 
-template <typename IdxT>
+template <typename IdxT, int BATCH, bool WEIGHTED>
 __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradParams p, const int window) {
+  constexpr int kGsBatch = BATCH;
+  constexpr int kRing = kGsStages * BATCH;   // ring slots
+  static_assert(32 % BATCH == 0 && kRing <= 32, "a batch may not straddle a cycle of 32 positions");
   extern __shared__ __align__(128) uint8_t gs_ring[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -369,7 +382,9 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   const int total = static_cast<int>(static_cast<int64_t>(offsets[ce]) - p0);
   const uint32_t rb = static_cast<uint32_t>(p.nvec) * 16u;
   const bool col = lane < p.nvec;
-  uint8_t* my_ring = gs_ring + static_cast<size_t>(warp) * 32u * rb + 16u * lane;   // this lane's column
+  uint8_t* my_ring = gs_ring + static_cast<size_t>(warp) * kRing * rb + 16u * lane;   // this lane's column
+  // WEIGHTED: one weight per ring slot, behind the rings of the block's warps
+  float* wcell = reinterpret_cast<float*>(gs_ring + static_cast<size_t>(kGsWarps) * kRing * rb) + warp * kRing;
   const uint8_t* my_grads = p.grads + 16u * lane;
 
   // metadata of 32 chunks at a time: lane j holds chunk cw + j
@@ -393,19 +408,45 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
     }
   };
 
-  // `row` holds the gradient row of position 32 * cycle + lane for the cycle being issued
-  IdxT row = lane < total ? inverse[p0 + lane] : IdxT(0);
+  // Positions are issued in cycles of 32: lane l of `row_cur` holds the gradient row of position
+  // 32 * issue_cycle + l, `row_nxt` the same for the following cycle (fetched a whole cycle early,
+  // so the load is never waited for).
+  auto load_rows = [&](int cycle) {
+    const int at = 32 * cycle + lane;
+    return at < total ? inverse[p0 + at] : IdxT(0);
+  };
+  auto load_weights = [&](int cycle) {
+    const int at = 32 * cycle + lane;
+    return (WEIGHTED && at < total) ? p.pos_weight[p0 + at] : 1.f;
+  };
+  IdxT row_cur = load_rows(0);
+  IdxT row_nxt = load_rows(1);
+  float w_cur = load_weights(0);
+  float w_nxt = load_weights(1);
+  int issue_cycle = 0;
   const int batches = (total + kGsBatch - 1) / kGsBatch;
-  // copies of batch b (positions 8b .. 8b + 7) into ring slots 8 * (b % 4) ..; always one commit
+  // copies of batch b (positions BATCH * b ..) into ring slots BATCH * (b % stages) ..; always one commit
   auto issue_batch = [&](int b) {
     if (b < batches) {
-      const int q = b % kGsStages;
+      const int within = (b * kGsBatch) & 31;        // first position of the batch inside its cycle
+      if (within == 0 && b > 0) {
+        row_cur = row_nxt;
+        w_cur = w_nxt;
+        issue_cycle++;
+        row_nxt = load_rows(issue_cycle + 1);
+        w_nxt = load_weights(issue_cycle + 1);
+      }
+      const int slot0 = (b % kGsStages) * kGsBatch;
       const int cnt = min(kGsBatch, total - b * kGsBatch);
+      if constexpr (WEIGHTED) {
+        // the lanes holding this batch's positions park their weights beside the ring slots
+        if (lane >= within && lane < within + kGsBatch) wcell[slot0 + lane - within] = w_cur;
+      }
 #pragma unroll
       for (int i = 0; i < kGsBatch; i++) {
-        const int64_t r = static_cast<int64_t>(__shfl_sync(0xffffffffu, row, q * kGsBatch + i));
+        const int64_t g = static_cast<int64_t>(__shfl_sync(0xffffffffu, row_cur, within + i));
         if (col && i < cnt) {
-          cp_async16(my_ring + static_cast<size_t>(q * kGsBatch + i) * rb, my_grads + r * p.grad_stride);
+          cp_async16(my_ring + static_cast<size_t>(slot0 + i) * rb, my_grads + g * p.grad_stride);
         }
       }
     }
@@ -413,7 +454,6 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   };
 #pragma unroll
   for (int b = 0; b < kGsStages; b++) issue_batch(b);
-  row = 32 + lane < total ? inverse[p0 + 32 + lane] : IdxT(0);   // positions of cycle 1
   load_window();
 
   int64_t c = cb;
@@ -461,48 +501,60 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
     }
   };
 
+  constexpr int SUB = BATCH < 8 ? BATCH : 8;      // rows summed per unrolled step
   for (int b = 0; b < batches; b++) {
     const int q = b % kGsStages;
-    if (q == 0 && b > 0) {
-      // entering a new cycle: its copies were all issued during the previous one; fetch the rows
-      // of the cycle after it
-      const int at = 32 * (b / kGsStages + 1) + lane;
-      row = at < total ? inverse[p0 + at] : IdxT(0);
-    }
-    cp_async_wait<kGsStages - 1>();   // the oldest of the four groups in flight has landed
-    const int first = b * kGsBatch;
-    const int cnt = min(kGsBatch, total - first);
-    const uint8_t* stage = my_ring + static_cast<size_t>(q * kGsBatch) * rb;
-    int s = 0;
-    if (cnt == kGsBatch && cur_end - first >= kGsBatch) {
-      // the whole batch lies inside the current chunk: eight independent loads, then the adds
-      if (col) {
-        float4 v[kGsBatch];
+    cp_async_wait<kGsStages - 1>();   // the oldest of the groups in flight has landed
+    if constexpr (WEIGHTED) __syncwarp();   // weights parked by other lanes are visible
+    const int cnt_all = min(kGsBatch, total - b * kGsBatch);
+#pragma unroll 1
+    for (int h = 0; h < kGsBatch; h += SUB) {
+      const int first = b * kGsBatch + h;
+      const int cnt = min(SUB, cnt_all - h);
+      if (cnt <= 0) break;
+      const uint8_t* stage = my_ring + static_cast<size_t>(q * kGsBatch + h) * rb;
+      const float* wstage = wcell + q * kGsBatch + h;
+      int s = 0;
+      if (cnt == SUB && cur_end - first >= SUB) {
+        // these rows lie inside the current chunk: independent loads first, then the adds
+        if (col) {
+          float4 v[SUB];
 #pragma unroll
-        for (int i = 0; i < kGsBatch; i++) {
-          v[i] = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(i) * rb);
-        }
+          for (int i = 0; i < SUB; i++) {
+            v[i] = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(i) * rb);
+            if constexpr (WEIGHTED) {
+              const float w = wstage[i];
+              v[i] = make_float4(__fmul_rn(w, v[i].x), __fmul_rn(w, v[i].y), __fmul_rn(w, v[i].z),
+                                 __fmul_rn(w, v[i].w));
+            }
+          }
 #pragma unroll
-        for (int i = 0; i < kGsBatch; i++) {
-          acc.x = __fadd_rn(acc.x, v[i].x);
-          acc.y = __fadd_rn(acc.y, v[i].y);
-          acc.z = __fadd_rn(acc.z, v[i].z);
-          acc.w = __fadd_rn(acc.w, v[i].w);
+          for (int i = 0; i < SUB; i++) {
+            acc.x = __fadd_rn(acc.x, v[i].x);
+            acc.y = __fadd_rn(acc.y, v[i].y);
+            acc.z = __fadd_rn(acc.z, v[i].z);
+            acc.w = __fadd_rn(acc.w, v[i].w);
+          }
         }
+        s = SUB;
+        if (first + s == cur_end) finish_chunk();
       }
-      s = kGsBatch;
-      if (first + s == cur_end) finish_chunk();
-    }
-    for (; s < cnt; s++) {
-      if (col) {
-        const float4 v = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(s) * rb);
-        acc.x = __fadd_rn(acc.x, v.x);
-        acc.y = __fadd_rn(acc.y, v.y);
-        acc.z = __fadd_rn(acc.z, v.z);
-        acc.w = __fadd_rn(acc.w, v.w);
+      for (; s < cnt; s++) {
+        if (col) {
+          float4 v = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(s) * rb);
+          if constexpr (WEIGHTED) {
+            const float w = wstage[s];
+            v = make_float4(__fmul_rn(w, v.x), __fmul_rn(w, v.y), __fmul_rn(w, v.z), __fmul_rn(w, v.w));
+          }
+          acc.x = __fadd_rn(acc.x, v.x);
+          acc.y = __fadd_rn(acc.y, v.y);
+          acc.z = __fadd_rn(acc.z, v.z);
+          acc.w = __fadd_rn(acc.w, v.w);
+        }
+        if (first + s + 1 == cur_end) finish_chunk();
       }
-      if (first + s + 1 == cur_end) finish_chunk();
     }
+    if constexpr (WEIGHTED) __syncwarp();   // every lane has read this stage's weights
     issue_batch(b + kGsStages);   // refill the stage just read (this lane read only what it copied)
   }
   cp_async_wait<0>();
@@ -515,14 +567,31 @@ bool grad_stream_eligible(const GradParams& p, bool allow) {
 
 template <typename IdxT>
 void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
-  const size_t smem = static_cast<size_t>(kGsWarps) * 32u * static_cast<size_t>(p.nvec) * 16u;
+  // rows per stage: 4 (a ring of 16 rows per warp; default, measured best on skewed and on all-distinct
+  // batches alike) or 8 (32 rows, half the warps per SM)
+  static const int forced = [] {
+    const char* e = std::getenv("NVE_B200_GRAD_BATCH");   // tuning knob
+    const int v = e ? std::atoi(e) : 0;
+    return (v == 4 || v == 8) ? v : 0;
+  }();
+  const size_t row_bytes = static_cast<size_t>(p.nvec) * 16u;
+  const int batch = forced ? forced : 4;
+  const size_t smem = static_cast<size_t>(kGsWarps) * kGsStages * batch * (row_bytes + (p.pos_weight ? 4 : 0));
   static const int window = [] {
     const char* e = std::getenv("NVE_B200_GRAD_WINDOW");   // tuning knob: positions per warp
     const int v = e ? std::atoi(e) : 0;
     return v >= 32 && v <= (1 << 20) ? v : kGsWindow;
   }();
   const int64_t warps = (n + window - 1) / window;
-  grad_stream_kernel<IdxT><<<blocks_for(warps, kGsWarps), kGsWarps * 32, smem, s>>>(p, window);
+  const unsigned grid = blocks_for(warps, kGsWarps);
+  const int block = kGsWarps * 32;
+  if (p.pos_weight) {
+    if (batch == 4) grad_stream_kernel<IdxT, 4, true><<<grid, block, smem, s>>>(p, window);
+    else grad_stream_kernel<IdxT, 8, true><<<grid, block, smem, s>>>(p, window);
+  } else {
+    if (batch == 4) grad_stream_kernel<IdxT, 4, false><<<grid, block, smem, s>>>(p, window);
+    else grad_stream_kernel<IdxT, 8, false><<<grid, block, smem, s>>>(p, window);
+  }
 }
 
 // Second pass: split groups.  A warp scans 32 chunks (one per lane) for first chunks of split
@@ -600,6 +669,82 @@ void launch_grad_finish(const GradParams& p, cudaStream_t s) {
 
 }  // namespace
 
+// ---- pooled backward: which bag-gradient row, and with which weight, each position contributes ---
+namespace {
+
+// bag_sum[b] = number of keys of bag b (unweighted) or the sum of its weights, added in bag order.
+template <typename IdxT>
+__global__ void bag_sums_kernel(const IdxT* __restrict__ csr, int64_t num_bags, int64_t hot,
+                                const float* __restrict__ weights, float* __restrict__ bag_sum) {
+  const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (b >= num_bags) return;
+  const int64_t s = csr ? static_cast<int64_t>(csr[b]) : b * hot;
+  const int64_t e = csr ? static_cast<int64_t>(csr[b + 1]) : s + hot;
+  float acc = 0.f;
+  if (weights) {
+    for (int64_t i = s; i < e; i++) acc = __fadd_rn(acc, weights[i]);
+  } else {
+    acc = static_cast<float>(e - s);
+  }
+  bag_sum[b] = acc;
+}
+
+// For sorted position q (original position op = inverse[q]): src_row[q] = bag of op,
+// pos_w[q] = weight of op, divided by its bag's sum for the mean forms.
+template <typename IdxT>
+__global__ void pooled_sources_kernel(const IdxT* __restrict__ inverse, const IdxT* __restrict__ num_runs,
+                                      const IdxT* __restrict__ dedup_offsets,
+                                      const IdxT* __restrict__ csr, int64_t num_bags, int64_t hot,
+                                      const float* __restrict__ weights, const float* __restrict__ bag_sum,
+                                      IdxT* __restrict__ src_row, float* __restrict__ pos_w, int64_t n_bound) {
+  const int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t n = static_cast<int64_t>(dedup_offsets[num_runs[1]]);
+  if (q >= n || q >= n_bound) return;
+  const int64_t op = static_cast<int64_t>(inverse[q]);
+  int64_t b;
+  if (csr) {
+    int64_t lo = 0, hi = num_bags;            // last b with csr[b] <= op
+    while (hi - lo > 1) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (static_cast<int64_t>(csr[mid]) <= op) lo = mid; else hi = mid;
+    }
+    b = lo;
+  } else {
+    b = op / hot;
+  }
+  src_row[q] = static_cast<IdxT>(b);
+  if (pos_w) {
+    float w = weights ? weights[op] : 1.f;
+    if (bag_sum) w = __fdiv_rn(w, bag_sum[b]);
+    pos_w[q] = w;
+  }
+}
+
+}  // namespace
+
+void pooled_sources_run(nve_key_type_t key_type, const void* inverse, const void* num_runs_dev,
+                        const void* dedup_offsets, const void* csr, int64_t num_bags, int64_t hot,
+                        const float* weights, bool mean, float* bag_sum, void* src_row, float* pos_w,
+                        int64_t num_keys, cudaStream_t stream) {
+  const int T = 256;
+  const bool i64 = key_type == NVE_KEY_INT64;
+  if (mean) {
+    if (i64) bag_sums_kernel<int64_t><<<blocks_for(num_bags, T), T, 0, stream>>>(
+        static_cast<const int64_t*>(csr), num_bags, hot, weights, bag_sum);
+    else bag_sums_kernel<int32_t><<<blocks_for(num_bags, T), T, 0, stream>>>(
+        static_cast<const int32_t*>(csr), num_bags, hot, weights, bag_sum);
+  }
+  if (i64) pooled_sources_kernel<int64_t><<<blocks_for(num_keys, T), T, 0, stream>>>(
+      static_cast<const int64_t*>(inverse), static_cast<const int64_t*>(num_runs_dev),
+      static_cast<const int64_t*>(dedup_offsets), static_cast<const int64_t*>(csr), num_bags, hot, weights,
+      mean ? bag_sum : nullptr, static_cast<int64_t*>(src_row), pos_w, num_keys);
+  else pooled_sources_kernel<int32_t><<<blocks_for(num_keys, T), T, 0, stream>>>(
+      static_cast<const int32_t*>(inverse), static_cast<const int32_t*>(num_runs_dev),
+      static_cast<const int32_t*>(dedup_offsets), static_cast<const int32_t*>(csr), num_bags, hot, weights,
+      mean ? bag_sum : nullptr, static_cast<int32_t*>(src_row), pos_w, num_keys);
+  NVE_B200_CUDA(cudaGetLastError());
+}
+
 size_t dedup_workspace_bytes(nve_key_type_t key_type, int64_t capacity) {
   if (key_type == NVE_KEY_INT64) {
     return carve<int64_t>(nullptr, capacity, cub_bytes_for<int64_t>(capacity)).total;
@@ -631,7 +776,7 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     int64_t num_keys, bool streamed, cudaStream_t stream) {
+                     int64_t num_keys, bool streamed, const float* pos_weight, cudaStream_t stream) {
   NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
   NVE_B200_ARG(grad_stride % 16 == 0 && dst_stride % 16 == 0 &&
                    reinterpret_cast<uint64_t>(grads) % 16 == 0 &&
@@ -641,6 +786,7 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   p.grads = static_cast<const uint8_t*>(grads);
   p.grad_stride = grad_stride;
   p.inverse = inverse;
+  p.pos_weight = pos_weight;
   p.offsets = offsets;
   p.loc_map = loc_map;
   p.unique = unique;
@@ -732,6 +878,6 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
     dedup_grads_run(key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
                     max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
                     dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
-                    num_keys, /*streamed=*/false, static_cast<cudaStream_t>(stream));
+                    num_keys, /*streamed=*/false, /*pos_weight=*/nullptr, static_cast<cudaStream_t>(stream));
   });
 }

@@ -19,6 +19,8 @@ const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int6
 // dst[u] = sum of grads rows of group u (fused == false), or
 // table[unique[u]] += alpha * sum (fused == true; dst is the table, keys outside
 // [0, table_rows) are skipped).  fp32 rows, 16-byte aligned.
+// pos_weight: optional weight per position of `inverse`: rows are multiplied by it before they are
+// added (one rounding each: multiply, then add).
 // streamed: let rows of up to 512 bytes take the first pass that streams them through shared
 // memory with asynchronous copies; false keeps the register form for every width.
 void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
@@ -26,6 +28,16 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     int64_t num_keys, bool streamed, cudaStream_t stream);
+                     int64_t num_keys, bool streamed, const float* pos_weight, cudaStream_t stream);
+
+// Pooled backward, preparation: for every sorted position q of a dedup() result, src_row[q] = the
+// bag its key came from (CSR offsets of the key type, or fixed hotness when csr == null) and, when
+// pos_w != null, pos_w[q] = its weight (1 without weights), divided by the bag's weight sum / key
+// count for the mean forms.  dedup_grads_run then takes src_row as `inverse` and pos_w as
+// `pos_weight` with the bag gradients as `grads`.  bag_sum: scratch of num_bags floats (mean only).
+void pooled_sources_run(nve_key_type_t key_type, const void* inverse, const void* num_runs_dev,
+                        const void* dedup_offsets, const void* csr, int64_t num_bags, int64_t hot,
+                        const float* weights, bool mean, float* bag_sum, void* src_row, float* pos_w,
+                        int64_t num_keys, cudaStream_t stream);
 
 }  // namespace nve_b200

@@ -1,0 +1,54 @@
+"""Host-resident table storage that the GPU kernels read in place.
+
+``ManagedMemBlock`` mirrors the reference's class of the same name (``src/memblock.cpp:108-135``,
+exposed to Python by its binding): managed memory with the host as preferred location and the
+listed GPUs as accessors.  It is the storage to use for the backing table of the cached
+(LinearUVM) layer: GPU kernels keep the host link's rate over the whole table, which memory from
+``cudaHostAlloc`` / ``tensor.pin_memory()`` does not beyond a few GB.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import capi
+
+
+class ManagedMemBlock:
+    def __init__(self, size_in_bytes: int, gpu_ids=(0,)):
+        ids = (C.c_int32 * len(gpu_ids))(*gpu_ids)
+        p = C.c_void_p()
+        capi.check(capi.lib.nve_b200_managed_block_create(C.byref(p), size_in_bytes, ids, len(gpu_ids)))
+        self.ptr = p.value
+        self.size = size_in_bytes
+
+    def get_ptr(self) -> int:
+        return self.ptr
+
+    def get_size_in_bytes(self) -> int:
+        return self.size
+
+    def data_ptr(self) -> int:          # so that a block can be passed wherever a tensor is accepted
+        return self.ptr
+
+    def as_tensor(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A CPU tensor over the block (no copy).  The block must outlive the tensor."""
+        count = int(np.prod(shape))
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        if count * itemsize > self.size:
+            raise ValueError("shape does not fit the block")
+        raw = (C.c_uint8 * (count * itemsize)).from_address(self.ptr)
+        return torch.frombuffer(raw, dtype=dtype, count=count).view(*shape)
+
+    def close(self):
+        if self.ptr:
+            capi.check(capi.lib.nve_b200_managed_block_destroy(self.ptr))
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -109,6 +109,19 @@ class NVEmbedBinding:
         Scratch (inverse map, offsets, chunk map) is owned by this object and grows on demand."""
         if self._dtype != DataType_t.Float32:
             raise NotImplementedError("concat_backprop is provided for Float32 gradients")
+        self._ensure_deduper(num_keys)
+        s = stream or None
+        capi.check(capi.lib.nve_b200_deduper_dedup(
+            self._deduper, keys, num_keys, unique_keys, self._counts.data_ptr(),
+            self._loc_map.data_ptr(), self._runs, self._inverse.data_ptr(), self._offsets.data_ptr(),
+            s, 0))
+        capi.check(capi.lib.nve_b200_dedup_grads(
+            self._deduper, grads, self._row_bytes, self._row_bytes, num_keys, unique_keys,
+            self._inverse.data_ptr(), self._offsets.data_ptr(), self._loc_map.data_ptr(),
+            output_grads, self._row_bytes, 0, 0, 1.0, s))
+        return int(self._runs[0])
+
+    def _ensure_deduper(self, num_keys: int):
         import torch
         if num_keys > self._dedup_capacity:
             if self._deduper:
@@ -123,19 +136,26 @@ class NVEmbedBinding:
             self._offsets = torch.empty(cap + 1, dtype=torch.int64, device=dev)
             self._loc_map = torch.empty(cap + 1, dtype=torch.int64, device=dev)
             self._dedup_capacity = num_keys
-        s = stream or None
-        capi.check(capi.lib.nve_b200_deduper_dedup(
-            self._deduper, keys, num_keys, unique_keys, self._counts.data_ptr(),
-            self._loc_map.data_ptr(), self._runs, self._inverse.data_ptr(), self._offsets.data_ptr(),
-            s, 0))
-        capi.check(capi.lib.nve_b200_dedup_grads(
-            self._deduper, grads, self._row_bytes, self._row_bytes, num_keys, unique_keys,
-            self._inverse.data_ptr(), self._offsets.data_ptr(), self._loc_map.data_ptr(),
-            output_grads, self._row_bytes, 0, 0, 1.0, s))
-        return int(self._runs[0])
 
-    def pooling_backprop(self, *args, **kwargs):
-        raise NotImplementedError("pooled backward is outside the lookup hot path")
+    def pooling_backprop(self, num_keys: int, keys: int, grads: int, unique_keys: int, output_grads: int,
+                         pooling_type: int, num_offsets: int, offsets: int, data_type: int = 0,
+                         weights: int = 0, stream: int = 0) -> int:
+        """Backward of a pooled lookup (binding_layers.hpp:191-250): ``grads`` holds one fp32 row
+        per bag, ``offsets`` the int64 CSR offsets of ``num_offsets`` bags (``num_offsets + 1``
+        entries), ``weights`` optional fp32 per-key weights.  Writes the unique keys and, per unique
+        key, the weighted sum of the gradients of the bags it occurs in; returns the number of
+        unique keys."""
+        if self._dtype != DataType_t.Float32:
+            raise NotImplementedError("pooling_backprop is provided for Float32 gradients")
+        if weights and data_type not in (0, int(DataType_t.Float32)):
+            raise NotImplementedError("pooling_backprop takes Float32 weights")
+        self._ensure_deduper(num_keys)
+        n_unique = C.c_int64(0)
+        capi.check(capi.lib.nve_b200_pooling_backprop(
+            self._deduper, num_keys, keys, grads, self._row_bytes, self._row_bytes, int(pooling_type),
+            capi.SPARSE_CSR, offsets, num_offsets, 0, weights or None, unique_keys, output_grads,
+            self._row_bytes, C.byref(n_unique), stream or None))
+        return int(n_unique.value)
 
     def close(self) -> None:
         for ctx in self._ctx.values():

@@ -66,7 +66,17 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     """LinearUVM cached lookup, no pooling: table in pinned host memory, 10 % of rows cached."""
     row_bytes = dim * 2
     stream = torch.cuda.current_stream()
-    table = torch.empty((rows, dim), dtype=torch.float16).pin_memory()
+    # Table storage: a managed block advised to stay in host memory (what the reference's
+    # ManagedMemBlock gives a LinearUVM layer).  NVE_B200_C3_TABLE=pinned uses cudaHostAlloc'ed
+    # memory instead, for the comparison quoted in the design notes.
+    storage = os.environ.get("NVE_B200_C3_TABLE", "managed")
+    if storage == "managed":
+        from .memblock import ManagedMemBlock
+        block = ManagedMemBlock(rows * row_bytes, (torch.cuda.current_device(),))
+        table = block.as_tensor((rows, dim), torch.float16)
+    else:
+        block = None
+        table = torch.empty((rows, dim), dtype=torch.float16).pin_memory()
     _fill_rows_fp16(table, 30)
     cache_bytes = int(rows * cache_frac) * row_bytes
     gt = GpuTable(cache_bytes, row_bytes, "float16", uvm_table=table, uvm_num_rows=rows)
@@ -80,7 +90,7 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     link = h2d_probe_gbs()
     peak, kind = _hbm_peak(root)
     res = {"workload": "C3 LinearUVM: 100M x 128 fp16 in pinned host memory, 10% GPU cache, 262144 keys, no pooling",
-           "host_link_probe_gbs": link, "gather": "bulk-copy" if os.environ.get("NVE_B200_GATHER_BULK") == "1" else "lane-vector",
+           "host_link_probe_gbs": link, "table_storage": storage, "gather": "bulk-copy" if os.environ.get("NVE_B200_GATHER_BULK") == "1" else "lane-vector",
            "runs": {}}
     nb = 16   # distinct batches per run, cycled: missed rows must come over the link every time
     for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(batch, rows, 1.2, 320 + 2 * b)),
@@ -119,6 +129,9 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
             res["reference_gpu"][name] = {"us_per_lookup": ms * 1e3, "keys_per_s": batch / (ms * 1e-3),
                                           "hit_rate_first_batch": 1.0 - misses / batch}
         rc.close()
+    del table
+    if block is not None:
+        block.close()
     return res
 
 

@@ -69,6 +69,28 @@ class Oracle:
                                  d["num_chunks"], _ptr(out), grads.shape[1])
         return out
 
+    def pooling_backprop(self, keys: np.ndarray, csr: np.ndarray, bag_grads: np.ndarray, pooling: str,
+                         weights: np.ndarray | None = None, max_run: int = 1024):
+        """Backward of a pooled lookup: (unique keys, per-key gradient sums).  Per position the
+        gradient is fl32(w * bag_grad[bag]) with w = 1, 1/len, weight or weight / sum of the bag's
+        weights (fp32 sum in bag order, IEEE division); positions of a key are then added in the
+        order of dedup_grads (cuda_ops/gradient_calculator.cuh:85-136,254-286)."""
+        n = keys.size
+        lens = np.diff(csr)
+        bag = np.repeat(np.arange(lens.size), lens)
+        w = np.ones(n, np.float32) if weights is None or pooling in ("sum", "mean") else weights.astype(np.float32)
+        if pooling in ("mean", "wmean"):
+            sums = np.zeros(lens.size, np.float32)
+            for b in range(lens.size):          # fp32, in bag order
+                acc = np.float32(0)
+                for i in range(csr[b], csr[b + 1]):
+                    acc = np.float32(acc + w[i])
+                sums[b] = acc
+            w = (w / sums[bag]).astype(np.float32)
+        per_pos = (w[:, None] * bag_grads.astype(np.float32)[bag]).astype(np.float32)
+        d = self.dedup(keys, max_run=max_run)
+        return d["unique"], self.dedup_grads(per_pos, d)
+
     def gather(self, table2d: np.ndarray, keys: np.ndarray, out: np.ndarray, hit_mask=None) -> int:
         rows = table2d.reshape(table2d.shape[0], -1).view(np.uint8)
         return self.lib.nve_oracle_gather(_ptr(rows), rows.shape[0], rows.shape[1], _ptr(keys),
@@ -368,6 +390,7 @@ class ReferenceGpu:
             "refgpu_dedup_grads": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
             "refgpu_dedup_grads_timed": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                          C.POINTER(f32)],
+            "refgpu_pooling_backprop": [_vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(_i64)],
             "refgpu_find_and_combine": [_i32, _i64, _vp, pp, pp, _i32, _i32, _i32, _vp, _i32, _i32,
                                         C.POINTER(f32)],
         }
@@ -383,6 +406,14 @@ class ReferenceGpu:
     # ---- cache
     def cache(self, cache_bytes, row_bytes, sentinel=-1, decay=0.95, max_modify=1 << 20):
         return RefGpuCache(self, cache_bytes, row_bytes, sentinel, decay, max_modify)
+
+    def pooling_backprop(self, keys_ptr, n, csr_ptr, num_bags, grads_ptr, weights_ptr, pooling, width,
+                         unique_ptr, out_ptr) -> int:
+        """pooling: "sum", "mean", "wsum", "wmean" (the mean forms need weights)."""
+        u = _i64(0)
+        self.check(self.lib.refgpu_pooling_backprop(keys_ptr, n, csr_ptr, num_bags, grads_ptr, weights_ptr,
+                                                    POOL[pooling], width, unique_ptr, out_ptr, C.byref(u)))
+        return u.value
 
     def deduper(self, max_run, max_keys):
         return RefGpuDeduper(self, max_run, max_keys)

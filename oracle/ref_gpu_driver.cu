@@ -10,6 +10,7 @@
 //   cuda_ops/gather_keys_data_ptrs.cuh                    DefaultGPUHistogram (src/gpu_table.cu:443-467
 //                                                         shows the call order reproduced below)
 //   cuda_ops/deduper.cuh, cuda_ops/dedup_grads_kernel.cuh Deduper, CallComputeGradients
+//   cuda_ops/gradient_calculator.cuh                      GradientCalculator (pooled backward)
 #include <cstdint>
 #include <cstdio>
 #include <memory>
@@ -26,6 +27,7 @@
 #include "cuda_ops/gather_keys_data_ptrs.cuh"
 #include "cuda_ops/deduper.cuh"
 #include "cuda_ops/dedup_grads_kernel.cuh"
+#include "cuda_ops/gradient_calculator.cuh"
 // Only the combinations used below are instantiated (the public dispatcher would instantiate the
 // whole type matrix); this macro drops the extern declarations of the pre-built matrix.
 #define NVE_FAC_SKIP_EXTERN_DECLS
@@ -414,6 +416,31 @@ int refgpu_dedup_grads_timed(const float* d_grads, float* d_unique_grads, const 
     *ms_per_call = ms / static_cast<float>(iters);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+  });
+}
+
+// Pooled backward by the reference's GradientCalculator<int64_t, 1024> (fp32 gradients and weights,
+// CSR bags).  pooling: 1 Sum, 2 Mean, 3 WeightedSum, 4 WeightedMean (the reference's enum values).
+// The mean forms read d_weights, so it must not be null for them.
+int refgpu_pooling_backprop(const int64_t* d_keys, int64_t n, const int64_t* d_csr, int64_t num_bags,
+                            const float* d_bag_grads, const float* d_weights, int pooling, int width,
+                            int64_t* d_unique_out, float* d_grads_out, int64_t* num_unique) {
+  return guarded([&] {
+    nve::GradientCalculator<Key, 1024> calc(nve::GetDefaultAllocator());
+    size_t dev = 0, host = 0;
+    calc.get_alloc_requirements(static_cast<Key>(n), sizeof(float), dev, host);
+    char* d_tmp = nullptr;
+    char* h_tmp = nullptr;
+    ck(cudaMalloc(&d_tmp, dev ? dev : 16), "cudaMalloc");
+    ck(cudaMallocHost(&h_tmp, host ? host : 16), "cudaMallocHost");
+    calc.set_and_init_buffers(static_cast<Key>(n), sizeof(float), d_tmp, h_tmp);
+    ck(cudaDeviceSynchronize(), "sync");
+    *num_unique = static_cast<int64_t>(calc.compute_gradients<float, false>(
+        d_keys, d_csr, d_bag_grads, d_weights, d_grads_out, d_unique_out, static_cast<uint32_t>(num_bags),
+        static_cast<Key>(n), 0, static_cast<uint32_t>(width), static_cast<nve::PoolingType_t>(pooling), 0));
+    ck(cudaDeviceSynchronize(), "sync");
+    cudaFree(d_tmp);
+    cudaFreeHost(h_tmp);
   });
 }
 

@@ -1,5 +1,5 @@
-"""GPU checks of the cached layer over a linear backing table (pinned host memory and device
-memory) and of the pynve-named Python edge, against the oracle.  Outputs never depend on what is
+"""GPU checks of the cached layer over a linear backing table (pinned host memory, a managed block
+kept in host memory, and device memory) and of the pynve-named Python edge, against the oracle.  Outputs never depend on what is
 cached; hit rates must equal the oracle cache's."""
 import numpy as np
 import pytest
@@ -14,14 +14,21 @@ pytestmark = pytest.mark.gpu
 def make_layer(torch, table_np, cache_rows, where, dtype="float16", default_row=-1):
     from nv_embedding_cache_b200.layers import GpuTable, LinearUVMEmbeddingLayer
     rows, row_bytes = table_np.shape[0], table_np.strides[0]
-    backing = torch.from_numpy(table_np).pin_memory() if where == "host" else torch.from_numpy(table_np).cuda()
+    if where == "managed":
+        from nv_embedding_cache_b200.memblock import ManagedMemBlock
+        backing = ManagedMemBlock(table_np.nbytes, (0,))
+        backing.as_tensor(table_np.shape, torch.from_numpy(table_np).dtype).copy_(torch.from_numpy(table_np))
+    elif where == "host":
+        backing = torch.from_numpy(table_np).pin_memory()
+    else:
+        backing = torch.from_numpy(table_np).cuda()
     cache_bytes = (cache_rows // 8) * (64 + 8 * row_bytes + 32)
     gt = GpuTable(cache_bytes, row_bytes, dtype, uvm_table=backing, uvm_num_rows=rows)
     layer = LinearUVMEmbeddingLayer(gt, default_row_index=default_row)
     return layer, gt, backing, cache_bytes
 
 
-@pytest.mark.parametrize("where", ["host", "device"])
+@pytest.mark.parametrize("where", ["host", "device", "managed"])
 def test_unpooled_lookup_is_byte_exact_and_hitrate_matches(torch_cuda, oracle, where):
     torch = torch_cuda
     rows, dim = 20000, 128
