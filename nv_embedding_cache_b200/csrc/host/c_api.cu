@@ -7,7 +7,6 @@
 struct nve_context_s { nve_b200::context_ptr_t ptr; };
 struct nve_table_s { std::shared_ptr<nve_b200::Table> ptr; nve_key_type_t key_type; };
 struct nve_layer_s { std::shared_ptr<nve_b200::EmbeddingLayer> ptr; nve_key_type_t key_type; };
-struct nve_heuristic_s { int kind; };
 struct nve_thread_pool_s { int unused; };
 struct nve_allocator_s { int unused; };
 struct nve_table_factory_s { int unused; };
@@ -101,17 +100,17 @@ nve_status_t nve_thread_pool_destroy(nve_thread_pool_t) { return not_impl("nve_t
 nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t, int64_t*) { return not_impl("nve_thread_pool_num_workers"); }
 nve_status_t nve_configure_default_thread_pool(const char*) { return not_impl("nve_configure_default_thread_pool"); }
 
-// ---- heuristics: handles only ----
+// ---- insert heuristics (used by the cached layer's automatic cache population) ----
 nve_status_t nve_heuristic_create_default(nve_heuristic_t* out, const float* thresholds,
                                           int64_t num_thresholds) {
   if (!out) return bad_arg("out must not be NULL");
   if (num_thresholds < 0 || (num_thresholds > 0 && !thresholds)) return bad_arg("invalid thresholds");
-  *out = new nve_heuristic_s{0};
+  *out = new nve_heuristic_s{0, std::vector<float>(thresholds, thresholds + num_thresholds)};
   return NVE_SUCCESS;
 }
 nve_status_t nve_heuristic_create_never(nve_heuristic_t* out) {
   if (!out) return bad_arg("out must not be NULL");
-  *out = new nve_heuristic_s{1};
+  *out = new nve_heuristic_s{1, {}};
   return NVE_SUCCESS;
 }
 nve_status_t nve_heuristic_destroy(nve_heuristic_t h) {

@@ -11,6 +11,7 @@
 //   * the backing-table write-through of update / update_accumulate always runs as a GPU kernel.
 #include <algorithm>
 #include <mutex>
+#include <random>
 
 #include "../kernels/cache_modify.cuh"
 #include "layers.hpp"
@@ -336,13 +337,43 @@ class GpuTable : public Table {
 }  // namespace
 
 // ---- cached layer over a linear backing table ------------------------------------------------
-// Reference LinearUVMEmbeddingLayer<KeyType> (src/linear_embedding_layer.cu:30-316).  Automatic
-// cache population (insert heuristics) is not part of the lookup path: callers insert explicitly.
+// Reference LinearUVMEmbeddingLayer<KeyType> (src/linear_embedding_layer.cu:30-316).
+//
+// Automatic cache population follows the reference's AutoInsertHandler (src/layer_utils.cpp:62-275):
+// the insert heuristic sees the hit rate of lookups; when it asks for an insert the keys of the
+// following lookups are collected until min_insert_size_gpu of them are there, then their rows are
+// promoted from the backing table, and min_insert_freq_gpu lookups pass before the heuristic is
+// asked again.  Unlike the reference, no lookup waits for its own hit rate: the miss counter is
+// copied to pinned memory behind the lookup and read at a LATER lookup once its event has
+// completed, keys are collected device to device on the lookup stream, and the insert runs on the
+// modify stream.  A NULL heuristic means the default one (threshold 0.75), as in the reference;
+// it needs a table configured with count_misses.
 class LinearUVMEmbeddingLayer : public EmbeddingLayer {
+  struct AutoInsert {
+    bool enabled = false;
+    float threshold = 0.75f;
+    int64_t min_wait = 0, min_size = 1 << 16;
+    std::mt19937 gen{98437598437ULL};               // the reference's fixed seed
+    std::uniform_real_distribution<> dis{0.0, 1.0};
+    std::mutex mu;
+    int64_t wait_cnt = 0;
+    int64_t* h_counts = nullptr;                    // pinned: miss counter before / after a lookup
+    cudaEvent_t readback_done = nullptr;
+    bool pending = false;
+    int64_t pending_keys = 0;
+    void* buf[2] = {nullptr, nullptr};              // collected keys (device), alternating
+    cudaEvent_t buf_free[2] = {nullptr, nullptr};   // the insert that read the buffer is done
+    int cur = 0;
+    int64_t capacity = 0, target = 0, collected = 0;
+    bool collecting = false;
+    int64_t inserts_launched = 0;
+  };
+
  public:
   LinearUVMEmbeddingLayer(const nve_linear_uvm_layer_config_t& cfg, nve_key_type_t key_type,
                           std::shared_ptr<GpuTable> table)
       : default_row_(cfg.default_row_index), key_type_(key_type), table_(std::move(table)) {
+    init_auto_insert(cfg);
     NVE_B200_CHECK(table_ != nullptr, "Invalid GPU table");
     NVE_B200_CHECK(table_->config().uvm_table != nullptr, "GPU Table must be backed by a UVM buffer");
     NVE_B200_CHECK(table_->config().uvm_num_rows > 0, "uvm_num_rows must be >0");
@@ -379,6 +410,7 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
       NVE_B200_CHECK(tc.count_misses, "GPU table was not configured to report hit counts");
       table_->reset_lookup_counter(ctx);
     }
+    const bool armed = auto_insert_before(ctx, num_keys, d_keys.device, s);
 
     if (pool_params && !raw_concat) {
       const bool concat = pool_params->pooling_type == NVE_POOL_CONCATENATE;
@@ -454,6 +486,7 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
                           default_row_, s);
     }
     d_out.copy_back(s);
+    if (armed) auto_insert_after(c, num_keys, s);
 
     if (hitrates) {
       int64_t* host_misses = static_cast<int64_t*>(c.scratch("miss_readback", 64, true));
@@ -493,12 +526,29 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
     NVE_B200_CHECK(value_size == table_->config().row_size_in_bytes, "Invalid value size");
     table_->update_accumulate(ctx, num_keys, keys, value_stride, value_size, values, value_type);
   }
-  void clear(context_ptr_t& ctx) override { table_->clear(ctx); }
+  void clear(context_ptr_t& ctx) override {
+    drop_collection();
+    table_->clear(ctx);
+  }
   void erase(context_ptr_t& ctx, int64_t num_keys, const void* keys, int64_t table_id) override {
     NVE_B200_CHECK(table_id < get_num_tables(), "Invalid table_id");
     NVE_B200_CHECK(num_keys >= 0, "Invalid num_keys");
     NVE_B200_CHECK(keys != nullptr, "Invalid keys buffer");
+    drop_collection();
     table_->erase(ctx, num_keys, keys);
+  }
+  ~LinearUVMEmbeddingLayer() override {
+    if (ai_.h_counts) (void)cudaFreeHost(ai_.h_counts);
+    if (ai_.readback_done) (void)cudaEventDestroy(ai_.readback_done);
+    for (int i = 0; i < 2; i++) {
+      if (ai_.buf[i]) (void)cudaFree(ai_.buf[i]);
+      if (ai_.buf_free[i]) (void)cudaEventDestroy(ai_.buf_free[i]);
+    }
+    (void)cudaGetLastError();
+  }
+  int64_t auto_inserts_launched() {
+    std::lock_guard<std::mutex> lock(ai_.mu);
+    return ai_.inserts_launched;
   }
   context_ptr_t create_execution_context(cudaStream_t lookup_stream,
                                          cudaStream_t modify_stream) override {
@@ -507,9 +557,98 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
   int64_t get_num_tables() const override { return 1; }
 
  private:
+  void init_auto_insert(const nve_linear_uvm_layer_config_t& cfg) {
+    const nve_gpu_table_config_t& tc = table_->config();
+    const nve_heuristic_s* h = cfg.insert_heuristic;
+    if (h && h->kind == 1) return;                  // never-insert heuristic
+    if (!tc.count_misses) return;                   // no hit rate to steer by
+    if (h && !h->thresholds.empty()) ai_.threshold = h->thresholds[0];
+    if (h && h->thresholds.empty()) return;         // a default heuristic for zero tables
+    ai_.min_wait = std::max<int64_t>(cfg.min_insert_freq_gpu, 0);
+    ai_.min_size = std::max<int64_t>(cfg.min_insert_size_gpu, 1);
+    ai_.capacity = std::max<int64_t>(tc.max_modify_size, 1);
+    ScopedDevice sd(tc.device_id);
+    NVE_B200_CUDA(cudaMallocHost(&ai_.h_counts, 2 * sizeof(int64_t)));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.readback_done, cudaEventDisableTiming));
+    for (int i = 0; i < 2; i++) {
+      NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.buf_free[i], cudaEventDisableTiming));
+    }
+    ai_.enabled = true;
+  }
+
+  // The reference's default heuristic (src/insert_heuristic.cpp:26-35).
+  bool insert_needed(float hitrate) {
+    const double warmup = 1.0 - hitrate;
+    const double steady = warmup * warmup * warmup;
+    return hitrate < ai_.threshold ? ai_.dis(ai_.gen) < warmup : ai_.dis(ai_.gen) < steady;
+  }
+
+  void drop_collection() {
+    if (!ai_.enabled) return;
+    std::lock_guard<std::mutex> lock(ai_.mu);
+    ai_.collecting = false;
+    ai_.collected = 0;
+  }
+
+  // Before the lookup kernels of a batch: use the hit rate of an earlier lookup if its read-back has
+  // landed, collect this batch's keys when an insert is wanted, launch the insert when enough keys
+  // are there.  Returns true when this lookup's miss count is to be read back.
+  bool auto_insert_before(context_ptr_t& ctx, int64_t num_keys, const void* d_keys, cudaStream_t s) {
+    if (!ai_.enabled || num_keys <= 0) return false;
+    std::lock_guard<std::mutex> lock(ai_.mu);
+    const int kb = key_bytes(key_type_);
+    bool have_rate = false;
+    float rate = 0.f;
+    if (ai_.pending && cudaEventQuery(ai_.readback_done) == cudaSuccess) {
+      const int64_t missed = ai_.h_counts[1] - ai_.h_counts[0];
+      rate = 1.f - static_cast<float>(missed) / static_cast<float>(ai_.pending_keys);
+      have_rate = true;
+      ai_.pending = false;
+    }
+    (void)cudaGetLastError();   // cudaErrorNotReady from the query is not an error
+    bool collect = ai_.collecting;
+    if (!collect && have_rate && --ai_.wait_cnt < 0 && insert_needed(rate)) {
+      ai_.collecting = collect = true;
+      ai_.collected = 0;
+      ai_.target = std::min(std::max(num_keys, ai_.min_size), ai_.capacity);
+    }
+    if (ai_.wait_cnt < 0) ai_.wait_cnt = 0;
+    if (collect) {
+      if (!ai_.buf[ai_.cur]) NVE_B200_CUDA(cudaMalloc(&ai_.buf[ai_.cur], size_t(ai_.capacity) * kb));
+      if (ai_.collected == 0) NVE_B200_CUDA(cudaStreamWaitEvent(s, ai_.buf_free[ai_.cur], 0));
+      const int64_t part = std::min(num_keys, ai_.target - ai_.collected);
+      NVE_B200_CUDA(cudaMemcpyAsync(static_cast<char*>(ai_.buf[ai_.cur]) + size_t(ai_.collected) * kb, d_keys,
+                                    size_t(part) * kb, cudaMemcpyDeviceToDevice, s));
+      ai_.collected += part;
+      if (ai_.collected >= ai_.target || ai_.collected >= ai_.min_size) {
+        table_->insert_from_table(ctx, ai_.collected, ai_.buf[ai_.cur]);
+        NVE_B200_CUDA(cudaEventRecord(ai_.buf_free[ai_.cur], ctx->modify_stream()));
+        ai_.cur ^= 1;
+        ai_.collecting = false;
+        ai_.collected = 0;
+        ai_.wait_cnt = ai_.min_wait;
+        ai_.inserts_launched++;
+      }
+    }
+    if (ai_.pending) return false;                  // one read-back in flight at a time
+    NVE_B200_CUDA(cudaMemcpyAsync(&ai_.h_counts[0], ctx->miss_counter(), sizeof(int64_t),
+                                  cudaMemcpyDeviceToHost, s));
+    return true;
+  }
+
+  void auto_insert_after(ExecutionContext& c, int64_t num_keys, cudaStream_t s) {
+    std::lock_guard<std::mutex> lock(ai_.mu);
+    NVE_B200_CUDA(cudaMemcpyAsync(&ai_.h_counts[1], c.miss_counter(), sizeof(int64_t),
+                                  cudaMemcpyDeviceToHost, s));
+    NVE_B200_CUDA(cudaEventRecord(ai_.readback_done, s));
+    ai_.pending = true;
+    ai_.pending_keys = num_keys;
+  }
+
   int64_t default_row_;
   nve_key_type_t key_type_;
   std::shared_ptr<GpuTable> table_;
+  AutoInsert ai_;
 };
 
 std::shared_ptr<Table> make_gpu_table(const nve_gpu_table_config_t& config, nve_key_type_t key_type) {

@@ -1,7 +1,17 @@
 // Table interface behind nve_table_t (reference include/table.hpp:28-181).
 #pragma once
 
+#include <vector>
+
 #include "context.hpp"
+
+// Insert heuristic behind nve_heuristic_t: the reference's default heuristic (thresholds per table,
+// src/insert_heuristic.cpp:21-35) or the never-insert heuristic.  The cached layer copies it at
+// creation, so the handle may be destroyed afterwards.
+struct nve_heuristic_s {
+  int kind;                       // 0 = default (probabilistic on the hit rate), 1 = never
+  std::vector<float> thresholds;  // default kind: one per table
+};
 
 namespace nve_b200 {
 

@@ -21,15 +21,10 @@ void launch_flags(const PoolKernelParams& p, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>((p.num_bags * GROUP + block - 1) / block);
   const bool weighted = p.weights != nullptr;
   const bool sanitize = p.default_row >= 0;
-  if (p.num_shards > 0) {
-    if (weighted) pool_dense_kernel<IN, GROUP, U, true, true, true><<<grid, block, 0, stream>>>(p);
-    else pool_dense_kernel<IN, GROUP, U, false, true, true><<<grid, block, 0, stream>>>(p);
-    return;
-  }
   if constexpr (IN == In::I8 || IN == In::U8) {
     if (p.word_loads) {
-      if (weighted) pool_dense_kernel<IN, GROUP, U, true, true, false, true><<<grid, block, 0, stream>>>(p);
-      else pool_dense_kernel<IN, GROUP, U, false, true, false, true><<<grid, block, 0, stream>>>(p);
+      if (weighted) pool_dense_kernel<IN, GROUP, U, true, true, true><<<grid, block, 0, stream>>>(p);
+      else pool_dense_kernel<IN, GROUP, U, false, true, true><<<grid, block, 0, stream>>>(p);
       return;
     }
   }

@@ -46,16 +46,13 @@ __device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, f
   }
 }
 
-// SHARDED: the table is split over peer-mapped shards (row r in shard r % W at local row r / W);
-// the owner lane then keeps the full 64-bit row address and rows are read with ordinary loads.
 // WORDS: rows that are only 4-byte aligned (quantised rows stored back to back: 256 values + a
 // 4-byte scale = 260 bytes).  A lane still owns 16 values, but fetches them as four 32-bit words,
 // word j of lane l being word j * nvec + l of the row, so that each of the four loads of a lane
 // group covers one contiguous run of the row.  Lane l then holds the columns
 // 4 * (j * nvec + l) .. + 3 for j = 0..3 and stores them as four short vectors.
-template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool SHARDED = false, bool WORDS = false>
+template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool WORDS = false>
 __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams p) {
-  static_assert(!(WORDS && SHARDED), "word loads are not combined with peer shards");
   constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
   constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
   const int lane = threadIdx.x & 31;
@@ -86,7 +83,6 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   for (int c = 0; c < len; c += GROUP) {
     const int n = min(GROUP, len - c);
     uint32_t my_key = 0;
-    uint64_t my_addr = 0;   // SHARDED only: address of the row's first byte
     float my_w = 1.f, my_scale = 1.f, my_qoff = 0.f;
     if (gl < n) {
       const int64_t k = start + c + gl;
@@ -96,15 +92,9 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
         key = p.default_row;
       }
       my_key = static_cast<uint32_t>(key);
-      if constexpr (SHARDED) {
-        const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
-        const uint32_t owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
-        my_addr = reinterpret_cast<uint64_t>(p.shard_base[owner]) + local * stride;
-      }
       if (WEIGHTED) my_w = load_weight(p.weights, p.w16, k);
       if constexpr (QUANT) {
-        const uint8_t* meta = SHARDED ? reinterpret_cast<const uint8_t*>(my_addr) + p.row_width
-                                      : p.table + static_cast<uint64_t>(my_key) * stride + p.row_width;
+        const uint8_t* meta = p.table + static_cast<uint64_t>(my_key) * stride + p.row_width;
         my_scale = load_meta(meta, p.meta_bytes);
         if (p.has_qoffset) my_qoff = load_meta(meta + p.meta_bytes, p.meta_bytes);
       }
@@ -116,10 +106,7 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
       uint4 raw[U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        if constexpr (SHARDED) {
-          const uint64_t a = __shfl_sync(gmask, my_addr, min(s + u, n - 1), GROUP);
-          if (lane_on) raw[u] = *reinterpret_cast<const uint4*>(a + gl * 16);
-        } else {
+        {
           const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
           if (lane_on) {
             if constexpr (WORDS) {
@@ -174,12 +161,14 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   }
 }
 
-// The lean kernel covers: no cache, 16-byte vectors, at most 32 vectors per row, rows addressable
-// with 32 bits, non-negative bag lengths below 2^31.
+// The lean kernel covers: no cache, no peer shards (rows fetched over NVLink want more loads in
+// flight per lane than this kernel keeps: the general kernel measured 845 GB/s per rank against
+// 751 GB/s for a sharded form of this one), 16-byte vectors or word loads, at most 32 vectors per
+// row, rows addressable with 32 bits, non-negative bag lengths below 2^31.
 // `p.nvec` counts 16-byte groups of values here, also for the word-load form (vb == 4).
 inline bool pool_dense_eligible(const PoolKernelParams& p, int vb) {
   if (p.cache.enabled || (vb != 16 && !p.word_loads) || p.nvec < 1 || p.nvec > 32 || p.row_stride > 0x7fffffffll) return false;
-  if (p.num_shards > 0) return !p.word_loads;             // peer-mapped shards: 64-bit addresses
+  if (p.num_shards > 0) return false;
   return p.table != nullptr && p.num_rows > 0 && p.num_rows <= 0xffffffffll;
 }
 

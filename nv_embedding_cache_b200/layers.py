@@ -195,13 +195,32 @@ class LinearUVMEmbeddingLayer(_Layer):
     (nve_linear_uvm_layer_create).  The layer keeps its GpuTable alive."""
 
     def __init__(self, gpu_table: GpuTable, *, default_row_index: int = -1,
-                 layer_name: str = "linear_uvm_layer"):
+                 layer_name: str = "linear_uvm_layer", insert_heuristic="never",
+                 min_insert_freq_gpu: int | None = None, min_insert_size_gpu: int | None = None):
+        """insert_heuristic: "never" (this wrapper's default: the cache holds what the caller
+        inserts), "default" (the C ABI's default: NULL handle, threshold 0.75) or a float threshold
+        for the default heuristic.  Automatic inserts need a table created with count_misses."""
         cfg = capi.lib.nve_linear_uvm_layer_config_default()
         self._name = layer_name.encode()
         cfg.layer_name = self._name
         cfg.default_row_index = default_row_index
+        if min_insert_freq_gpu is not None:
+            cfg.min_insert_freq_gpu = min_insert_freq_gpu
+        if min_insert_size_gpu is not None:
+            cfg.min_insert_size_gpu = min_insert_size_gpu
+        heuristic = C.c_void_p()
+        if insert_heuristic == "never":
+            capi.check(capi.lib.nve_heuristic_create_never(C.byref(heuristic)))
+        elif insert_heuristic != "default":
+            thr = (C.c_float * 1)(float(insert_heuristic))
+            capi.check(capi.lib.nve_heuristic_create_default(C.byref(heuristic), thr, 1))
+        cfg.insert_heuristic = heuristic
         self.gpu_table = gpu_table
         h = C.c_void_p()
-        capi.check(capi.lib.nve_linear_uvm_layer_create(C.byref(h), gpu_table.key_type,
-                                                        C.byref(cfg), gpu_table.handle, None))
+        try:
+            capi.check(capi.lib.nve_linear_uvm_layer_create(C.byref(h), gpu_table.key_type,
+                                                            C.byref(cfg), gpu_table.handle, None))
+        finally:
+            if heuristic:                       # the layer copied it
+                capi.check(capi.lib.nve_heuristic_destroy(heuristic))
         self.handle = h

@@ -37,6 +37,9 @@ class EmbedLayerConfig:
         self.kernel_mode_value_2 = 0
         self.max_modify_size = 1 << 20
         self.default_row_index = -1
+        # cached layer only: "default" = the reference's default insert heuristic (automatic cache
+        # population, threshold 0.75), "never", or a float threshold
+        self.insert_heuristic = "default"
 
 
 _POOL_NAME = {PoolingType_t.Concatenate: "concatenate", PoolingType_t.Sum: "sum",
@@ -199,7 +202,8 @@ class LinearUVMEmbedding(NVEmbedBinding):
         self._table = GpuTable(gpu_cache_size, row_size * elem, int(data_type), device_id=device_id,
                                uvm_table=_address(memblock), uvm_num_rows=num_embeddings,
                                max_modify_size=config.max_modify_size)
-        layer = LinearUVMEmbeddingLayer(self._table, default_row_index=config.default_row_index)
+        layer = LinearUVMEmbeddingLayer(self._table, default_row_index=config.default_row_index,
+                                        insert_heuristic=getattr(config, "insert_heuristic", "default"))
         super().__init__(layer, row_size, data_type, device_id)
 
     def close(self) -> None:

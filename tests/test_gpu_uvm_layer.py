@@ -105,6 +105,37 @@ def test_layer_rejects_hitmask_and_bad_default_row(torch_cuda):
     ctx.destroy(); layer.destroy(); gt.destroy()
 
 
+@pytest.mark.parametrize("heuristic,expect_hits", [("default", True), (0.5, True), ("never", False)])
+def test_automatic_cache_population(torch_cuda, heuristic, expect_hits):
+    """No explicit insert: with the default heuristic the layer promotes the keys of looked-up
+    batches on its own (hit rate climbs from 0), with the never-insert heuristic the cache stays
+    empty.  Rows are exact either way, whatever is resident at the moment."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GpuTable, LinearUVMEmbeddingLayer
+    rows, dim = 20000, 128
+    table = dg.normal_table(rows, dim, 0.02, 1, np.float16)
+    backing = torch.from_numpy(table).pin_memory()
+    cache_bytes = (4000 // 8) * (64 + 8 * dim * 2 + 32)
+    gt = GpuTable(cache_bytes, dim * 2, "float16", uvm_table=backing, uvm_num_rows=rows)
+    layer = LinearUVMEmbeddingLayer(gt, insert_heuristic=heuristic, min_insert_size_gpu=2000)
+    ctx = layer.create_execution_context()
+    perm = dg.permutation(rows)
+    rates = []
+    for step in range(14):
+        keys = dg.zipf_keys(5000, rows, 1.2, 40 + step, perm)
+        d_keys = to_dev(torch, keys)
+        out = torch.zeros((5000, dim), dtype=torch.float16, device="cuda")
+        rates.append(layer.lookup(ctx, keys.size, d_keys, out, dim * 2, want_hitrate=True))
+        ctx.wait()
+        assert np.array_equal(out.cpu().numpy(), table[keys])
+    assert rates[0] == 0.0
+    if expect_hits:
+        assert max(rates[3:]) > 0.3, rates
+    else:
+        assert max(rates) == 0.0, rates
+    ctx.destroy(); layer.destroy(); gt.destroy()
+
+
 def test_pynve_named_edge(torch_cuda, oracle):
     """GPUEmbedding / LinearUVMEmbedding with raw addresses and stream handles, as pynve passes them."""
     torch = torch_cuda
