@@ -167,7 +167,9 @@ NVE_C_API nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t deduper);
  * grouped by key, ascending inside a group; d_offsets[C+1] chunk starts in the inverse buffer
  * (C == U without splitting); d_loc_map_out[C] group of each chunk (only when splitting);
  * h_num_runs_out[0] = U, [1] = C (host memory, valid on return: the call synchronises `stream`
- * once).  Only the low `end_bit` bits of the keys take part in the ordering (0 = all bits).
+ * once; NULL = no read-back and no synchronisation, for callers whose following kernels take the
+ * counts from nve_b200_deduper_device_num_runs).  Only the low `end_bit` bits of the keys take part
+ * in the ordering (0 = all bits).
  */
 NVE_C_API nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t deduper, const void* d_keys,
                                               int64_t num_keys, void* d_unique_out,

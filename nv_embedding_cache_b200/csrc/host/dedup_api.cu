@@ -89,11 +89,10 @@ nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, in
     NVE_B200_ARG(num_keys >= 0, "negative key count");
     NVE_B200_ARG(num_keys <= d->capacity,
                  "dedup called with more keys than the deduper was created for");
-    NVE_B200_ARG(h_num_runs_out != nullptr, "h_num_runs_out must not be NULL");
     if (end_bit <= 0 || end_bit > kb * 8) end_bit = kb * 8;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (num_keys == 0) {
-      std::memset(h_num_runs_out, 0, size_t(2) * kb);
+      if (h_num_runs_out) std::memset(h_num_runs_out, 0, size_t(2) * kb);
       if (d_offsets) NVE_B200_CUDA(cudaMemsetAsync(d_offsets, 0, kb, s));
       NVE_B200_CUDA(cudaMemsetAsync(const_cast<void*>(nve_b200::dedup_device_num_runs(
                                         d->key_type, d->workspace, d->capacity)),
@@ -107,6 +106,11 @@ nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, in
     nve_b200::dedup_run(d->key_type, d->workspace, d->capacity, d_keys, num_keys, d_unique_out,
                         d_counts_out, d_loc_map_out, d_inverse_buffer, d_offsets, d->max_run,
                         end_bit, d->pinned, s);
+    if (h_num_runs_out == nullptr) {
+      // no host read-back wanted: kernels that follow take {U, C} from the device copy
+      d->last_num_keys = -1;
+      return;
+    }
     NVE_B200_CUDA(cudaStreamSynchronize(s));  // the counts are part of the return value
     std::memcpy(h_num_runs_out, d->pinned, size_t(2) * kb);
     d->last_num_keys = num_keys;

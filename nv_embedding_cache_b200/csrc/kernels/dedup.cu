@@ -324,11 +324,17 @@ constexpr int kGsStages = 4;
 constexpr int kGsWindow = 128;     // positions per warp (default)
 constexpr int kGsMaxRowBytes = 512;
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                   static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-               "l"(gmem_src)
-               : "memory");
+// Shared-memory operands are 32-bit addresses in the shared window (one add per access instead
+// of 64-bit generic pointer arithmetic plus a conversion).
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t smem_src) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(smem_src));
+  return v;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -382,10 +388,13 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   const int total = static_cast<int>(static_cast<int64_t>(offsets[ce]) - p0);
   const uint32_t rb = static_cast<uint32_t>(p.nvec) * 16u;
   const bool col = lane < p.nvec;
-  uint8_t* my_ring = gs_ring + static_cast<size_t>(warp) * kRing * rb + 16u * lane;   // this lane's column
+  // this lane's column of ring slot 0, as an address in the shared window
+  const uint32_t my_ring = static_cast<uint32_t>(__cvta_generic_to_shared(gs_ring)) +
+                           static_cast<uint32_t>(warp) * kRing * rb + 16u * lane;
   // WEIGHTED: one weight per ring slot, behind the rings of the block's warps
   float* wcell = reinterpret_cast<float*>(gs_ring + static_cast<size_t>(kGsWarps) * kRing * rb) + warp * kRing;
   const uint8_t* my_grads = p.grads + 16u * lane;
+  const uint32_t gstride = static_cast<uint32_t>(p.grad_stride);   // checked below 4 GiB by the launcher
 
   // metadata of 32 chunks at a time: lane j holds chunk cw + j
   int64_t cw = cb;
@@ -444,9 +453,11 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
       }
 #pragma unroll
       for (int i = 0; i < kGsBatch; i++) {
-        const int64_t g = static_cast<int64_t>(__shfl_sync(0xffffffffu, row_cur, within + i));
+        // row indices are below 2^31 (the deduper's capacity), so 32 x 32 -> 64 bits addresses a row
+        const uint32_t g = static_cast<uint32_t>(__shfl_sync(0xffffffffu, row_cur, within + i));
         if (col && i < cnt) {
-          cp_async16(my_ring + static_cast<size_t>(slot0 + i) * rb, my_grads + g * p.grad_stride);
+          cp_async16(my_ring + static_cast<uint32_t>(slot0 + i) * rb,
+                     my_grads + static_cast<uint64_t>(g) * gstride);
         }
       }
     }
@@ -512,7 +523,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
       const int first = b * kGsBatch + h;
       const int cnt = min(SUB, cnt_all - h);
       if (cnt <= 0) break;
-      const uint8_t* stage = my_ring + static_cast<size_t>(q * kGsBatch + h) * rb;
+      const uint32_t stage = my_ring + static_cast<uint32_t>(q * kGsBatch + h) * rb;
       const float* wstage = wcell + q * kGsBatch + h;
       int s = 0;
       if (cnt == SUB && cur_end - first >= SUB) {
@@ -521,7 +532,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
           float4 v[SUB];
 #pragma unroll
           for (int i = 0; i < SUB; i++) {
-            v[i] = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(i) * rb);
+            v[i] = lds_f4(stage + static_cast<uint32_t>(i) * rb);
             if constexpr (WEIGHTED) {
               const float w = wstage[i];
               v[i] = make_float4(__fmul_rn(w, v[i].x), __fmul_rn(w, v[i].y), __fmul_rn(w, v[i].z),
@@ -541,7 +552,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
       }
       for (; s < cnt; s++) {
         if (col) {
-          float4 v = *reinterpret_cast<const float4*>(stage + static_cast<size_t>(s) * rb);
+          float4 v = lds_f4(stage + static_cast<uint32_t>(s) * rb);
           if constexpr (WEIGHTED) {
             const float w = wstage[s];
             v = make_float4(__fmul_rn(w, v.x), __fmul_rn(w, v.y), __fmul_rn(w, v.z), __fmul_rn(w, v.w));
@@ -562,7 +573,8 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
 
 bool grad_stream_eligible(const GradParams& p, bool allow) {
   static const bool off = std::getenv("NVE_B200_NO_GRAD_STREAM") != nullptr;
-  return !off && allow && p.nvec >= 1 && p.nvec <= 32 && p.nvec * 16 <= kGsMaxRowBytes;
+  return !off && allow && p.nvec >= 1 && p.nvec <= 32 && p.nvec * 16 <= kGsMaxRowBytes &&
+         p.grad_stride > 0 && p.grad_stride < (int64_t{1} << 32);
 }
 
 template <typename IdxT>

@@ -62,18 +62,17 @@ class CudaStages:
         return torch.cuda.current_stream().cuda_stream
 
     def dedup_and_route(self, keys: torch.Tensor):
-        """-> (num_unique, send_keys[:U], send_counts[W] device tensor)"""
+        """-> (send_keys, send_counts[W]): unique keys grouped by owner (the first sum(send_counts)
+        entries are valid) and how many go to each rank.  Nothing is read back to the host here."""
         n = keys.numel()
-        runs = (C.c_int64 * 2)()
         capi.check(capi.lib.nve_b200_deduper_dedup(
             self.deduper, keys.data_ptr(), n, self.unique.data_ptr(), self.counts.data_ptr(), None,
-            runs, self.inverse.data_ptr(), self.offsets.data_ptr(), self._stream(), 0))
-        u = int(runs[0])
+            None, self.inverse.data_ptr(), self.offsets.data_ptr(), self._stream(), 0))
         capi.check(capi.lib.nve_b200_shard_route(
-            capi.KEY_INT64, self.unique.data_ptr(), self.num_unique_dev, max(u, 1), self.world,
+            capi.KEY_INT64, self.unique.data_ptr(), self.num_unique_dev, max(n, 1), self.world,
             self.send_keys.data_ptr(), self.slot_of_unique.data_ptr(), self.send_counts.data_ptr(),
             self.route_scratch.data_ptr(), self.route_scratch.numel(), self._stream()))
-        return u, self.send_keys[:u], self.send_counts[:self.world]
+        return self.send_keys, self.send_counts[:self.world]
 
     def serve(self, shard: torch.Tensor, recv_keys: torch.Tensor) -> torch.Tensor:
         """Rows of the local shard for the received GLOBAL keys (localised in place)."""
@@ -219,17 +218,22 @@ class ShardedEmbeddingTable:
             return self._lookup_peer(keys, pooling, fixed_hotness, csr_offsets, out)
         n = keys.numel()
         w = self.world
-        u, send_keys, send_counts = self.stages.dedup_and_route(keys)
+        send_keys, send_counts = self.stages.dedup_and_route(keys)
         if w > 1:
             recv_counts = torch.empty_like(send_counts)
             dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-            send_splits, recv_splits = _split_list(send_counts), _split_list(recv_counts)
+            # the one host read-back of a lookup: NCCL takes the split sizes from the host
+            both = _split_list(torch.cat([send_counts, recv_counts]))
+            send_splits, recv_splits = both[:w], both[w:]
+            u = sum(send_splits)
+            send_keys = send_keys[:u]
             recv_keys = torch.empty(sum(recv_splits), dtype=send_keys.dtype, device=send_keys.device)
             dist.all_to_all_single(recv_keys, send_keys.contiguous(), recv_splits, send_splits,
                                    group=self.group)
         else:
+            u = _split_list(send_counts)[0]
             send_splits = recv_splits = [u]
-            recv_keys = send_keys.clone()
+            recv_keys = send_keys[:u].clone()
         served = self.stages.serve(self.shard, recv_keys)
         if w > 1:
             rows = torch.empty((u, self.shard.shape[1]), dtype=self.shard.dtype, device=served.device)

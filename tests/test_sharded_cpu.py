@@ -28,7 +28,7 @@ class HostStages:
         self.slot_of_unique = np.empty_like(order)
         self.slot_of_unique[order] = np.arange(order.size)
         counts = np.bincount(owner, minlength=self.world).astype(np.int64)
-        return self.unique.size, torch.from_numpy(self.unique[order].copy()), torch.from_numpy(counts)
+        return torch.from_numpy(self.unique[order].copy()), torch.from_numpy(counts)
 
     def serve(self, shard, recv_keys):
         local = (recv_keys.numpy().astype(np.uint64) // np.uint64(self.world)).astype(np.int64)
