@@ -60,7 +60,9 @@ typedef struct {
   /* Row-sharded table (optional): HOST array of num_shards device addresses, one per rank, each
    * mapped into this GPU's address space (peer / symmetric memory).  Row r is read from
    * shard_tables[r % num_shards] at local row r / num_shards; `table` is ignored, `num_rows` is
-   * the global row count.  num_shards == 0: plain table.  At most 32 shards. */
+   * the global row count.  num_shards == 0: plain table.  At most 32 shards.  With `cache` set as
+   * well, keys resident in the cache are served from local HBM and only the others are read from
+   * their owner: the reference's arrangement of a GPU cache in front of an NVLink memory block. */
   const void* const* shard_tables;
   int32_t num_shards;
 } nve_b200_pool_args_t;

@@ -98,8 +98,8 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
   NVE_B200_ARG(a.table != nullptr || a.cache != nullptr || a.num_shards > 0,
                "lookup_pool: no table and no cache");
   NVE_B200_ARG(a.num_shards >= 0 && a.num_shards <= kMaxShards, "lookup_pool: at most 32 shards");
-  NVE_B200_ARG(a.num_shards == 0 || (a.shard_tables != nullptr && a.cache == nullptr),
-               "lookup_pool: a sharded table needs shard_tables and no cache");
+  NVE_B200_ARG(a.num_shards == 0 || a.shard_tables != nullptr,
+               "lookup_pool: a sharded table needs shard_tables");
   NVE_B200_ARG(a.output != nullptr, "lookup_pool: output is NULL");
   NVE_B200_ARG(a.pooling_type == NVE_POOL_SUM || a.pooling_type == NVE_POOL_MEAN ||
                    a.pooling_type == NVE_POOL_WEIGHTED_SUM ||

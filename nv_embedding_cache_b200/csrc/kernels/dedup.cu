@@ -52,6 +52,34 @@ __global__ void mark_group_heads_kernel(const KeyT* sorted, uint32_t* head, int6
   if (i < n) head[i] = (i == 0 || sorted[i] != sorted[i - 1]) ? 1u : 0u;
 }
 
+// Packed form of the sort for orderings on at most 32 key bits: (low key bits, position) in one
+// 64-bit word, sorted as keys only, so a radix pass moves 8 bytes per entry instead of a 16-byte
+// (key, position) pair.  `flip` = 0x80000000 gives 32-bit signed keys their signed order.
+template <typename KeyT>
+__global__ void pack_kernel(const KeyT* __restrict__ keys, uint64_t* __restrict__ packed, int64_t n,
+                            uint32_t flip) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) {
+    packed[i] = (static_cast<uint64_t>(static_cast<uint32_t>(keys[i]) ^ flip) << 32) |
+                static_cast<uint32_t>(i);
+  }
+}
+
+// Sorted packed words -> sorted full keys (fetched through the position), the inverse buffer and
+// the group heads (full keys compared, as the run-length encoding does).
+template <typename KeyT>
+__global__ void unpack_heads_kernel(const uint64_t* __restrict__ packed, const KeyT* __restrict__ keys,
+                                    KeyT* __restrict__ sorted, KeyT* __restrict__ inverse,
+                                    uint32_t* __restrict__ head, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t pos = static_cast<uint32_t>(packed[i]);
+  const KeyT k = keys[pos];
+  sorted[i] = k;
+  inverse[i] = static_cast<KeyT>(pos);
+  head[i] = (i == 0 || keys[static_cast<uint32_t>(packed[i - 1])] != k) ? 1u : 0u;
+}
+
 // After rank = exclusive_scan(head): every group head publishes its key and start.
 template <typename KeyT>
 __global__ void emit_groups_kernel(const KeyT* sorted, const uint32_t* head, const uint32_t* rank,
@@ -108,6 +136,7 @@ template <typename KeyT>
 struct Workspace {
   KeyT *sorted, *pos, *group_start, *num_out;
   uint32_t *head, *rank, *chunks, *chunk_base;
+  uint64_t *packed_in, *packed_out;
   void* cub_tmp;
   size_t cub_bytes;
   size_t total;
@@ -132,6 +161,8 @@ Workspace<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
   w.rank = static_cast<uint32_t*>(take(N * 4));
   w.chunks = static_cast<uint32_t*>(take(N * 4));
   w.chunk_base = static_cast<uint32_t*>(take(N * 4));
+  w.packed_in = static_cast<uint64_t*>(take(N * 8));
+  w.packed_out = static_cast<uint64_t*>(take(N * 8));
   w.cub_tmp = take(cub_bytes);
   w.cub_bytes = cub_bytes;
   w.total = off + 256;
@@ -140,12 +171,14 @@ Workspace<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
 
 template <typename KeyT>
 size_t cub_bytes_for(int64_t n) {
-  size_t a = 0, b = 0;
+  size_t a = 0, b = 0, c = 0;
   KeyT* k = nullptr;
   uint32_t* u = nullptr;
+  uint64_t* q = nullptr;
   cub::DeviceRadixSort::SortPairs(nullptr, a, k, k, k, k, static_cast<int>(n));
   cub::DeviceScan::ExclusiveSum(nullptr, b, u, u, static_cast<int>(n));
-  return std::max(a, b);
+  cub::DeviceRadixSort::SortKeys(nullptr, c, q, q, static_cast<int>(n));
+  return std::max(a, std::max(b, c));
 }
 
 template <typename KeyT>
@@ -162,10 +195,19 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
   const int T = 256;
   const int N = static_cast<int>(n);
   size_t tmp = w.cub_bytes;
-  iota_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.pos, n);
-  NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, keys, w.sorted, w.pos, inverse, N,
-                                                0, end_bit, s));
-  mark_group_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, n);
+  if (end_bit <= 32) {
+    const uint32_t flip = (sizeof(KeyT) == 4 && end_bit == 32) ? 0x80000000u : 0u;
+    pack_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(keys, w.packed_in, n, flip);
+    NVE_B200_CUDA(cub::DeviceRadixSort::SortKeys(w.cub_tmp, tmp, w.packed_in, w.packed_out, N, 32,
+                                                 32 + end_bit, s));
+    unpack_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, keys, w.sorted, inverse,
+                                                             w.head, n);
+  } else {
+    iota_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.pos, n);
+    NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, keys, w.sorted, w.pos, inverse, N,
+                                                  0, end_bit, s));
+    mark_group_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, n);
+  }
   tmp = w.cub_bytes;
   NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.head, w.rank, N, s));
   emit_groups_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, w.rank, n, unique,

@@ -5,12 +5,12 @@ namespace nve_b200 {
 
 namespace {
 
-// NVE_B200_DENSE_U (4 or 8) and NVE_B200_POOL_BLOCK (32..128) are tuning knobs.
+// NVE_B200_DENSE_U (2, 4 or 8) and NVE_B200_POOL_BLOCK (32..128) are tuning knobs.
 int dense_unroll() {
   static const int value = [] {
     const char* e = std::getenv("NVE_B200_DENSE_U");
     const int v = e ? std::atoi(e) : 0;
-    return (v == 4 || v == 8) ? v : 4;
+    return (v == 2 || v == 4 || v == 8) ? v : 4;
   }();
   return value;
 }
@@ -48,6 +48,7 @@ void launch_group(const PoolKernelParams& p, cudaStream_t stream) {
 template <In IN>
 void launch_any(const PoolKernelParams& p, cudaStream_t stream) {
   if (dense_unroll() == 8) launch_group<IN, 8>(p, stream);
+  else if (dense_unroll() == 2) launch_group<IN, 2>(p, stream);
   else launch_group<IN, 4>(p, stream);
 }
 

@@ -153,7 +153,7 @@ class ShardedEmbeddingTable:
     POOLING = {"sum": capi.POOL_SUM, "mean": capi.POOL_MEAN}
 
     def __init__(self, local_shard: torch.Tensor, *, max_keys: int, group=None, stages=None,
-                 mode: str = "alltoall"):
+                 mode: str = "alltoall", cache_bytes: int = 0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -172,10 +172,47 @@ class ShardedEmbeddingTable:
             else:
                 ptrs = [local_shard.data_ptr()]
             self._shard_ptrs = (C.c_void_p * len(ptrs))(*ptrs)
+            self._cache = None
+            self.use_cache = True          # set False to bypass the cache without dropping it
+            if cache_bytes > 0:
+                # a local set-associative cache in front of the peer reads (mode="peer" only): rows
+                # it holds are served from this GPU's HBM, the others from their owner over NVLink
+                from .layers import GpuTable
+                row_bytes = local_shard.shape[1] * local_shard.element_size()
+                dt = "float16" if local_shard.dtype == torch.float16 else "float32"
+                self._cache = GpuTable(cache_bytes, row_bytes, dt, max_modify_size=max(max_keys, 1),
+                                       device_id=local_shard.device.index)
+                self._cache_ctx = self._cache.create_execution_context()
+                self._cache_view = capi.CacheData()
+                capi.check(capi.lib.nve_b200_gpu_table_get_cache_data(
+                    self._cache.handle, self._cache_ctx.handle, C.byref(self._cache_view)))
         else:
             self.stages = stages if stages is not None else CudaStages(max_keys, self.world)
 
-    def _lookup_peer(self, keys, pooling, fixed_hotness, csr_offsets, out):
+    def populate_cache(self, keys: torch.Tensor):
+        """Insert the rows of `keys` (global row ids) into the local cache, most frequent first
+        (the cache's replacement policy).  Call between lookups; returns after the insert ran."""
+        if self._cache is None:
+            raise RuntimeError("the table was created without a cache")
+        n = keys.numel()
+        rows = self._lookup_peer(keys, "sum", 1, None, None, use_cache=False)   # one row per key
+        torch.cuda.current_stream().synchronize()
+        row_bytes = self.shard.shape[1] * self.shard.element_size()
+        self._cache.insert(self._cache_ctx, n, keys, row_bytes, row_bytes, rows)
+        self._cache_ctx.wait()
+
+    def cache_misses(self, reset: bool = False) -> int:
+        """Keys not served by the local cache since the counter was last reset (synchronises)."""
+        torch.cuda.current_stream().synchronize()
+        v = C.c_int64(0)
+        capi.check(capi.lib.nve_table_get_lookup_counter(self._cache.handle, self._cache_ctx.handle, C.byref(v)))
+        self._cache_ctx.wait()
+        if reset:
+            capi.check(capi.lib.nve_table_reset_lookup_counter(self._cache.handle, self._cache_ctx.handle))
+            self._cache_ctx.wait()
+        return v.value
+
+    def _lookup_peer(self, keys, pooling, fixed_hotness, csr_offsets, out, use_cache=True):
         n = keys.numel()
         num_bags = (csr_offsets.numel() - 1) if csr_offsets is not None else n // fixed_hotness
         if out is None:
@@ -187,7 +224,8 @@ class ShardedEmbeddingTable:
         a.value_dtype = capi.DTYPE_FLOAT16 if self.shard.dtype == torch.float16 else capi.DTYPE_FLOAT32
         a.row_width = self.shard.shape[1]
         a.default_row_index = -1
-        a.cache = None
+        cached = use_cache and self.use_cache and self._cache is not None
+        a.cache = C.pointer(self._cache_view) if cached else None
         a.key_type = capi.KEY_INT64
         a.keys = keys.data_ptr()
         a.num_keys = n
@@ -208,7 +246,7 @@ class ShardedEmbeddingTable:
             a.table = self.shard.data_ptr()
         capi.check(capi.lib.nve_b200_lookup_pool(C.byref(a), torch.cuda.current_stream().cuda_stream))
         row_bytes = self.shard.shape[1] * self.shard.element_size()
-        self.last_exchange = {"unique": None, "served": None,
+        self.last_exchange = {"unique": None, "served": None, "cached": bool(cached),
                               "nvlink_bytes_in": n * row_bytes * (self.world - 1) // self.world}
         return out
 
@@ -253,3 +291,8 @@ class ShardedEmbeddingTable:
     def close(self):
         if self.stages is not None and hasattr(self.stages, "close"):
             self.stages.close()
+        if getattr(self, "_cache", None) is not None:
+            self._cache_ctx.wait()
+            self._cache_ctx.destroy()
+            self._cache.destroy()
+            self._cache = None

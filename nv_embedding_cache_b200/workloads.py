@@ -267,32 +267,65 @@ def run_c5(root, steps=30, warmup=5, rows_per_rank=250_000_000, dim=64, bags=131
     _fill_rows_fp16(shard, 60 + rank)
     total = rows_per_rank * world
     n = bags * hot
-    t = ShardedEmbeddingTable(shard, max_keys=n, mode=mode)
+    # peer mode, optionally with a local cache in front of the peer reads: NVE_B200_C5_CACHE_FRAC is the
+    # cache size as a fraction of the local shard's bytes (0 = no cache; the cached run is reported
+    # beside the uncached one)
+    cache_frac = float(os.environ.get("NVE_B200_C5_CACHE_FRAC", "0")) if mode == "peer" else 0.0
+    row_bytes = dim * 2
+    t = ShardedEmbeddingTable(shard, max_keys=n, mode=mode,
+                              cache_bytes=int(rows_per_rank * cache_frac) * row_bytes)
     batches = [torch.from_numpy(dg.zipf_keys(n, total, 1.05, 600 + 10 * b + rank)).cuda() for b in range(4)]
     out = torch.empty((bags, dim), dtype=torch.float16, device="cuda")
 
     def step(i):
         t.lookup_pooled(batches[i % 4], "sum", fixed_hotness=hot, out=out)
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(steps):
-        step(warmup + i)
-    e1.record(stream)
-    torch.cuda.synchronize()
-    sec = torch.tensor([e0.elapsed_time(e1) * 1e-3 / steps], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(sec, op=dist.ReduceOp.MAX)
-    sec = float(sec.item())
-    ex = t.last_exchange
+
+    def timed():
+        for i in range(warmup):
+            step(i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            step(warmup + i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        sec = torch.tensor([e0.elapsed_time(e1) * 1e-3 / steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+        return float(sec.item())
+
+    if cache_frac > 0:
+        t.use_cache = False
+    sec = timed()
+    ex = dict(t.last_exchange)
+    res = {"workload": "C5 sharded table: 250M x W rows x 64 fp16, 131072 bags x 8 per rank, Zipf(1.05), sum",
+           "mode": mode, "n_gpus": world, "keys_per_s": n * world / sec, "ms_per_step": sec * 1e3,
+           "unique_per_rank": ex.get("unique"), "served_per_rank": ex.get("served"),
+           "nvlink_gbs_per_rank": (ex.get("nvlink_bytes_out") or ex.get("nvlink_bytes_in") or 0) / sec / 1e9,
+           "scaling": "weak"}
+    if cache_frac > 0:
+        for b in range(12):                                   # explicit, deterministic warm-up of the cache
+            k = torch.from_numpy(dg.zipf_keys(n, total, 1.05, 700 + 10 * b + rank)).cuda()
+            t.populate_cache(k)
+        t.use_cache = True
+        ref_out = out.clone()
+        t.use_cache = False
+        step(0)
+        torch.cuda.synchronize()
+        ref_out.copy_(out)
+        t.use_cache = True
+        t.cache_misses(reset=True)
+        step(0)
+        misses = t.cache_misses(reset=True)
+        same = bool(torch.equal(out, ref_out))
+        sec_c = timed()
+        hit = 1.0 - misses / n
+        res["with_cache"] = {"cache_frac_of_shard": cache_frac, "hit_rate": hit, "same_output": same,
+                             "keys_per_s": n * world / sec_c, "ms_per_step": sec_c * 1e3,
+                             "nvlink_gbs_per_rank": misses * row_bytes * (world - 1) / max(world, 1) / sec_c / 1e9}
     t.close()
-    return {"workload": "C5 sharded table: 250M x W rows x 64 fp16, 131072 bags x 8 per rank, Zipf(1.05), sum",
-            "mode": mode, "n_gpus": world, "keys_per_s": n * world / sec, "ms_per_step": sec * 1e3,
-            "unique_per_rank": ex.get("unique"), "served_per_rank": ex.get("served"),
-            "nvlink_gbs_per_rank": (ex.get("nvlink_bytes_out") or ex.get("nvlink_bytes_in") or 0) / sec / 1e9,
-            "scaling": "weak"}
+    return res

@@ -86,20 +86,32 @@ rows_per_rank, dim = 40000, 64
 total = rows_per_rank * world
 table = dg.dyadic_table(total, dim, 3, np.float16)
 mode = os.environ.get("NVE_TEST_SHARD_MODE", "alltoall")
-if mode == "peer":
+if mode.startswith("peer"):
     from nv_embedding_cache_b200.sharded import allocate_symmetric_shard
     shard = allocate_symmetric_shard(rows_per_rank, dim, torch.float16)
     shard.copy_(torch.from_numpy(table[rank::world].copy()))
 else:
     shard = torch.from_numpy(table[rank::world].copy()).cuda()
-t = ShardedEmbeddingTable(shard, max_keys=1 << 16, mode=mode)
+cached = mode == "peer_cached"
+if cached:
+    mode = "peer"
+t = ShardedEmbeddingTable(shard, max_keys=1 << 16, mode=mode,
+                          cache_bytes=(2000 // 8) * (64 + 8 * dim * 2 + 32) if cached else 0)
 ok = True
+hits = 0
 for step in range(3):
     keys = dg.zipf_keys(2048 * 8, total, 1.05, 100 + 10 * step + rank, dg.permutation(total))
+    if cached:      # rows of an earlier batch are resident: some keys are served locally, results identical
+        t.populate_cache(torch.from_numpy(dg.zipf_keys(4096, total, 1.05, 50 + step + rank, dg.permutation(total))).cuda())
+        t.cache_misses(reset=True)
     out = t.lookup_pooled(torch.from_numpy(keys).cuda(), "sum", fixed_hotness=8)
     torch.cuda.synchronize()
+    if cached:
+        hits += keys.size - t.cache_misses(reset=True)
     want = table[keys].astype(np.float32).reshape(2048, 8, dim).sum(1).astype(np.float16)
     ok = ok and bool(np.array_equal(out.cpu().numpy(), want))
+if cached:
+    ok = ok and hits > 1000
 flag = torch.tensor([1 if ok else 0], device="cuda")
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 t.close()
@@ -109,7 +121,7 @@ sys.exit(0 if int(flag.item()) == 1 else 3)
 '''
 
 
-@pytest.mark.parametrize("mode", ["alltoall", "peer"])
+@pytest.mark.parametrize("mode", ["alltoall", "peer", "peer_cached"])
 def test_two_ranks_nccl(torch_cuda, tmp_path, mode):
     torch = torch_cuda
     if torch.cuda.device_count() < 2:
