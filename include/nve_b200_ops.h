@@ -198,6 +198,19 @@ NVE_C_API nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t deduper, const vo
                                             void* stream);
 
 /*
+ * nve_b200_dedup_grads for fp16 gradient rows (row_bytes = 2 * width, a multiple of 16): the rows of
+ * a group are added in fp16, one rounding per addition, in ascending position and chunk order,
+ * which is what the reference's half accumulators do (cuda_ops/dedup_grads_kernel.cuh:56-109 with
+ * DataType = half vectors, cuda_ops/kernels_common.cuh:340-371).  Sums go to d_dst[u]; the fused
+ * table update is fp32 only.
+ */
+NVE_C_API nve_status_t nve_b200_dedup_grads_f16(nve_b200_deduper_t deduper, const void* d_grads,
+                                                int64_t grad_stride, int64_t row_bytes,
+                                                int64_t num_keys, const void* d_inverse,
+                                                const void* d_offsets, const void* d_loc_map,
+                                                void* d_dst, int64_t dst_stride, void* stream);
+
+/*
  * Backward of a pooled lookup in one call (replaces GradientCalculator::compute_gradients, pooling
  * branch, cuda_ops/gradient_calculator.cuh:85-180,254-286, which the Python binding exposes as
  * pooling_backprop): de-duplicates the keys of the batch and writes, for unique key u,
@@ -282,6 +295,17 @@ NVE_C_API nve_status_t nve_b200_shard_expand_slots(nve_key_type_t key_type, cons
                                                    const void* d_slot_of_unique,
                                                    const void* d_num_unique, int64_t n,
                                                    void* d_slot_of_position, void* stream);
+
+/*
+ * Masked row copy, the merge step of a multi-tier lookup: d_dst[i] = d_src[i] (row_bytes each) for
+ * every position i < num_rows whose bit in d_hit_mask is 0; positions whose bit is 1 were served by
+ * an earlier tier and keep their rows.  d_hit_mask NULL copies every row.  Replaces
+ * EmbeddingForwardScatter (cuda_ops/scatter.cuh:29-140), which the reference's hierarchical layer
+ * uses between its GPU cache tier and the tiers behind it.
+ */
+NVE_C_API nve_status_t nve_b200_scatter_rows(const void* d_src, int64_t src_stride, void* d_dst,
+                                             int64_t dst_stride, int64_t row_bytes,
+                                             const uint64_t* d_hit_mask, int64_t num_rows, void* stream);
 
 /*
  * Host-resident table memory that GPU kernels read in place (the backing table of the cached

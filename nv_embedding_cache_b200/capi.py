@@ -162,8 +162,10 @@ PROTOTYPES = {
                                             _vp, _vp, _i64, _i32, _i64, C.c_float, _vp]),
     "nve_b200_update_rows": (_i32, [_vp, _i64, _i64, _i32, _i64, C.c_int, _vp, _i64, _vp, _i64,
                                      C.c_int, C.c_int, _vp]),
+    "nve_b200_dedup_grads_f16": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),
     "nve_b200_pooling_backprop": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, C.c_int, C.c_int, _vp, _i64, _i64,
                                           _vp, _vp, _vp, _i64, C.POINTER(_i64), _vp]),
+    "nve_b200_scatter_rows": (_i32, [_vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp]),
     "nve_b200_managed_block_create": (_i32, [C.POINTER(_vp), _u64, C.POINTER(_i32), _i32]),
     "nve_b200_managed_block_destroy": (_i32, [_vp]),
 }

@@ -143,7 +143,30 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, /*pos_weight=*/nullptr, static_cast<cudaStream_t>(stream));
+        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/false, static_cast<cudaStream_t>(stream));
+  });
+}
+
+nve_status_t nve_b200_dedup_grads_f16(nve_b200_deduper_t d, const void* d_grads, int64_t grad_stride,
+                                      int64_t row_bytes, int64_t num_keys, const void* d_inverse,
+                                      const void* d_offsets, const void* d_loc_map, void* d_dst,
+                                      int64_t dst_stride, void* stream) {
+  if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
+  return guarded([&] {
+    if (num_keys <= 0) return;
+    NVE_B200_ARG(d_grads && d_inverse && d_offsets && d_dst, "dedup_grads_f16: NULL buffer");
+    NVE_B200_ARG(d->max_run <= 0 || d_loc_map != nullptr,
+                 "dedup_grads_f16: the chunk map is required when runs are split");
+    nve_b200::ensure_partial(d, num_keys, row_bytes);
+    int64_t max_chunks = d->max_run > 0 ? num_keys + num_keys / d->max_run + 1 : num_keys;
+    if (d->last_num_keys == num_keys && d->last_chunks > 0) max_chunks = d->last_chunks;
+    nve_b200::dedup_grads_run(
+        d->key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
+        d->max_run > 0 ? d_loc_map : nullptr, nullptr,
+        nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
+        dst_stride, /*fused=*/false, 0, 1.0f, d->partial,
+        d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
+        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/true, static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -217,7 +240,7 @@ nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, c
         d->max_run > 0 ? loc_map : nullptr, d_unique_out, num_runs, max_chunks, d_grads_out, out_stride,
         /*fused=*/false, 0, 1.0f, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, need_w ? pos_w : nullptr, s);
+        /*streamed=*/true, need_w ? pos_w : nullptr, /*f16=*/false, s);
     NVE_B200_CUDA(cudaStreamSynchronize(s));   // the number of unique keys is part of the return value
     *h_num_unique = kb == 8 ? static_cast<const int64_t*>(d->pinned)[0]
                             : static_cast<const int32_t*>(d->pinned)[0];

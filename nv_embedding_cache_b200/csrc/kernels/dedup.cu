@@ -245,7 +245,25 @@ struct GradParams {
   int32_t nvec;              // float4 vectors per row
   bool idx64;
   bool fused;
+  bool f16;                  // rows hold fp16 values, added in fp16 (un-fused, un-weighted form only)
 };
+
+// acc += v for one 16-byte vector of a gradient row: four fp32 values, or eight fp16 values added
+// in fp16 (one rounding per addition, the arithmetic of the reference's half accumulators,
+// cuda_ops/kernels_common.cuh:365-371).  An all-zero vector is zero in both readings.
+__device__ __forceinline__ void add_vec16(float4& acc, const float4& v, bool f16) {
+  if (f16) {
+    __half2* a = reinterpret_cast<__half2*>(&acc);
+    const __half2* b = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) a[i] = __hadd2(a[i], b[i]);
+  } else {
+    acc.x = __fadd_rn(acc.x, v.x);
+    acc.y = __fadd_rn(acc.y, v.y);
+    acc.z = __fadd_rn(acc.z, v.z);
+    acc.w = __fadd_rn(acc.w, v.w);
+  }
+}
 
 __device__ __forceinline__ int64_t ld_idx(const void* p, bool is64, int64_t i) {
   return is64 ? reinterpret_cast<const int64_t*>(p)[i]
@@ -310,10 +328,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
                 r[k].z = __fmul_rn(w[k], r[k].z);
                 r[k].w = __fmul_rn(w[k], r[k].w);
               }
-              acc.x = __fadd_rn(acc.x, r[k].x);
-              acc.y = __fadd_rn(acc.y, r[k].y);
-              acc.z = __fadd_rn(acc.z, r[k].z);
-              acc.w = __fadd_rn(acc.w, r[k].w);
+              add_vec16(acc, r[k], p.f16);
             }
           }
         }
@@ -583,10 +598,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
           }
 #pragma unroll
           for (int i = 0; i < SUB; i++) {
-            acc.x = __fadd_rn(acc.x, v[i].x);
-            acc.y = __fadd_rn(acc.y, v[i].y);
-            acc.z = __fadd_rn(acc.z, v[i].z);
-            acc.w = __fadd_rn(acc.w, v[i].w);
+            add_vec16(acc, v[i], p.f16);
           }
         }
         s = SUB;
@@ -599,10 +611,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
             const float w = wstage[s];
             v = make_float4(__fmul_rn(w, v.x), __fmul_rn(w, v.y), __fmul_rn(w, v.z), __fmul_rn(w, v.w));
           }
-          acc.x = __fadd_rn(acc.x, v.x);
-          acc.y = __fadd_rn(acc.y, v.y);
-          acc.z = __fadd_rn(acc.z, v.z);
-          acc.w = __fadd_rn(acc.w, v.w);
+          add_vec16(acc, v, p.f16);
         }
         if (first + s + 1 == cur_end) finish_chunk();
       }
@@ -681,10 +690,7 @@ __global__ void __launch_bounds__(128) grad_finish_kernel(const GradParams p) {
         if (slot < p.partial_rows) {
           const float4 r =
               reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
-          acc.x = __fadd_rn(acc.x, r.x);
-          acc.y = __fadd_rn(acc.y, r.y);
-          acc.z = __fadd_rn(acc.z, r.z);
-          acc.w = __fadd_rn(acc.w, r.w);
+          add_vec16(acc, r, p.f16);
         }
       }
       if (p.fused) {
@@ -830,7 +836,10 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     int64_t num_keys, bool streamed, const float* pos_weight, cudaStream_t stream) {
+                     int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
+                     cudaStream_t stream) {
+  NVE_B200_ARG(!f16 || (!fused && pos_weight == nullptr),
+               "dedup_grads: fp16 gradients are summed un-weighted into a gradient buffer only");
   NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
   NVE_B200_ARG(grad_stride % 16 == 0 && dst_stride % 16 == 0 &&
                    reinterpret_cast<uint64_t>(grads) % 16 == 0 &&
@@ -855,6 +864,7 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   p.nvec = static_cast<int32_t>(row_bytes / 16);
   p.idx64 = key_type == NVE_KEY_INT64;
   p.fused = fused;
+  p.f16 = f16;
   if (grad_stream_eligible(p, streamed)) {
     if (p.idx64) launch_grad_stream<int64_t>(p, num_keys, stream);
     else launch_grad_stream<int32_t>(p, num_keys, stream);
@@ -932,6 +942,7 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
     dedup_grads_run(key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,
                     max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
                     dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
-                    num_keys, /*streamed=*/false, /*pos_weight=*/nullptr, static_cast<cudaStream_t>(stream));
+                    num_keys, /*streamed=*/false, /*pos_weight=*/nullptr, /*f16=*/false,
+                    static_cast<cudaStream_t>(stream));
   });
 }

@@ -18,7 +18,7 @@ const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int6
 
 // dst[u] = sum of grads rows of group u (fused == false), or
 // table[unique[u]] += alpha * sum (fused == true; dst is the table, keys outside
-// [0, table_rows) are skipped).  fp32 rows, 16-byte aligned.
+// [0, table_rows) are skipped).  fp32 rows (or, with f16, fp16 rows added in fp16), 16-byte aligned.
 // pos_weight: optional weight per position of `inverse`: rows are multiplied by it before they are
 // added (one rounding each: multiply, then add).
 // streamed: let rows of up to 512 bytes take the first pass that streams them through shared
@@ -28,7 +28,8 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      const void* loc_map, const void* unique, const void* num_runs_dev,
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
-                     int64_t num_keys, bool streamed, const float* pos_weight, cudaStream_t stream);
+                     int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
+                     cudaStream_t stream);
 
 // Pooled backward, preparation: for every sorted position q of a dedup() result, src_row[q] = the
 // bag its key came from (CSR offsets of the key type, or fixed hotness when csr == null) and, when

@@ -110,14 +110,18 @@ class NVEmbedBinding:
         """Backward of an un-pooled lookup: unique keys and the per-key sum of the incoming
         gradient rows.  Returns the number of unique keys (binding_layers.hpp:131-189).
         Scratch (inverse map, offsets, chunk map) is owned by this object and grows on demand."""
-        if self._dtype != DataType_t.Float32:
-            raise NotImplementedError("concat_backprop is provided for Float32 gradients")
         self._ensure_deduper(num_keys)
         s = stream or None
         capi.check(capi.lib.nve_b200_deduper_dedup(
             self._deduper, keys, num_keys, unique_keys, self._counts.data_ptr(),
             self._loc_map.data_ptr(), self._runs, self._inverse.data_ptr(), self._offsets.data_ptr(),
             s, 0))
+        if self._dtype != DataType_t.Float32:        # fp16 rows: added in fp16, as the reference does
+            capi.check(capi.lib.nve_b200_dedup_grads_f16(
+                self._deduper, grads, self._row_bytes, self._row_bytes, num_keys,
+                self._inverse.data_ptr(), self._offsets.data_ptr(), self._loc_map.data_ptr(),
+                output_grads, self._row_bytes, s))
+            return int(self._runs[0])
         capi.check(capi.lib.nve_b200_dedup_grads(
             self._deduper, grads, self._row_bytes, self._row_bytes, num_keys, unique_keys,
             self._inverse.data_ptr(), self._offsets.data_ptr(), self._loc_map.data_ptr(),

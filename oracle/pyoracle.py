@@ -388,6 +388,7 @@ class ReferenceGpu:
             "refgpu_deduper_destroy": [_vp],
             "refgpu_deduper_dedup": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
             "refgpu_dedup_grads": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
+            "refgpu_dedup_grads_f16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
             "refgpu_dedup_grads_timed": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                          C.POINTER(f32)],
             "refgpu_pooling_backprop": [_vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(_i64)],
@@ -509,6 +510,12 @@ class RefGpuDeduper:
                                                          loc_map_ptr, runs.ctypes.data, inverse_ptr,
                                                          offsets_ptr, end_bit))
         return int(runs[0]), int(runs[1])
+
+    def grads_f16(self, grads_ptr, out_ptr, unique_ptr, inverse_ptr, loc_map_ptr, offsets_ptr, num_unique,
+                  num_chunks, width):
+        runs = np.array([num_unique, num_chunks], np.int64)
+        self.ref.check(self.ref.lib.refgpu_dedup_grads_f16(grads_ptr, out_ptr, unique_ptr, inverse_ptr,
+                                                           loc_map_ptr, offsets_ptr, runs.ctypes.data, width))
 
     def grads(self, grads_ptr, out_ptr, unique_ptr, inverse_ptr, loc_map_ptr, offsets_ptr, num_unique,
               num_chunks, width, warmup=0, iters=0):

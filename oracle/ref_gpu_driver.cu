@@ -444,4 +444,16 @@ int refgpu_pooling_backprop(const int64_t* d_keys, int64_t n, const int64_t* d_c
   });
 }
 
+// fp16 gradient rows, summed by the reference in fp16 (CallComputeGradients<int64_t, __half>).
+int refgpu_dedup_grads_f16(const void* d_grads, void* d_unique_grads, const int64_t* d_unique,
+                           const int64_t* d_inverse, const int64_t* d_loc_map, const int64_t* d_offsets,
+                           const int64_t* h_num_runs, int width) {
+  return guarded([&] {
+    CallComputeGradients<Key, __half>(static_cast<const __half*>(d_grads), static_cast<__half*>(d_unique_grads),
+                                      d_unique, d_inverse, d_loc_map, d_offsets, h_num_runs,
+                                      static_cast<uint32_t>(width), 0);
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
 }  // extern "C"

@@ -172,3 +172,41 @@ def test_update_and_accumulate_write_through(torch_cuda, oracle, dtype, npdt):
     gpu.find(np.arange(rows, dtype=np.int64), out)
     assert np.array_equal(out, hb)
     gpu.close()
+
+
+def test_two_tier_lookup_with_scatter_merge(torch_cuda, oracle):
+    """GPU-tier glue of a multi-tier lookup: the cache serves its hits and reports the hit mask, a
+    slower tier (here: the host table, indexed like the batch) resolves every position, and
+    nve_b200_scatter_rows merges only the positions the cache missed.  The result is the table's
+    rows; hit positions must come from the cache (they are poisoned in the staging buffer)."""
+    import ctypes as C
+    from nv_embedding_cache_b200 import capi
+    from nve_helpers import to_dev
+    torch = torch_cuda
+    rows, n = 4000, 3000
+    t = table(rows, seed=21)
+    gpu = CacheTable(64 * per_set(), ROW, key_dtype=np.int64)
+    warm = dg.zipf_keys(2000, rows, 1.2, 31, dg.permutation(rows))
+    gpu.insert(warm, t[warm])
+    keys = dg.zipf_keys(n, rows, 1.2, 32, dg.permutation(rows))
+    out = np.zeros((n, ROW), np.uint8)
+    mask = np.zeros((n + 63) // 64, np.uint64)
+    misses = gpu.find(keys, out, mask)
+    bits = ((mask[np.arange(n) // 64] >> (np.arange(n) % 64).astype(np.uint64)) & np.uint64(1)).astype(bool)
+    assert 0 < misses < n and int((~bits).sum()) == misses
+    staged = t[keys].copy()
+    staged[bits] = 0xEE                      # a wrong row wherever the cache already answered
+    d_out, d_staged, d_mask = to_dev(torch, out), to_dev(torch, staged), to_dev(torch, mask.view(np.int64))
+    capi.check(capi.lib.nve_b200_scatter_rows(d_staged.data_ptr(), ROW, d_out.data_ptr(), ROW, ROW,
+                                              d_mask.data_ptr(), n, None))
+    torch.cuda.synchronize()
+    assert np.array_equal(d_out.cpu().numpy(), t[keys])
+    # odd row size and strides: the narrow copy paths
+    src = np.random.default_rng(5).integers(0, 256, (50, 23), dtype=np.uint8)
+    d_src = to_dev(torch, src)
+    d_dst = torch.zeros((50, 29), dtype=torch.uint8, device="cuda")
+    capi.check(capi.lib.nve_b200_scatter_rows(d_src.data_ptr(), 23, d_dst.data_ptr(), 29, 21, None, 50, None))
+    torch.cuda.synchronize()
+    got = d_dst.cpu().numpy()
+    assert np.array_equal(got[:, :21], src[:, :21]) and not got[:, 21:].any()
+    gpu.close()

@@ -225,6 +225,54 @@ def test_gradient_sums(torch_cuda, reference_gpu, max_run, width):
     rd.close()
 
 
+@pytest.mark.parametrize("max_run", [-1, 1024])
+def test_gradient_sums_fp16(torch_cuda, reference_gpu, max_run):
+    """fp16 gradient rows are added in fp16, in position order: un-split groups are bit-identical to
+    the reference kernel and to a one-rounding-per-addition evaluation on the host; split groups
+    (half atomics in the reference, any order) within fp16 accumulation error."""
+    torch = torch_cuda
+    n, rows, width = 30000, 2500, 64
+    keys = dg.zipf_keys(n, rows, 1.05, 15, dg.permutation(rows))
+    keys[::4] = keys[0]
+    k_dev = to_dev(torch, keys)
+    b = dedup_buffers(torch, n, max_run)
+    rd = RefGpuDeduper(reference_gpu, max_run, n)
+    u, c = rd.dedup(k_dev.data_ptr(), n, b["unique"].data_ptr(), b["counts"].data_ptr(),
+                    b["loc_map"].data_ptr(), b["inverse"].data_ptr(), b["offsets"].data_ptr())
+    md = MyDeduper(max_run, n)
+    a = dedup_buffers(torch, n, max_run)
+    runs = np.zeros(2, np.int64)
+    capi.check(capi.lib.nve_b200_deduper_dedup(md.h, k_dev.data_ptr(), n, a["unique"].data_ptr(),
+                                               a["counts"].data_ptr(), a["loc_map"].data_ptr(),
+                                               runs.ctypes.data, a["inverse"].data_ptr(),
+                                               a["offsets"].data_ptr(), None, 0))
+    grads_np = np.random.default_rng(3).normal(0, 0.05, (n, width)).astype(np.float16)
+    g = to_dev(torch, grads_np)
+    want = torch.zeros((u, width), dtype=torch.float16, device="cuda")
+    rd.grads_f16(g.data_ptr(), want.data_ptr(), b["unique"].data_ptr(), b["inverse"].data_ptr(),
+                 b["loc_map"].data_ptr() if max_run > 0 else None, b["offsets"].data_ptr(), u, c, width)
+    got = torch.full((u, width), 5.0, dtype=torch.float16, device="cuda")
+    capi.check(capi.lib.nve_b200_dedup_grads_f16(md.h, g.data_ptr(), width * 2, width * 2, n,
+                                                 a["inverse"].data_ptr(), a["offsets"].data_ptr(),
+                                                 a["loc_map"].data_ptr(), got.data_ptr(), width * 2, None))
+    torch.cuda.synchronize()
+    got_np, want_np = got.cpu().numpy(), want.cpu().numpy()
+    counts = b["counts"][:u].cpu().numpy()
+    short = counts <= 1024 if max_run > 0 else np.ones(u, bool)
+    assert np.array_equal(got_np[short], want_np[short])
+    assert np.max(np.abs(got_np.astype(np.float32) - want_np.astype(np.float32))) <= 0.25
+    # host evaluation, one fp16 rounding per addition, for a sample of short groups
+    inv, offs = a["inverse"][:n].cpu().numpy(), a["offsets"][:c + 1].cpu().numpy()
+    if max_run == -1:
+        for grp in list(range(0, u, max(1, u // 40)))[:40]:
+            acc = np.zeros(width, np.float16)
+            for pos in inv[offs[grp]:offs[grp + 1]]:
+                acc = (acc.astype(np.float64) + grads_np[pos].astype(np.float64)).astype(np.float16)
+            assert np.array_equal(acc, got_np[grp]), grp
+    md.close()
+    rd.close()
+
+
 def test_pooled_lookup_fp16(torch_cuda, reference_gpu):
     """fp16 rows: CSR bags with mean pooling and fixed-hotness sum pooling against the reference's
     find_and_combine kernel reading the table directly."""
