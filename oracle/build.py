@@ -23,7 +23,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REFERENCE = Path(os.environ.get("NVE_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: NVE_REFERENCE_DIR, else a directory named "reference" beside this repository
+REFERENCE = Path(os.environ.get("NVE_REFERENCE_DIR", str(HERE.parents[1] / "reference")))
 
 REF_SOURCES = [
     "host_embedding_layer", "linear_host_table", "host_table", "host_table_detail", "table",
