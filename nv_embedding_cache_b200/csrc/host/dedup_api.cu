@@ -22,6 +22,7 @@ struct nve_b200_deduper_s {
   void* bp_arrays = nullptr;
   int64_t bp_bags = 0;
   float* bp_bag_sum = nullptr;
+  void* heavy = nullptr;       // scratch of the block-per-chunk gradient kernel
 };
 
 namespace nve_b200 {
@@ -63,6 +64,7 @@ nve_status_t nve_b200_deduper_create(nve_b200_deduper_t* out, nve_key_type_t key
     NVE_B200_CUDA(cudaGetDevice(&d->device));
     NVE_B200_CUDA(cudaMalloc(&d->workspace, nve_b200::dedup_workspace_bytes(key_type, max_keys)));
     NVE_B200_CUDA(cudaMallocHost(&d->pinned, 16));
+    NVE_B200_CUDA(cudaMalloc(&d->heavy, nve_b200::grad_heavy_scratch_bytes(max_keys)));
     *out = d.release();
   });
 }
@@ -72,6 +74,7 @@ nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t d) {
   (void)cudaFree(d->workspace);
   (void)cudaFreeHost(d->pinned);
   if (d->partial) (void)cudaFree(d->partial);
+  if (d->heavy) (void)cudaFree(d->heavy);
   if (d->bp_arrays) (void)cudaFree(d->bp_arrays);
   if (d->bp_bag_sum) (void)cudaFree(d->bp_bag_sum);
   (void)cudaGetLastError();
@@ -143,7 +146,8 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/false, static_cast<cudaStream_t>(stream));
+        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/false, d->heavy,
+        nve_b200::grad_heavy_capacity(d->capacity), static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -166,7 +170,8 @@ nve_status_t nve_b200_dedup_grads_f16(nve_b200_deduper_t d, const void* d_grads,
         nve_b200::dedup_device_num_runs(d->key_type, d->workspace, d->capacity), max_chunks, d_dst,
         dst_stride, /*fused=*/false, 0, 1.0f, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/true, static_cast<cudaStream_t>(stream));
+        /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/true, d->heavy,
+        nve_b200::grad_heavy_capacity(d->capacity), static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -240,7 +245,8 @@ nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, c
         d->max_run > 0 ? loc_map : nullptr, d_unique_out, num_runs, max_chunks, d_grads_out, out_stride,
         /*fused=*/false, 0, 1.0f, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
-        /*streamed=*/true, need_w ? pos_w : nullptr, /*f16=*/false, s);
+        /*streamed=*/true, need_w ? pos_w : nullptr, /*f16=*/false, d->heavy,
+        nve_b200::grad_heavy_capacity(d->capacity), s);
     NVE_B200_CUDA(cudaStreamSynchronize(s));   // the number of unique keys is part of the return value
     *h_num_unique = kb == 8 ? static_cast<const int64_t*>(d->pinned)[0]
                             : static_cast<const int32_t*>(d->pinned)[0];

@@ -243,6 +243,10 @@ struct GradParams {
   int64_t partial_rows;
   float alpha;
   int32_t nvec;              // float4 vectors per row
+  void* heavy_list;          // chunks longer than heavy_threshold, deferred by the streamed pass (index type)
+  int32_t heavy_threshold;
+  unsigned long long* heavy_count;
+  int64_t heavy_capacity;
   bool idx64;
   bool fused;
   bool f16;                  // rows hold fp16 values, added in fp16 (un-fused, un-weighted form only)
@@ -380,6 +384,10 @@ constexpr int kGsStages = 4;
 // rows per stage: a template parameter (4 or 8); the ring holds kGsStages * BATCH rows
 constexpr int kGsWindow = 128;     // positions per warp (default)
 constexpr int kGsMaxRowBytes = 512;
+constexpr int kHvThreshold = 128;  // chunks with more rows than this (or NVE_B200_GRAD_HEAVY) go to grad_heavy_kernel
+constexpr int kHvWarps = 4;
+constexpr int kHvStages = 4;
+constexpr int kHvBatch = 16;       // rows per stage: kHvBatch / kHvWarps copies per warp and stage
 
 // Shared-memory operands are 32-bit addresses in the shared window (one add per access instead
 // of 64-bit generic pointer arithmetic plus a conversion).
@@ -438,8 +446,20 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   const int64_t t0 = (static_cast<int64_t>(blockIdx.x) * kGsWarps + warp) * window;
   if (t0 >= n) return;
   const int64_t cb = first_chunk_from(offsets, C, t0, lane);
-  const int64_t ce = first_chunk_from(offsets, C, min(t0 + window, n), lane);
+  int64_t ce = first_chunk_from(offsets, C, min(t0 + window, n), lane);
   if (cb >= ce) return;
+  // Only the last chunk that starts in the window can reach beyond it.  When it is long it is left
+  // to grad_heavy_kernel, where a whole block streams it (one warp moves about 5 rows per
+  // microsecond whatever the ring depth: the copy instructions of a warp issue ~140 cycles apart).
+  if (p.heavy_list != nullptr &&
+      static_cast<int64_t>(offsets[ce]) - static_cast<int64_t>(offsets[ce - 1]) > p.heavy_threshold) {
+    if (lane == 0) {
+      const unsigned long long at = atomicAdd(p.heavy_count, 1ull);
+      if (static_cast<int64_t>(at) < p.heavy_capacity) static_cast<IdxT*>(p.heavy_list)[at] = static_cast<IdxT>(ce - 1);
+    }
+    ce -= 1;
+    if (cb >= ce) return;
+  }
 
   const int64_t p0 = offsets[cb];
   const int total = static_cast<int>(static_cast<int64_t>(offsets[ce]) - p0);
@@ -622,6 +642,138 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   cp_async_wait<0>();
 }
 
+// ---- long chunks: one block per chunk ---------------------------------------------------------
+// A chunk must be added in position order, so it cannot be split over tasks; what can be shared is
+// the fetching.  The kHvWarps warps of a block copy alternating rows of the chunk into a common
+// ring (each warp's copy instructions issue in parallel with the others'), a block barrier makes
+// a stage visible, then thread t adds word t of every row of the stage in order (a row of 512
+// bytes is 128 words for 128 threads; fp16 rows add both halves of the word in fp16).  Same
+// arithmetic and order as the other forms.
+template <typename IdxT, bool WEIGHTED>
+__global__ void __launch_bounds__(kHvWarps * 32) grad_heavy_kernel(const GradParams p) {
+  extern __shared__ __align__(128) uint8_t hv_ring[];
+  constexpr int kRing = kHvStages * kHvBatch;
+  constexpr int kPerWarp = kHvBatch / kHvWarps;     // copies per warp and stage
+  const unsigned long long listed = *p.heavy_count;
+  if (blockIdx.x >= listed || static_cast<int64_t>(blockIdx.x) >= p.heavy_capacity) return;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const IdxT* __restrict__ offsets = static_cast<const IdxT*>(p.offsets);
+  const IdxT* __restrict__ inverse = static_cast<const IdxT*>(p.inverse);
+  const IdxT* __restrict__ loc_map = static_cast<const IdxT*>(p.loc_map);
+  const int64_t C = static_cast<const IdxT*>(p.num_runs_dev)[1];
+  const int64_t c = static_cast<int64_t>(static_cast<const IdxT*>(p.heavy_list)[blockIdx.x]);
+  const int64_t p0 = offsets[c];
+  const int total = static_cast<int>(static_cast<int64_t>(offsets[c + 1]) - p0);
+  const uint32_t rb = static_cast<uint32_t>(p.nvec) * 16u;
+  const int words = p.nvec * 4;                     // 32-bit words per row
+  const bool col = lane < p.nvec;                   // copies: one 16-byte vector per lane
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(hv_ring));
+  float* wcell = reinterpret_cast<float*>(hv_ring + static_cast<size_t>(kRing) * rb);
+  const uint8_t* my_grads = p.grads + 16u * lane;
+  const uint32_t gstride = static_cast<uint32_t>(p.grad_stride);
+
+  // This warp copies the positions kHvWarps * j + warp.  Lane l of `row_cur` holds the row of the
+  // warp's position j = 32 * cycle + l; `row_nxt` is the following cycle, fetched a cycle early.
+  auto load_rows = [&](int cycle) {
+    const int at = kHvWarps * (32 * cycle + lane) + warp;
+    return at < total ? inverse[p0 + at] : IdxT(0);
+  };
+  auto load_weights = [&](int cycle) {
+    const int at = kHvWarps * (32 * cycle + lane) + warp;
+    return (WEIGHTED && at < total) ? p.pos_weight[p0 + at] : 1.f;
+  };
+  IdxT row_cur = load_rows(0), row_nxt = load_rows(1);
+  float w_cur = load_weights(0), w_nxt = load_weights(1);
+  int issue_cycle = 0;
+  const int batches = (total + kHvBatch - 1) / kHvBatch;
+  auto issue_batch = [&](int b) {
+    if (b < batches) {
+      const int j0 = b * kPerWarp;                  // the warp's first position index of this batch
+      const int within = j0 & 31;
+      if (within == 0 && b > 0) {
+        row_cur = row_nxt;
+        w_cur = w_nxt;
+        issue_cycle++;
+        row_nxt = load_rows(issue_cycle + 1);
+        w_nxt = load_weights(issue_cycle + 1);
+      }
+      const int slot0 = (b % kHvStages) * kHvBatch;
+#pragma unroll
+      for (int i = 0; i < kPerWarp; i++) {
+        const int pos = kHvWarps * (j0 + i) + warp;            // position inside the chunk
+        const int slot = slot0 + (pos - b * kHvBatch);
+        const uint32_t g = static_cast<uint32_t>(__shfl_sync(0xffffffffu, row_cur, within + i));
+        const float w = __shfl_sync(0xffffffffu, w_cur, within + i);
+        if (pos < total) {
+          if (col) cp_async16(ring + static_cast<uint32_t>(slot) * rb + 16u * lane,
+                              my_grads + static_cast<uint64_t>(g) * gstride);
+          if (WEIGHTED && lane == 0) wcell[slot] = w;
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int b = 0; b < kHvStages; b++) issue_batch(b);
+
+  uint32_t acc = 0u;                                // one fp32 value, or two fp16 values
+  const bool mine = tid < words;
+  for (int b = 0; b < batches; b++) {
+    cp_async_wait<kHvStages - 1>();
+    __syncthreads();                                // every warp's copies of this stage have landed
+    const int cnt = min(kHvBatch, total - b * kHvBatch);
+    if (mine) {
+      const uint32_t stage = ring + static_cast<uint32_t>((b % kHvStages) * kHvBatch) * rb + 4u * tid;
+      const float* wstage = wcell + (b % kHvStages) * kHvBatch;
+#pragma unroll 4
+      for (int r = 0; r < cnt; r++) {
+        uint32_t v;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(stage + static_cast<uint32_t>(r) * rb));
+        if (p.f16) {
+          const __half2 s2 = __hadd2(*reinterpret_cast<__half2*>(&acc), *reinterpret_cast<__half2*>(&v));
+          acc = *reinterpret_cast<const uint32_t*>(&s2);
+        } else {
+          float f = __uint_as_float(v);
+          if constexpr (WEIGHTED) f = __fmul_rn(wstage[r], f);
+          acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), f));
+        }
+      }
+    }
+    __syncthreads();                                // the stage may be refilled
+    issue_batch(b + kHvStages);
+  }
+  cp_async_wait<0>();
+
+  // the chunk's sum: same destinations as finish_chunk of the streamed pass
+  if (!mine) return;
+  const int64_t u = loc_map ? static_cast<int64_t>(loc_map[c]) : c;
+  bool first = true, last = true;
+  if (loc_map) {
+    first = (c == 0) || static_cast<int64_t>(loc_map[c - 1]) != u;
+    last = (c + 1 >= C) || static_cast<int64_t>(loc_map[c + 1]) != u;
+  }
+  if (first && last) {
+    if (p.fused) {
+      const int64_t key = static_cast<int64_t>(static_cast<const IdxT*>(p.unique)[u]);
+      if (static_cast<uint64_t>(key) < static_cast<uint64_t>(p.table_rows)) {
+        atomicAdd(reinterpret_cast<float*>(p.dst + key * p.dst_stride) + tid,
+                  __fmul_rn(p.alpha, __uint_as_float(acc)));
+      }
+    } else {
+      reinterpret_cast<uint32_t*>(p.dst + u * p.dst_stride)[tid] = acc;
+    }
+  } else {
+    int64_t group_first = c;
+    while (group_first > 0 && static_cast<int64_t>(loc_map[group_first - 1]) == u) group_first--;
+    const int64_t slot = 2 * (group_first - u) + (c - group_first);
+    if (slot < p.partial_rows) {
+      reinterpret_cast<uint32_t*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[tid] = acc;
+    }
+  }
+}
+
 bool grad_stream_eligible(const GradParams& p, bool allow) {
   static const bool off = std::getenv("NVE_B200_NO_GRAD_STREAM") != nullptr;
   return !off && allow && p.nvec >= 1 && p.nvec <= 32 && p.nvec * 16 <= kGsMaxRowBytes &&
@@ -648,12 +800,20 @@ void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
   const int64_t warps = (n + window - 1) / window;
   const unsigned grid = blocks_for(warps, kGsWarps);
   const int block = kGsWarps * 32;
+  if (p.heavy_list) NVE_B200_CUDA(cudaMemsetAsync(p.heavy_count, 0, sizeof(unsigned long long), s));
   if (p.pos_weight) {
     if (batch == 4) grad_stream_kernel<IdxT, 4, true><<<grid, block, smem, s>>>(p, window);
     else grad_stream_kernel<IdxT, 8, true><<<grid, block, smem, s>>>(p, window);
   } else {
     if (batch == 4) grad_stream_kernel<IdxT, 4, false><<<grid, block, smem, s>>>(p, window);
     else grad_stream_kernel<IdxT, 8, false><<<grid, block, smem, s>>>(p, window);
+  }
+  if (p.heavy_list) {
+    // at most n / kHvThreshold chunks can be that long; blocks beyond the listed count leave at once
+    const unsigned hgrid = static_cast<unsigned>(std::min<int64_t>(n / kHvThreshold + 1, p.heavy_capacity));
+    const size_t hsmem = static_cast<size_t>(kHvStages) * kHvBatch * (row_bytes + (p.pos_weight ? 4 : 0));
+    if (p.pos_weight) grad_heavy_kernel<IdxT, true><<<hgrid, kHvWarps * 32, hsmem, s>>>(p);
+    else grad_heavy_kernel<IdxT, false><<<hgrid, kHvWarps * 32, hsmem, s>>>(p);
   }
 }
 
@@ -680,17 +840,36 @@ __global__ void __launch_bounds__(128) grad_finish_kernel(const GradParams p) {
     todo &= todo - 1;
     const int64_t gu = __shfl_sync(0xffffffffu, u, j);
     const int64_t first = warp * 32 + j;
+    // chunks of the group: 32 chunk-map entries are probed at a time
     int64_t chunks = 1;
-    while (first + chunks < num_chunks && ld_idx(p.loc_map, p.idx64, first + chunks) == gu) chunks++;
+    for (;;) {
+      const int64_t idx = first + chunks + lane;
+      const bool same = idx < num_chunks && ld_idx(p.loc_map, p.idx64, idx) == gu;
+      const uint32_t m = __ballot_sync(0xffffffffu, same);
+      if (m == 0xffffffffu) {
+        chunks += 32;
+      } else {
+        chunks += __ffs(~m) - 1;
+        break;
+      }
+    }
     const int64_t slot_base = 2 * (first - gu);
     for (int v0 = lane; v0 < p.nvec; v0 += 32) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int64_t k = 0; k < chunks; k++) {
-        const int64_t slot = slot_base + k;
-        if (slot < p.partial_rows) {
-          const float4 r =
-              reinterpret_cast<const float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0];
-          add_vec16(acc, r, p.f16);
+      const float4* rows = reinterpret_cast<const float4*>(p.partial) + v0;
+      const int64_t room = p.partial_rows - slot_base;
+      const int64_t usable = room <= 0 ? 0 : (chunks < room ? chunks : room);
+      // eight partial rows are fetched together, then added in chunk order
+      for (int64_t k = 0; k < usable; k += 8) {
+        float4 r[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int64_t slot = slot_base + (k + i < usable ? k + i : usable - 1);
+          r[i] = rows[slot * p.nvec];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          if (k + i < usable) add_vec16(acc, r[i], p.f16);
         }
       }
       if (p.fused) {
@@ -805,6 +984,11 @@ void pooled_sources_run(nve_key_type_t key_type, const void* inverse, const void
   NVE_B200_CUDA(cudaGetLastError());
 }
 
+int64_t grad_heavy_capacity(int64_t capacity) { return capacity / kHvThreshold + 2; }
+size_t grad_heavy_scratch_bytes(int64_t capacity) {
+  return 8 + static_cast<size_t>(grad_heavy_capacity(capacity)) * 8;
+}
+
 size_t dedup_workspace_bytes(nve_key_type_t key_type, int64_t capacity) {
   if (key_type == NVE_KEY_INT64) {
     return carve<int64_t>(nullptr, capacity, cub_bytes_for<int64_t>(capacity)).total;
@@ -837,7 +1021,7 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
                      int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
-                     cudaStream_t stream) {
+                     void* heavy_scratch, int64_t heavy_capacity, cudaStream_t stream) {
   NVE_B200_ARG(!f16 || (!fused && pos_weight == nullptr),
                "dedup_grads: fp16 gradients are summed un-weighted into a gradient buffer only");
   NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
@@ -865,10 +1049,21 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   p.idx64 = key_type == NVE_KEY_INT64;
   p.fused = fused;
   p.f16 = f16;
+  // heavy_scratch: 8 bytes of counter, then heavy_capacity chunk ids of the index type
+  p.heavy_count = static_cast<unsigned long long*>(heavy_scratch);
+  p.heavy_list = heavy_scratch ? static_cast<char*>(heavy_scratch) + 8 : nullptr;
+  p.heavy_capacity = heavy_scratch ? heavy_capacity : 0;
+  static const int threshold = [] {
+    const char* e = std::getenv("NVE_B200_GRAD_HEAVY");   // tuning knob: rows above which a chunk gets a block
+    const int v = e ? std::atoi(e) : 0;
+    return v >= kHvThreshold ? v : kHvThreshold;
+  }();
+  p.heavy_threshold = threshold;
   if (grad_stream_eligible(p, streamed)) {
     if (p.idx64) launch_grad_stream<int64_t>(p, num_keys, stream);
     else launch_grad_stream<int32_t>(p, num_keys, stream);
   } else {
+    p.heavy_list = nullptr;
     launch_grad_first(p, stream);
   }
   if (loc_map != nullptr) launch_grad_finish(p, stream);
@@ -943,6 +1138,6 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
                     max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
                     dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
                     num_keys, /*streamed=*/false, /*pos_weight=*/nullptr, /*f16=*/false,
-                    static_cast<cudaStream_t>(stream));
+                    /*heavy_scratch=*/nullptr, 0, static_cast<cudaStream_t>(stream));
   });
 }

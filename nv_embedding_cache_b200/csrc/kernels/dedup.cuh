@@ -21,6 +21,8 @@ const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int6
 // [0, table_rows) are skipped).  fp32 rows (or, with f16, fp16 rows added in fp16), 16-byte aligned.
 // pos_weight: optional weight per position of `inverse`: rows are multiplied by it before they are
 // added (one rounding each: multiply, then add).
+// heavy_scratch: device scratch of grad_heavy_scratch_bytes() (streamed form only; null keeps long
+// chunks in the streamed pass).
 // streamed: let rows of up to 512 bytes take the first pass that streams them through shared
 // memory with asynchronous copies; false keeps the register form for every width.
 void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
@@ -29,7 +31,12 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
                      int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
-                     cudaStream_t stream);
+                     void* heavy_scratch, int64_t heavy_capacity, cudaStream_t stream);
+
+// Bytes of `heavy_scratch` for batches of up to `capacity` keys (a counter and the ids of the chunks
+// that the streamed pass leaves to the block-per-chunk kernel), and how many ids that holds.
+size_t grad_heavy_scratch_bytes(int64_t capacity);
+int64_t grad_heavy_capacity(int64_t capacity);
 
 // Pooled backward, preparation: for every sorted position q of a dedup() result, src_row[q] = the
 // bag its key came from (CSR offsets of the key type, or fixed hotness when csr == null) and, when

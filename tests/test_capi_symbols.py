@@ -59,3 +59,20 @@ def test_heuristic_handles(capi):
     assert capi.lib.nve_heuristic_create_default(C.byref(h), None, 0) == 0
     assert capi.lib.nve_heuristic_destroy(h) == 0
     assert capi.lib.nve_heuristic_destroy(None) == capi.NVE_ERROR_INVALID_ARGUMENT
+
+
+def test_kernel_level_entry_points_check_arguments_before_any_gpu_work(capi):
+    """No GPU here: these calls must be answered from the argument checks alone."""
+    inv = capi.NVE_ERROR_INVALID_ARGUMENT
+    n = C.c_int64(0)
+    assert capi.lib.nve_b200_pooling_backprop(None, 8, None, None, 64, 64, capi.POOL_SUM, capi.SPARSE_CSR,
+                                              None, 1, 0, None, None, None, 64, C.byref(n), None) == inv
+    assert capi.lib.nve_b200_dedup_grads_f16(None, None, 64, 64, 8, None, None, None, None, 64, None) == inv
+    assert capi.lib.nve_b200_dedup_grads(None, None, 64, 64, 8, None, None, None, None, None, 64, 0, 0, 1.0,
+                                         None) == inv
+    assert capi.lib.nve_b200_deduper_dedup(None, None, 0, None, None, None, None, None, None, None, 0) == inv
+    assert capi.lib.nve_b200_managed_block_create(None, 1 << 20, None, 0) == inv
+    assert capi.lib.nve_b200_managed_block_destroy(None) == 0            # destroying nothing is fine
+    assert capi.lib.nve_b200_scatter_rows(None, 64, None, 64, 64, None, 0, None) == 0   # zero rows: nothing to do
+    assert capi.lib.nve_b200_scatter_rows(None, 64, None, 64, 64, None, 4, None) == inv
+    assert "NULL" in capi.last_error()
