@@ -1,22 +1,30 @@
-"""Row-sharded embedding table over several GPUs: one process per GPU, NCCL all-to-all over NVLink.
+"""Row-sharded embedding table over several GPUs, one process per GPU.
 
-Row ``r`` of the global table lives on rank ``r mod W`` at local index ``r // W``.  A pooled lookup
-on a rank runs
+Row ``r`` of the global table lives on rank ``r mod W`` at local index ``r // W``.  Two ways to
+serve a pooled lookup:
+
+``mode="peer"`` (the one to use on NVLink): every rank allocates its shard in symmetric memory, the
+ranks exchange the mapped base addresses once, and the fused lookup kernel of libnve_b200
+(``nve_b200_lookup_pool`` with ``shard_tables``) reads each row straight from its owner's HBM — no
+collective and no host synchronisation on the lookup path.  This is what the reference does with
+one address range mapped over all shards (src/distributed.cpp:155-256, src/memblock_nvl.cpp:40-119).
+``cache_bytes`` adds the set-associative cache in front of the peer reads.
+
+``mode="alltoall"`` (any process group):
 
     dedup keys -> bucket unique keys by owner -> all-to-all (counts, keys)
     -> owners gather their rows -> all-to-all (rows) -> pool from the received rows
 
-so every distinct row crosses NVLink once per rank and batch, whatever its multiplicity.  The
-device stages are the kernels of libnve_b200 (``nve_b200_deduper_dedup``, ``nve_b200_shard_route``,
+so every distinct row crosses the fabric once per rank and batch, whatever its multiplicity, at the
+price of a sort-based dedup, a routing sort and one host read-back (the split sizes) per lookup.
+The device stages are kernels of libnve_b200 (``nve_b200_deduper_dedup``, ``nve_b200_shard_route``,
 ``nve_b200_shard_localise``, ``nve_b200_gather_rows``, ``nve_b200_shard_expand_slots``,
-``nve_b200_lookup_pool``); torch.distributed supplies the collectives.  The reference instead maps
-all shards into one address range and lets its gather kernel read peers directly
-(src/distributed.cpp:155-256, src/memblock_nvl.cpp:40-119); results are the same as a lookup in
-the unsharded table.
+``nve_b200_lookup_pool``); torch.distributed supplies the collectives.  ``stages`` is the object
+that runs them: the product uses :class:`CudaStages`; the exchange protocol itself (split sizes,
+ordering) is backend-agnostic, which is what the multi-process CPU tests exercise with a host
+implementation of the same stage interface.
 
-``stages`` is the object that runs the device stages.  The product uses :class:`CudaStages`; the
-exchange protocol itself (split sizes, ordering) is backend-agnostic, which is what the
-multi-process CPU tests exercise with a host implementation of the same stage interface.
+Results of both modes are those of a lookup in the unsharded table.
 """
 from __future__ import annotations
 

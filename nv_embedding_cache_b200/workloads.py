@@ -63,7 +63,8 @@ def h2d_probe_gbs(nbytes: int = 1 << 30, reps: int = 10) -> float:
 
 
 def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, cache_frac=0.10, ref_gpu=None):
-    """LinearUVM cached lookup, no pooling: table in pinned host memory, 10 % of rows cached."""
+    """LinearUVM cached lookup, no pooling: table in host memory (a managed block advised to the
+    host, or cudaHostAlloc'ed memory with NVE_B200_C3_TABLE=pinned), 10 % of rows cached."""
     row_bytes = dim * 2
     stream = torch.cuda.current_stream()
     # Table storage: a managed block advised to stay in host memory (what the reference's
@@ -89,7 +90,7 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     out = torch.empty((batch, dim), dtype=torch.float16, device="cuda")
     link = h2d_probe_gbs()
     peak, kind = _hbm_peak(root)
-    res = {"workload": "C3 LinearUVM: 100M x 128 fp16 in pinned host memory, 10% GPU cache, 262144 keys, no pooling",
+    res = {"workload": "C3 LinearUVM: 100M x 128 fp16 in host memory, 10% GPU cache, 262144 keys, no pooling",
            "host_link_probe_gbs": link, "table_storage": storage, "gather": "bulk-copy" if os.environ.get("NVE_B200_GATHER_BULK") == "1" else "lane-vector",
            "runs": {}}
     nb = 16   # distinct batches per run, cycled: missed rows must come over the link every time
@@ -254,7 +255,8 @@ def run_c4b(root, steps=30, warmup=5, rows=10_000_000, dim=128, n=1_048_576, lr=
 
 def run_c5(root, steps=30, warmup=5, rows_per_rank=250_000_000, dim=64, bags=131_072, hot=8,
            mode=os.environ.get("NVE_B200_SHARD_MODE", "peer")):
-    """Row-sharded table, weak scaling: 32 GB of fp16 rows per rank, dedup + all-to-all each way."""
+    """Row-sharded table, weak scaling: 32 GB of fp16 rows per rank, read over peer mappings
+    (default) or served by dedup + all-to-all (NVE_B200_SHARD_MODE=alltoall)."""
     import torch.distributed as dist
     from .sharded import ShardedEmbeddingTable, allocate_symmetric_shard
     world = dist.get_world_size() if dist.is_initialized() else 1
