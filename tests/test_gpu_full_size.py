@@ -113,3 +113,100 @@ def test_c4b_full_batch_update_matches_oracle(torch_cuda, oracle):
     np.add.at(exact, local, -0.01 * grads.cpu().numpy().astype(np.float64))
     assert np.max(np.abs(got - exact) / np.maximum(np.abs(exact), 1e-2)) <= 1e-6 * 20
     capi.check(capi.lib.nve_b200_deduper_destroy(d))
+
+
+def test_dedup_properties_at_full_size(torch_cuda):
+    """1 048 576 keys (the C4b batch): properties that hold whatever the keys are — unique keys
+    strictly ascending, counts sum to n, the inverse buffer is a permutation whose keys are grouped
+    exactly as (unique, counts) say, positions ascend inside a group, chunks respect max_run and
+    tile the groups."""
+    torch = torch_cuda
+    n, rows, max_run = 1_048_576, 10_000_000, 1024
+    keys = to_dev(torch, dg.zipf_keys(n, rows, 1.05, 500))
+    d = C.c_void_p()
+    capi.check(capi.lib.nve_b200_deduper_create(C.byref(d), capi.KEY_INT64, max_run, n))
+    i64 = dict(dtype=torch.int64, device="cuda")
+    cap = n + n // max_run + 2
+    uniq, counts, inverse = torch.empty(n + 1, **i64), torch.empty(n + 1, **i64), torch.empty(n + 1, **i64)
+    offsets, loc = torch.empty(cap + 1, **i64), torch.empty(cap + 1, **i64)
+    runs = (C.c_int64 * 2)()
+    capi.check(capi.lib.nve_b200_deduper_dedup(d, keys.data_ptr(), n, uniq.data_ptr(), counts.data_ptr(),
+                                               loc.data_ptr(), runs, inverse.data_ptr(), offsets.data_ptr(),
+                                               None, 24))
+    u, c = runs[0], runs[1]
+    uq, ct, inv, off, lm = uniq[:u], counts[:u], inverse[:n], offsets[:c + 1], loc[:c]
+    assert bool((uq[1:] > uq[:-1]).all())
+    assert int(ct.sum()) == n and int(ct.min()) >= 1
+    assert bool((torch.sort(inv).values == torch.arange(n, device="cuda")).all())
+    assert bool((keys[inv] == torch.repeat_interleave(uq, ct)).all())
+    starts = torch.cumsum(ct, 0) - ct
+    same_group = torch.ones(n, dtype=torch.bool, device="cuda")
+    same_group[starts] = False
+    assert bool((inv[1:][same_group[1:]] > inv[:-1][same_group[1:]]).all())     # stable: ascending positions
+    lens = off[1:] - off[:-1]
+    assert int(off[0]) == 0 and int(off[-1]) == n and int(lens.max()) <= max_run and int(lens.min()) >= 1
+    per_group = torch.bincount(lm, minlength=u)
+    assert bool((per_group == (ct + max_run - 1) // max_run).all())
+    assert bool((off[:-1][torch.cat([torch.ones(1, dtype=torch.bool, device="cuda"), lm[1:] != lm[:-1]])] == starts).all())
+    capi.check(capi.lib.nve_b200_deduper_destroy(d))
+
+
+def test_pooled_sum_is_linear_in_the_table_at_full_size(torch_cuda):
+    """C2's shape with exactly summable (dyadic) fp32 rows: pooled(T1 + T2) == pooled(T1) + pooled(T2)
+    bit for bit, and a weighted sum with all weights 2 is twice the plain sum."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+    rows, dim, bags = 4_000_000, 128, 65_536
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(77)
+
+    def dyadic():
+        a = torch.randint(-8, 9, (rows, dim), generator=gen, device="cuda", dtype=torch.int32).float()
+        b = torch.randint(3, 10, (rows, dim), generator=gen, device="cuda", dtype=torch.int32).float()
+        return a / torch.exp2(b)
+    t1, t2 = dyadic(), dyadic()
+    _, offs = dg.csr_bags(bags, 1, 32, 1300)
+    keys = to_dev(torch, dg.zipf_keys(int(offs[-1]), rows, 1.1, 6300, dg.permutation(rows)))
+    d_offs = to_dev(torch, offs)
+
+    def pooled(table, weights=None):
+        layer = GPUEmbeddingLayer(table, rows, dim * 4, "float32")
+        ctx = layer.create_execution_context()
+        out = torch.zeros((bags, dim), dtype=torch.float32, device="cuda")
+        layer.lookup_pooled(ctx, keys.numel(), keys, out, dim * 4, "sum" if weights is None else "weighted_sum",
+                            "float32", csr_offsets=d_offs, num_csr_offsets=offs.size, weights=weights,
+                            weight_type="float32")
+        ctx.wait()
+        ctx.destroy(); layer.destroy()
+        return out
+    p1, p2 = pooled(t1), pooled(t2)
+    t1.add_(t2)
+    p12 = pooled(t1)
+    assert bool(torch.equal(p12, p1 + p2))
+    w = torch.full((keys.numel(),), 2.0, device="cuda")
+    assert bool(torch.equal(pooled(t1, w), 2 * p12))
+
+
+def test_cache_insert_is_idempotent_at_c3_batch_size(torch_cuda):
+    """Inserting the same 262 144-key batch twice leaves every tag where it was (all keys of the
+    second insert are resident or lose to resident keys exactly as before)."""
+    torch = torch_cuda
+    from nve_helpers import CacheTable
+    rows, row_bytes, batch = 8_000_000, 256, 262_144
+    table = torch.randint(0, 256, (rows, row_bytes), dtype=torch.uint8, device="cuda")
+    cache = CacheTable(int(rows * 0.1) * row_bytes, row_bytes, backing=table, backing_rows=rows,
+                       max_modify=batch)
+    keys = dg.zipf_keys(batch, rows, 1.2, 300)
+    cache.insert_from_backing(keys)
+    tags1 = cache.tags().copy()
+    cache.insert_from_backing(keys)
+    tags2 = cache.tags()
+    assert np.array_equal(tags1, tags2)
+    resident = int((tags1 != -1).sum())            # a tag is key / num_sets: count the occupied ways
+    assert resident > 10_000
+    out = np.zeros((1000, row_bytes), np.uint8)
+    probe = keys[:1000]
+    cache.find(probe, out, None)
+    hit = ~np.all(out == 0, axis=1)
+    assert hit.any() and np.array_equal(out[hit], table[torch.from_numpy(probe[hit]).cuda()].cpu().numpy())
+    cache.close()
