@@ -62,15 +62,51 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str | None = None):
         self.gpu_index = gpu_index
         self.rows = []
         self._lock = threading.Lock()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        # NVML in-process when the binding is there (a query is a few microseconds and touches one
+        # device); otherwise one nvidia-smi process per sample.
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            if uuid:
+                try:
+                    self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+                except Exception:
+                    self._handle = None
+            if self._handle is None:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n, h = self._nvml, self._handle
+        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        try:
+            power = n.nvmlDeviceGetPowerUsage(h) / 1000.0
+        except Exception:
+            power = 0.0
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            n.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = int(get(h))
+        flag = lambda mask: "Active" if bits & mask else "Not Active"   # NVML reason bits
+        return [str(sm), str(mx), f"{power:.1f}", flag(0x8), flag(0x40), flag(0x20), flag(0x4)]
 
     def sample_now(self):
         try:
+            if self._nvml is not None:
+                row = self._sample_nvml()
+                with self._lock:
+                    self.rows.append(row)
+                return
             out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}",
                                   "--format=csv,noheader,nounits", "-i", str(self.gpu_index)],
                                  capture_output=True, text=True, timeout=10).stdout.strip()
@@ -83,7 +119,7 @@ class ClockSampler:
     def _run(self):
         while not self._stop.is_set():
             self.sample_now()
-            self._stop.wait(0.1)
+            self._stop.wait(0.2)
 
     def __enter__(self):
         self._thread.start()
@@ -279,7 +315,7 @@ def run_ours(args):
             fn(i)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clk:
+        with ClockSampler(local_rank, str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or "")) as clk:
             e0.record(stream)
             if fan_out:
                 for ts in table_streams:
