@@ -17,6 +17,15 @@ from . import capi
 
 
 class ManagedMemBlock:
+    """``ManagedMemBlock(size_in_bytes, gpu_ids)`` or, as the reference binding also offers,
+    ``ManagedMemBlock(row_size, num_embeddings, elem_bytes, gpu_ids)`` through :meth:`for_table`."""
+
+    TYPE = "Managed"
+
+    @classmethod
+    def for_table(cls, row_size: int, num_embeddings: int, elem_bytes: int, gpu_ids=(0,)):
+        return cls(row_size * num_embeddings * elem_bytes, gpu_ids)
+
     def __init__(self, size_in_bytes: int, gpu_ids=(0,)):
         ids = (C.c_int32 * len(gpu_ids))(*gpu_ids)
         p = C.c_void_p()
@@ -29,6 +38,23 @@ class ManagedMemBlock:
 
     def get_size_in_bytes(self) -> int:
         return self.size
+
+    def get_handle(self) -> int:
+        return self.ptr
+
+    def get_type(self) -> str:
+        return self.TYPE
+
+    def copy_from(self, src) -> None:
+        """Copy a C-contiguous buffer (numpy array, tensor on any device) to the start of the block."""
+        t = src if isinstance(src, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(src))
+        if not t.is_contiguous():
+            raise ValueError("copy_from: source buffer must be C-contiguous")
+        nbytes = t.numel() * t.element_size()
+        if nbytes > self.size:
+            raise IndexError(f"copy_from: source is {nbytes} bytes but memblock holds {self.size} bytes")
+        self.as_tensor((t.numel(),), t.dtype).copy_(t.reshape(-1))
+        torch.cuda.synchronize()
 
     def data_ptr(self) -> int:          # so that a block can be passed wherever a tensor is accepted
         return self.ptr

@@ -17,7 +17,9 @@ def make_layer(torch, table_np, cache_rows, where, dtype="float16", default_row=
     if where == "managed":
         from nv_embedding_cache_b200.memblock import ManagedMemBlock
         backing = ManagedMemBlock(table_np.nbytes, (0,))
-        backing.as_tensor(table_np.shape, torch.from_numpy(table_np).dtype).copy_(torch.from_numpy(table_np))
+        backing.copy_from(table_np)
+        assert backing.get_type() == "Managed" and backing.get_size_in_bytes() == table_np.nbytes
+        assert backing.get_handle() == backing.data_ptr()
     elif where == "host":
         backing = torch.from_numpy(table_np).pin_memory()
     else:
