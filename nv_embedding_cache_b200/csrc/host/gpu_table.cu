@@ -255,7 +255,8 @@ class GpuTable : public Table {
     NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
     cache_insert_select(cs_, hash_, key_type_, d_keys.device, n, src, value_stride, from_table,
                         std::max<int64_t>(cfg_.max_modify_size, 0), ++global_ts_, kDecayRate,
-                        scratch, entries, count, s);
+                        scratch, entries, count, s,
+                        /*key_bound=*/from_table ? cfg_.uvm_num_rows : 0);
     const uint32_t cap = static_cast<uint32_t>(n);
     commit_entries(s, entries, count, cap, /*mode=*/0, value_stride, src);
   }

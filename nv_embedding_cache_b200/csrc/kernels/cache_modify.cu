@@ -433,7 +433,7 @@ template <typename KeyT>
 void insert_typed(const CacheStorage& cs, const SetHash& hash, const void* keys_v, int64_t n,
                   const uint8_t* values, int64_t value_stride, bool from_table,
                   int64_t max_modify, int64_t global_ts, float decay_rate, void* scratch,
-                  ModifyEntry* entries, uint32_t* num_entries, cudaStream_t s) {
+                  ModifyEntry* entries, uint32_t* num_entries, cudaStream_t s, int64_t key_bound) {
   const KeyT* keys = static_cast<const KeyT*>(keys_v);
   const size_t cub_bytes = cub_temp_bytes<KeyT>(n);
   Layout<KeyT> L = carve<KeyT>(scratch, n, cub_bytes);
@@ -442,8 +442,13 @@ void insert_typed(const CacheStorage& cs, const SetHash& hash, const void* keys_
   size_t tmp = L.cub_bytes;
 
   iota_kernel<<<blocks_for(n, T), T, 0, s>>>(L.pos, n);
+  // keys known to lie in [0, key_bound) (rows of a linear backing table) need only that many sort
+  // bits; the order among them, hence every result, is the same as with the full key width
+  const int sort_bits = key_bound > 0 ? std::min<int>(bits_for(static_cast<uint64_t>(key_bound)),
+                                                       static_cast<int>(sizeof(KeyT) * 8))
+                                      : static_cast<int>(sizeof(KeyT) * 8);
   NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(L.cub_tmp, tmp, keys, L.keys_sorted, L.pos,
-                                                L.pos_sorted, N, 0, sizeof(KeyT) * 8, s));
+                                                L.pos_sorted, N, 0, sort_bits, s));
   mark_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(L.keys_sorted, L.head, n);
   tmp = L.cub_bytes;
   NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(L.cub_tmp, tmp, L.head, L.rank, N, s));
@@ -482,14 +487,14 @@ void cache_insert_select(const CacheStorage& cs, const SetHash& hash, nve_key_ty
                          const void* keys, int64_t n, const uint8_t* values, int64_t value_stride,
                          bool from_table, int64_t max_modify, int64_t global_ts, float decay_rate,
                          void* scratch, ModifyEntry* entries, uint32_t* num_entries,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int64_t key_bound) {
   NVE_B200_ARG(n > 0 && n < (int64_t{1} << 31), "cache insert: batch size out of range");
   if (key_type == NVE_KEY_INT64) {
     insert_typed<int64_t>(cs, hash, keys, n, values, value_stride, from_table, max_modify,
-                          global_ts, decay_rate, scratch, entries, num_entries, stream);
+                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound);
   } else {
     insert_typed<int32_t>(cs, hash, keys, n, values, value_stride, from_table, max_modify,
-                          global_ts, decay_rate, scratch, entries, num_entries, stream);
+                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound);
   }
 }
 

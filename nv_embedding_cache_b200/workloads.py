@@ -83,15 +83,21 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     gt = GpuTable(cache_bytes, row_bytes, "float16", uvm_table=table, uvm_num_rows=rows)
     layer = LinearUVMEmbeddingLayer(gt)
     ctx = layer.create_execution_context(stream.cuda_stream, stream.cuda_stream)
+    import time
+    insert_s = []
     for b in range(20):                                    # explicit, deterministic warm-up
         k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
         capi.check(capi.lib.nve_b200_gpu_table_insert_from_backing(gt.handle, ctx.handle, batch, k.data_ptr()))
         ctx.wait()
+        insert_s.append(time.perf_counter() - t0)
     out = torch.empty((batch, dim), dtype=torch.float16, device="cuda")
     link = h2d_probe_gbs()
     peak, kind = _hbm_peak(root)
     res = {"workload": "C3 LinearUVM: 100M x 128 fp16 in host memory, 10% GPU cache, 262144 keys, no pooling",
-           "host_link_probe_gbs": link, "table_storage": storage, "gather": "bulk-copy" if os.environ.get("NVE_B200_GATHER_BULK") == "1" else "lane-vector",
+           "host_link_probe_gbs": link, "table_storage": storage,
+           "insert_us_median": float(np.median(insert_s[5:]) * 1e6), "gather": "bulk-copy" if os.environ.get("NVE_B200_GATHER_BULK") == "1" else "lane-vector",
            "runs": {}}
     nb = 16   # distinct batches per run, cycled: missed rows must come over the link every time
     for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(batch, rows, 1.2, 320 + 2 * b)),
@@ -117,10 +123,14 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     if ref_gpu is not None:
         # the reference cache, warmed with the same insert sequence, serving the same batches
         rc = ref_gpu.cache(cache_bytes, row_bytes, max_modify=batch)
+        ref_insert_s = []
         for b in range(20):
             k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
             rc.insert_from_table(k.data_ptr(), batch, table.data_ptr(), row_bytes)
-        res["reference_gpu"] = {}
+            ref_insert_s.append(time.perf_counter() - t0)
+        res["reference_gpu"] = {"insert_us_median": float(np.median(ref_insert_s[5:]) * 1e6)}
         for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(batch, rows, 1.2, 320 + 2 * b)),
                                ("uniform", lambda b: dg.uniform_keys(batch, rows, 321 + 2 * b))):
             batches = [torch.from_numpy(gen_keys(b)).cuda() for b in range(nb)]
