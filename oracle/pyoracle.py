@@ -391,6 +391,7 @@ class ReferenceGpu:
             "refgpu_dedup_grads_f16": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
             "refgpu_dedup_grads_timed": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                          C.POINTER(f32)],
+            "refgpu_update_accumulate_table": [_vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, C.POINTER(f32)],
             "refgpu_pooling_backprop": [_vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(_i64)],
             "refgpu_find_and_combine": [_i32, _i64, _vp, pp, pp, _i32, _i32, _i32, _vp, _i32, _i32,
                                         C.POINTER(f32)],
@@ -407,6 +408,13 @@ class ReferenceGpu:
     # ---- cache
     def cache(self, cache_bytes, row_bytes, sentinel=-1, decay=0.95, max_modify=1 << 20):
         return RefGpuCache(self, cache_bytes, row_bytes, sentinel, decay, max_modify)
+
+    def update_accumulate_table(self, src_ptr, keys_ptr, table_ptr, width, n, num_rows, warmup=0, iters=0):
+        """table[keys[i]] += src[i] (fp32 rows); returns mean ms per call when iters > 0."""
+        ms = C.c_float(0)
+        self.check(self.lib.refgpu_update_accumulate_table(src_ptr, keys_ptr, table_ptr, width, n, num_rows,
+                                                           warmup, iters, C.byref(ms)))
+        return ms.value
 
     def pooling_backprop(self, keys_ptr, n, csr_ptr, num_bags, grads_ptr, weights_ptr, pooling, width,
                          unique_ptr, out_ptr) -> int:

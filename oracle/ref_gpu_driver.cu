@@ -11,6 +11,7 @@
 //                                                         shows the call order reproduced below)
 //   cuda_ops/deduper.cuh, cuda_ops/dedup_grads_kernel.cuh Deduper, CallComputeGradients
 //   cuda_ops/gradient_calculator.cuh                      GradientCalculator (pooled backward)
+//   cuda_ops/update_accumulate.cuh                        UpdateAccumulateTable (table += rows)
 #include <cstdint>
 #include <cstdio>
 #include <memory>
@@ -28,6 +29,7 @@
 #include "cuda_ops/deduper.cuh"
 #include "cuda_ops/dedup_grads_kernel.cuh"
 #include "cuda_ops/gradient_calculator.cuh"
+#include "cuda_ops/update_accumulate.cuh"
 // Only the combinations used below are instantiated (the public dispatcher would instantiate the
 // whole type matrix); this macro drops the extern declarations of the pre-built matrix.
 #define NVE_FAC_SKIP_EXTERN_DECLS
@@ -453,6 +455,38 @@ int refgpu_dedup_grads_f16(const void* d_grads, void* d_unique_grads, const int6
                                       d_unique, d_inverse, d_loc_map, d_offsets, h_num_runs,
                                       static_cast<uint32_t>(width), 0);
     ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+// table[keys[i]] += src[i] over fp32 rows of `width` values (reference UpdateAccumulateTable; rows
+// packed, keys outside [0, num_rows) skipped by the kernel).  iters > 0: timed, mean ms per call.
+int refgpu_update_accumulate_table(const float* d_src, const int64_t* d_keys, float* d_table, int width,
+                                   int64_t n, int64_t num_rows, int warmup, int iters, float* ms_per_call) {
+  return guarded([&] {
+    auto once = [&] {
+      nve::UpdateAccumulateTable<Key, float>(d_src, d_keys, d_table, static_cast<uint32_t>(width),
+                                             static_cast<uint32_t>(width), static_cast<uint32_t>(width),
+                                             static_cast<int32_t>(n), static_cast<uint64_t>(num_rows), 0);
+    };
+    if (iters <= 0) {
+      once();
+      ck(cudaDeviceSynchronize(), "sync");
+      return;
+    }
+    cudaEvent_t e0, e1;
+    ck(cudaEventCreate(&e0), "event");
+    ck(cudaEventCreate(&e1), "event");
+    for (int i = 0; i < warmup + iters; i++) {
+      if (i == warmup) ck(cudaEventRecord(e0, 0), "record");
+      once();
+    }
+    ck(cudaEventRecord(e1, 0), "record");
+    ck(cudaEventSynchronize(e1), "sync");
+    float ms = 0.f;
+    ck(cudaEventElapsedTime(&ms, e0, e1), "elapsed");
+    *ms_per_call = ms / static_cast<float>(iters);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
   });
 }
 

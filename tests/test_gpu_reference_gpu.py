@@ -225,6 +225,31 @@ def test_gradient_sums(torch_cuda, reference_gpu, max_run, width):
     rd.close()
 
 
+@pytest.mark.parametrize("width", [128, 32, 20])
+def test_update_accumulate_table(torch_cuda, reference_gpu, width):
+    """table[key] += row against the reference's UpdateAccumulateTable: with unique keys each table
+    element takes exactly one fp32 addition, so both paths (atomic and load/store) are bit-identical;
+    keys outside the table are skipped by both."""
+    torch = torch_cuda
+    rows, n = 5000, 1500
+    rng = np.random.default_rng(11)
+    keys = rng.permutation(rows)[:n].astype(np.int64)
+    keys[::97] = rows + 5                      # out of range: skipped
+    keys[5] = -3
+    table_np = rng.normal(0, 1, (rows, width)).astype(np.float32)
+    upd = to_dev(torch, rng.normal(0, 1e-2, (n, width)).astype(np.float32))
+    k_dev = to_dev(torch, keys)
+    want = to_dev(torch, table_np)
+    reference_gpu.update_accumulate_table(upd.data_ptr(), k_dev.data_ptr(), want.data_ptr(), width, n, rows)
+    for unique in (0, 1):
+        got = to_dev(torch, table_np)
+        capi.check(capi.lib.nve_b200_update_rows(got.data_ptr(), rows, width * 4, capi.DTYPE_FLOAT32, width * 4,
+                                                 capi.KEY_INT64, k_dev.data_ptr(), n, upd.data_ptr(), width * 4,
+                                                 1, unique, None))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+
+
 @pytest.mark.parametrize("max_run", [-1, 1024])
 def test_gradient_sums_fp16(torch_cuda, reference_gpu, max_run):
     """fp16 gradient rows are added in fp16, in position order: un-split groups are bit-identical to
