@@ -12,6 +12,7 @@
 #define NVE_B200_OPS_H
 
 #include <stdbool.h>
+#include <stddef.h>
 
 #include "nve_c_api.h"
 
@@ -108,6 +109,35 @@ typedef struct {
  * raw-row gather of the dense layer (src/gpu_embedding_layer.cu:192-227).
  */
 NVE_C_API nve_status_t nve_b200_gather_rows(const nve_b200_gather_args_t* args, void* stream);
+
+/*
+ * The same raw-row lookup on the sort-gather schedule: every key is resolved first (hit mask, miss
+ * counter and miss list as above), the work is ordered so that the rows read from the backing
+ * table come before the rows served by the cache, each class in address order, and a warp then
+ * copies a tile of at most `tile` rows (0 = 1024).  Replaces lookup_sort_gather
+ * (include/ecache/ec_set_associative.h:471-526; kernels find / get_sort_key / gather / call_sort_gather,
+ * include/ecache/ec_set_associative.cuh:814-1057) with the same two-call protocol: scratch == NULL
+ * writes the scratch size for this batch to *scratch_bytes, a second call with a 256-byte aligned
+ * device buffer of that size runs the lookup.  Raw copies only (output_dtype == value_dtype);
+ * NVE_ERROR_INVALID_ARGUMENT for a decoding lookup.  Output identical to nve_b200_gather_rows.
+ */
+NVE_C_API nve_status_t nve_b200_gather_rows_sorted(const nve_b200_gather_args_t* args, int64_t tile,
+                                                   void* scratch, size_t* scratch_bytes, void* stream);
+
+/*
+ * Parameters of the pipeline-gather schedule (nve_gpu_table_config_t.kernel_mode_type ==
+ * NVE_KERNEL_PIPELINE_GATHER): kernel_mode_value is 0 (defaults: 1024 rows per host task, 16
+ * auxiliary streams) or the address of this struct, which is read once when the table is created.
+ * Replaces GatherKernelPipelineParams (cuda_ops/pipeline_gather.cuh:33-36) and the schedule
+ * gather_flow_pipeline (:264-412): lookups of a table with a host-readable backing table resolve and
+ * sort on the device, host threads gather the rows of the backing table into pinned staging memory
+ * while the device copies the rows its cache serves, and copy kernels on the auxiliary streams
+ * place the staged rows.  The lookup call blocks its thread until all of that is enqueued.
+ */
+typedef struct {
+  uint64_t task_size;        /* most rows one host task gathers; 0 = one task per host thread */
+  uint64_t num_aux_streams;  /* streams the staged rows are placed on; at least one is used */
+} nve_b200_pipeline_params_t;
 
 /*
  * table[key] = values[i] (accumulate == 0) or table[key] += values[i] (accumulate != 0) for keys in

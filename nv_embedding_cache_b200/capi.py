@@ -145,6 +145,7 @@ PROTOTYPES = {
     # kernel-level ABI (include/nve_b200_ops.h)
     "nve_b200_lookup_pool": (_i32, [C.POINTER(PoolArgs), _vp]),
     "nve_b200_gather_rows": (_i32, [C.POINTER(GatherArgs), _vp]),
+    "nve_b200_gather_rows_sorted": (_i32, [C.POINTER(GatherArgs), _i64, _vp, C.POINTER(C.c_size_t), _vp]),
     "nve_b200_gpu_table_get_cache_data": (_i32, [_vp, _vp, C.POINTER(CacheData)]),
     "nve_b200_gpu_table_get_policy_state": (_i32, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "nve_b200_gpu_table_insert_from_backing": (_i32, [_vp, _vp, _i64, _vp]),

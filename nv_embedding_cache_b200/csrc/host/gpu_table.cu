@@ -41,6 +41,11 @@ class GpuTable : public Table {
     if (cfg.data_storage_on_host) {
       throw NotImplemented("cache data storage on host is not provided");
     }
+    if (cfg.kernel_mode_type == NVE_KERNEL_PIPELINE_GATHER && cfg.kernel_mode_value != 0) {
+      // the value is the address of the schedule's parameters (as in the reference, where it points
+      // at a GatherKernelPipelineParams); they are read once, here
+      pipeline_ = *reinterpret_cast<const nve_b200_pipeline_params_t*>(cfg.kernel_mode_value);
+    }
     const int kb = key_bytes(key_type);
     // sets that fit: tags + rows + counters per set, each rounded up to 16 bytes
     // (reference include/ecache/ec_set_associative.h:666-685, device-modify counters
@@ -81,6 +86,10 @@ class GpuTable : public Table {
     (void)cudaFree(cs_.set_ts);
     if (invalidate_done_) (void)cudaEventDestroy(invalidate_done_);
     if (modify_done_) (void)cudaEventDestroy(modify_done_);
+    for (cudaStream_t st : pipeline_res_.aux) (void)cudaStreamDestroy(st);
+    for (cudaEvent_t ev : pipeline_res_.aux_done) (void)cudaEventDestroy(ev);
+    if (pipeline_res_.sorted) (void)cudaEventDestroy(pipeline_res_.sorted);
+    if (pipeline_res_.words) (void)cudaEventDestroy(pipeline_res_.words);
     if (prev >= 0) (void)cudaSetDevice(prev);
     (void)cudaGetLastError();
   }
@@ -148,7 +157,64 @@ class GpuTable : public Table {
     g.row_copy_bytes = cfg_.row_size_in_bytes;
     g.hit_mask = d_hit_mask;
     order_lookup(s);
+    if (cfg_.uvm_table != nullptr && d_values != nullptr &&
+        cfg_.kernel_mode_type == NVE_KERNEL_PIPELINE_GATHER) {
+      // Part of this lookup runs on auxiliary streams that join the lookup stream only at the end
+      // of the call, so no cache modification may be assembled meanwhile (the reference brackets
+      // the same span with its ScopedCustomFlow, cuda_ops/pipeline_gather.cuh:349-398).
+      std::lock_guard<std::mutex> gate(modify_mu_);
+      ensure_pipeline_resources();
+      const PipelineBufferFn buffer = [&c](const char* name, size_t bytes, bool pinned) {
+        return c.scratch(name, bytes, pinned);
+      };
+      if (gather_rows_pipeline(g, cfg_.invalid_key, pipeline_.task_size, pipeline_res_, buffer, s)) return;
+    }
+    if (cfg_.uvm_table != nullptr && lookup_schedule(n) == NVE_KERNEL_SORT_GATHER) {
+      // two-call protocol of the sort-gather schedule: size the scratch, then run
+      size_t bytes = 0;
+      const int64_t tile = cfg_.kernel_mode_type == NVE_KERNEL_SORT_GATHER
+                               ? static_cast<int64_t>(cfg_.kernel_mode_value) : 0;
+      if (gather_rows_sorted(g, cfg_.invalid_key, tile, nullptr, &bytes, s)) {
+        void* scratch = c.scratch("sort_gather", bytes, false);
+        gather_rows_sorted(g, cfg_.invalid_key, tile, scratch, &bytes, s);
+        return;
+      }
+    }
     gather_rows(g, cfg_.invalid_key, s);
+  }
+
+  // Which lookup schedule a batch of n keys takes against a backing table (reference
+  // get_kernel_mode, src/gpu_table.cu:271-291).  Forced modes are honoured.  The dynamic mode of
+  // the reference switches to sort-gather from 2^20 keys (or kernel_mode_value) on; here it does so
+  // only when kernel_mode_value names a threshold, because the fused kernel measured faster at
+  // every batch size on B200.  The pipeline schedule is handled before this is asked (it falls back
+  // to the fused kernel when the table is not host-readable).
+  nve_kernel_type_t lookup_schedule(int64_t n) const {
+    switch (cfg_.kernel_mode_type) {
+      case NVE_KERNEL_DYNAMIC:
+        return (cfg_.kernel_mode_value != 0 && n >= static_cast<int64_t>(cfg_.kernel_mode_value))
+                   ? NVE_KERNEL_SORT_GATHER : NVE_KERNEL_LOOKUP_UVM;
+      case NVE_KERNEL_LOOKUP_UVM: return NVE_KERNEL_LOOKUP_UVM;
+      case NVE_KERNEL_SORT_GATHER: return NVE_KERNEL_SORT_GATHER;
+      case NVE_KERNEL_PIPELINE_GATHER: return NVE_KERNEL_LOOKUP_UVM;
+      default: throw NotImplemented("unknown kernel_mode_type");
+    }
+  }
+
+  // Streams and events of the pipeline schedule, made at the first lookup that takes it.
+  void ensure_pipeline_resources() {
+    if (!pipeline_res_.aux.empty()) return;
+    const size_t streams = static_cast<size_t>(std::max<uint64_t>(1, std::min<uint64_t>(pipeline_.num_aux_streams, 64)));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&pipeline_res_.sorted, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&pipeline_res_.words, cudaEventDisableTiming));
+    for (size_t i = 0; i < streams; i++) {
+      cudaStream_t st = nullptr;
+      cudaEvent_t ev = nullptr;
+      NVE_B200_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+      pipeline_res_.aux.push_back(st);
+      NVE_B200_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+      pipeline_res_.aux_done.push_back(ev);
+    }
   }
 
   void insert(context_ptr_t& ctx, int64_t n, const void* keys, int64_t value_stride,
@@ -328,6 +394,8 @@ class GpuTable : public Table {
   cudaEvent_t invalidate_done_ = nullptr;
   cudaEvent_t modify_done_ = nullptr;
   int64_t global_ts_ = 0;
+  nve_b200_pipeline_params_t pipeline_{1024, 16};   // reference defaults (src/gpu_table.cu:343-347)
+  PipelineResources pipeline_res_;
 
 
  public:

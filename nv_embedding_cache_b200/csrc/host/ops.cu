@@ -2,13 +2,17 @@
 // choice of vector width from the alignments involved, kernel parameter packing and launch.
 #include "ops_internal.hpp"
 
+#include <cstring>
 #include <mutex>
 
 #include "../kernels/lookup_pool.cuh"
 #include "../kernels/pool_dense.cuh"
 #include "../kernels/lookup_rows.cuh"
 #include "../kernels/gather_bulk.cuh"
+#include "../kernels/gather_sorted.cuh"
 #include "../kernels/update_rows.cuh"
+#include "context.hpp"
+#include "host_workers.hpp"
 
 namespace nve_b200 {
 
@@ -214,13 +218,14 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
   NVE_B200_CUDA(cudaGetLastError());
 }
 
-void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStream_t stream) {
-  NVE_B200_ARG(a.num_keys >= 0, "gather_rows: negative key count");
-  if (a.num_keys == 0) return;
+namespace {
+// Checks the arguments of the gather family and packs the kernel parameters; `mode` is -1 for a raw
+// byte copy or the In id of a decoding lookup, `vb` the vector width every address involved allows.
+void pack_gather_params(const nve_b200_gather_args_t& a, int64_t sentinel_tag, GatherKernelParams& p,
+                        int& mode, int& vb) {
   NVE_B200_ARG(a.keys != nullptr, "gather_rows: keys is NULL");
   NVE_B200_ARG(a.table != nullptr || a.cache != nullptr, "gather_rows: no table and no cache");
 
-  GatherKernelParams p{};
   p.table = static_cast<const uint8_t*>(a.table);
   p.num_rows = a.num_rows;
   p.row_stride = a.row_stride;
@@ -242,8 +247,8 @@ void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStre
     cache_base = reinterpret_cast<uint64_t>(p.cache.cache_ptr);
     cache_row = p.cache.row_size;
   }
-  int mode = -1;
-  int vb = 16;
+  mode = -1;
+  vb = 16;
   if (a.output == nullptr) {
     p.nvec = 0;
   } else if (a.output_dtype == a.value_dtype) {
@@ -277,6 +282,15 @@ void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStre
     p.out_vec_ok = (reinterpret_cast<uint64_t>(a.output) % store_bytes == 0) &&
                    (static_cast<uint64_t>(a.output_stride) % store_bytes == 0);
   }
+}
+}  // namespace
+
+void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStream_t stream) {
+  NVE_B200_ARG(a.num_keys >= 0, "gather_rows: negative key count");
+  if (a.num_keys == 0) return;
+  GatherKernelParams p{};
+  int mode, vb;
+  pack_gather_params(a, sentinel_tag, p, mode, vb);
   // NVE_B200_GATHER_BULK=1 moves raw rows with the bulk-copy engine instead of lane vectors
   static const bool bulk = std::getenv("NVE_B200_GATHER_BULK") != nullptr &&
                            std::getenv("NVE_B200_GATHER_BULK")[0] == '1';
@@ -286,6 +300,103 @@ void gather_rows(const nve_b200_gather_args_t& a, int64_t sentinel_tag, cudaStre
     launch_lookup_rows(p, mode, vb, stream);
   }
   NVE_B200_CUDA(cudaGetLastError());
+}
+
+bool gather_rows_sorted(const nve_b200_gather_args_t& a, int64_t sentinel_tag, int64_t tile, void* scratch,
+                        size_t* scratch_bytes, cudaStream_t stream) {
+  NVE_B200_ARG(a.num_keys >= 0, "gather_rows_sorted: negative key count");
+  NVE_B200_ARG(scratch_bytes != nullptr, "gather_rows_sorted: scratch_bytes is NULL");
+  NVE_B200_ARG(tile >= 0, "gather_rows_sorted: negative tile");
+  if (a.num_keys == 0) {
+    if (scratch == nullptr) *scratch_bytes = 0;
+    return true;
+  }
+  GatherKernelParams p{};
+  int mode, vb;
+  pack_gather_params(a, sentinel_tag, p, mode, vb);
+  SortedGatherLayout layout{};
+  if (mode != -1 || !gather_sorted_layout(p, &layout)) return false;
+  const size_t need = gather_sorted_scratch_bytes(a.num_keys);
+  if (scratch == nullptr) {
+    *scratch_bytes = need;
+    return true;
+  }
+  NVE_B200_ARG(*scratch_bytes >= need, "gather_rows_sorted: scratch buffer too small");
+  NVE_B200_ARG(reinterpret_cast<uint64_t>(scratch) % 256 == 0, "gather_rows_sorted: scratch must be 256-byte aligned");
+  launch_gather_sorted(p, layout, vb, tile > 0 ? tile : 1024, scratch, *scratch_bytes, sm_count(), stream);
+  return true;
+}
+
+bool gather_rows_pipeline(const nve_b200_gather_args_t& a, int64_t sentinel_tag, uint64_t task_size,
+                          PipelineResources& res, const PipelineBufferFn& buffer, cudaStream_t stream) {
+  NVE_B200_ARG(a.num_keys >= 0, "gather_rows_pipeline: negative key count");
+  if (a.num_keys == 0) return true;
+  GatherKernelParams p{};
+  int mode, vb;
+  pack_gather_params(a, sentinel_tag, p, mode, vb);
+  SortedGatherLayout layout{};
+  if (mode != -1 || p.out == nullptr || p.table == nullptr || res.aux.empty()) return false;
+  if (!gather_sorted_layout(p, &layout)) return false;
+  if (residency_of(a.table) == Residency::Device) return false;   // host threads read the table rows
+
+  const int64_t n = p.n;
+  const int64_t row = a.row_copy_bytes;
+  const int sms = sm_count();
+  const size_t sort_bytes = gather_sorted_scratch_bytes(n);
+  auto* scratch = static_cast<uint8_t*>(buffer("pipeline_sort", sort_bytes + 256, false));
+  auto* d_count = reinterpret_cast<unsigned long long*>(scratch + sort_bytes);
+  auto* h_count = static_cast<unsigned long long*>(buffer("pipeline_count", 64, true));
+
+  // resolve + sort; the number of rows the backing table serves (they sort first) comes back first
+  NVE_B200_CUDA(cudaMemsetAsync(d_count, 0, sizeof(*d_count), stream));
+  const uint64_t* sorted = launch_resolve_and_sort(p, layout, scratch, sort_bytes, d_count, stream);
+  NVE_B200_CUDA(cudaMemcpyAsync(h_count, d_count, sizeof(*d_count), cudaMemcpyDeviceToHost, stream));
+  NVE_B200_CUDA(cudaEventRecord(res.sorted, stream));
+  NVE_B200_CUDA(cudaEventSynchronize(res.sorted));
+  const int64_t from_table = static_cast<int64_t>(*h_count);
+
+  // device half: the rows the cache serves, on the first auxiliary stream
+  size_t used = 0;
+  if (n - from_table > 0) {
+    NVE_B200_CUDA(cudaStreamWaitEvent(res.aux[0], res.sorted, 0));
+    launch_copy_sorted(p, layout, vb, 128, sorted + from_table, n - from_table, nullptr, 0, sms, res.aux[0]);
+    used = 1;
+  }
+
+  // host half: worker threads gather the table rows into pinned staging in sorted order; the copy
+  // of each task's rows to their places in the output is launched by the worker that staged them
+  if (from_table > 0) {
+    auto* h_words = static_cast<uint64_t*>(buffer("pipeline_words", size_t(from_table) * 8, true));
+    auto* h_rows = static_cast<uint8_t*>(buffer("pipeline_rows", size_t(from_table) * row, true));
+    NVE_B200_CUDA(cudaMemcpyAsync(h_words, sorted, size_t(from_table) * 8, cudaMemcpyDeviceToHost, stream));
+    NVE_B200_CUDA(cudaEventRecord(res.words, stream));
+    HostWorkers& workers = HostWorkers::instance();
+    int64_t per_task = (from_table + workers.size() - 1) / workers.size();
+    if (task_size > 0 && static_cast<int64_t>(task_size) < per_task) per_task = static_cast<int64_t>(task_size);
+    const int64_t tasks = (from_table + per_task - 1) / per_task;
+    const size_t streams = res.aux.size();
+    used = std::min<size_t>(streams, std::max<size_t>(used, static_cast<size_t>(tasks)));
+    int device = 0;
+    NVE_B200_CUDA(cudaGetDevice(&device));
+    const auto* table = static_cast<const uint8_t*>(a.table);
+    NVE_B200_CUDA(cudaEventSynchronize(res.words));
+    workers.parallel_for(tasks, [&](int64_t t) {
+      const int64_t first = t * per_task;
+      const int64_t count = std::min(per_task, from_table - first);
+      for (int64_t j = first; j < first + count; j++) {
+        const uint64_t idx = sorted_word_index(h_words[j], layout);
+        std::memcpy(h_rows + j * row, table + idx * static_cast<uint64_t>(a.row_stride), size_t(row));
+      }
+      NVE_B200_CUDA(cudaSetDevice(device));
+      launch_copy_sorted(p, layout, vb, 128, sorted + first, count, h_rows + first * row, row, sms,
+                         res.aux[static_cast<size_t>(t) % streams]);
+    });
+  }
+  for (size_t i = 0; i < used; i++) {
+    NVE_B200_CUDA(cudaEventRecord(res.aux_done[i], res.aux[i]));
+    NVE_B200_CUDA(cudaStreamWaitEvent(stream, res.aux_done[i], 0));
+  }
+  return true;
 }
 
 void update_rows(void* table, int64_t num_rows, int64_t row_stride, nve_data_type_t value_dtype,
@@ -342,6 +453,18 @@ nve_status_t nve_b200_gather_rows(const nve_b200_gather_args_t* args, void* stre
   if (!args) return nve_b200::set_last_error(NVE_ERROR_INVALID_ARGUMENT, "args must not be NULL");
   return nve_b200::guarded(
       [&] { nve_b200::gather_rows(*args, -1, static_cast<cudaStream_t>(stream)); });
+}
+
+nve_status_t nve_b200_gather_rows_sorted(const nve_b200_gather_args_t* args, int64_t tile, void* scratch,
+                                         size_t* scratch_bytes, void* stream) {
+  if (!args) return nve_b200::set_last_error(NVE_ERROR_INVALID_ARGUMENT, "args must not be NULL");
+  return nve_b200::guarded([&] {
+    if (!nve_b200::gather_rows_sorted(*args, -1, tile, scratch, scratch_bytes, static_cast<cudaStream_t>(stream))) {
+      throw nve_b200::Error(NVE_ERROR_INVALID_ARGUMENT,
+                            "gather_rows_sorted: raw row copies only, and class, row index and position "
+                            "must fit one 64-bit sort word");
+    }
+  });
 }
 
 nve_status_t nve_b200_update_rows(void* table, int64_t num_rows, int64_t row_stride,

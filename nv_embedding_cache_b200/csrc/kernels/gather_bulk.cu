@@ -26,67 +26,15 @@ __global__ void __launch_bounds__(kBulkWarps * 32) gather_bulk_kernel(const Bulk
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
-  const int64_t i = base + lane;
 
-  // ---- phase 1: resolve (same rules as lookup_rows_kernel)
-  const uint32_t in_word = p.hit_mask ? p.hit_mask[base >> 5] : 0u;
-  const bool active = (i < p.n) && !((in_word >> lane) & 1u);
-  const uint8_t* row = nullptr;
-  bool from_cache = false, cache_missed = false;
-  int64_t key = 0;
-  if (active) {
-    key = load_index(p.keys, p.key64, i);
-    if (p.cache.enabled) {
-      uint32_t set;
-      const int way = p.key64 ? probe_set<int64_t>(p.cache, key, &set)
-                              : probe_set<int32_t>(p.cache, static_cast<int32_t>(key), &set);
-      if (way >= 0) {
-        row = p.cache.cache_ptr + (static_cast<uint64_t>(set) * 8u + way) * p.cache.row_size;
-        from_cache = true;
-      } else {
-        cache_missed = true;
-      }
-    }
-    if (row == nullptr && p.table != nullptr) {
-      int64_t k = key;
-      const bool in_range = static_cast<uint64_t>(k) < static_cast<uint64_t>(p.num_rows);
-      if (!in_range && p.default_row >= 0) k = p.default_row;
-      if (in_range || p.default_row >= 0) row = p.table + k * p.row_stride;
-    }
-  }
-  const bool resolved = row != nullptr;
-  const uint32_t m_cache = __ballot_sync(0xffffffffu, resolved && from_cache);
-  const uint32_t m_table = __ballot_sync(0xffffffffu, resolved && !from_cache);
-  const uint32_t m_unres = __ballot_sync(0xffffffffu, active && !resolved);
-  const uint32_t m_cmiss = __ballot_sync(0xffffffffu, cache_missed);
+  // ---- phase 1: resolve (shared with lookup_rows_kernel)
+  const ResolvedKey r = resolve_keys(p, base, lane);
+  const uint8_t* row = r.row;
+  const bool from_cache = r.from_cache;
+  const bool resolved = r.row != nullptr;
+  const uint32_t m_cache = r.m_cache;
+  const uint32_t m_table = r.m_table;
   const uint32_t lt = (1u << lane) - 1u;
-  if (p.hit_mask && lane == 0) p.hit_mask[base >> 5] = in_word | m_cache | m_table;
-  if (p.cache.enabled && p.cache.misses && m_cmiss && lane == 0) {
-    atomicAdd(reinterpret_cast<unsigned long long*>(p.cache.misses),
-              static_cast<unsigned long long>(__popc(m_cmiss)));
-  }
-  if (m_unres) {
-    if (p.miss_count && lane == 0) {
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.miss_count),
-                static_cast<unsigned long long>(__popc(m_unres)));
-    }
-    if (p.miss_list_len) {
-      unsigned long long cursor = 0;
-      if (lane == 0) {
-        cursor = atomicAdd(reinterpret_cast<unsigned long long*>(p.miss_list_len),
-                           static_cast<unsigned long long>(__popc(m_unres)));
-      }
-      cursor = __shfl_sync(0xffffffffu, cursor, 0);
-      if (active && !resolved) {
-        const int64_t at = static_cast<int64_t>(cursor) + __popc(m_unres & lt);
-        if (p.miss_positions) p.miss_positions[at] = i;
-        if (p.miss_keys) {
-          if (p.key64) reinterpret_cast<int64_t*>(p.miss_keys)[at] = key;
-          else reinterpret_cast<int32_t*>(p.miss_keys)[at] = static_cast<int32_t>(key);
-        }
-      }
-    }
-  }
   const int n_cache = __popc(m_cache);
   const int total = n_cache + __popc(m_table);
   if (total == 0) return;

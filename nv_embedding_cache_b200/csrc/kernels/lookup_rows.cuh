@@ -40,34 +40,27 @@ struct GatherKernelParams {
   bool out_vec_ok;
 };
 
-constexpr int kGatherWarps = 4;
+// What phase 1 of every un-pooled lookup kernel leaves in each lane.
+struct ResolvedKey {
+  const uint8_t* row;   // source row of this lane's key, nullptr when skipped or unresolved
+  int64_t index;        // cache slot (set * 8 + way) or table row the pointer was made from
+  bool from_cache;
+  uint32_t m_cache;     // warp ballots: lanes served by the cache / by the backing table
+  uint32_t m_table;
+};
 
-// MODE: -1 raw byte copy, otherwise static_cast<int>(In) = decode and convert.
-template <int MODE, int VB, int GROUP, int VPL>
-__global__ void __launch_bounds__(kGatherWarps * 32) lookup_rows_kernel(const GatherKernelParams p) {
-  constexpr bool RAW = MODE < 0;
-  constexpr In IN = RAW ? In::F32 : static_cast<In>(RAW ? 0 : MODE);
-  constexpr bool QUANT = !RAW && (IN == In::I8 || IN == In::U8);
-  constexpr int EPV = RAW ? 1 : VB / InTraits<IN>::kElemBytes;
-  constexpr int R = 32 / GROUP;
-  constexpr int U = (VPL == 1) ? 8 : (VPL == 2 ? 4 : 2);
-
-  __shared__ uint64_t s_ptr[kGatherWarps][32];
-  __shared__ float s_scale[kGatherWarps][32];
-  __shared__ float s_qoff[kGatherWarps][32];
-  __shared__ uint8_t s_src[kGatherWarps][32];
-
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int64_t base = (static_cast<int64_t>(blockIdx.x) * kGatherWarps + warp) * 32;
-  if (base >= p.n) return;
+// Phase 1 for the 32 keys starting at `base` (one per lane, whole warp calls): skip keys whose
+// hit-mask bit is already set, probe the cache, fall back to the backing table (out-of-range keys
+// go to the default row when there is one), then publish the hit-mask word, the cache's miss
+// counter, the count of unresolved keys and the miss list with one atomic each per warp.
+__device__ __forceinline__ ResolvedKey resolve_keys(const GatherKernelParams& p, int64_t base, int lane) {
   const int64_t i = base + lane;
-
-  // ---- phase 1: resolve
   const uint32_t in_word = p.hit_mask ? p.hit_mask[base >> 5] : 0u;
   const bool active = (i < p.n) && !((in_word >> lane) & 1u);
-  const uint8_t* row = nullptr;
-  bool from_cache = false;
+  ResolvedKey r;
+  r.row = nullptr;
+  r.index = 0;
+  r.from_cache = false;
   bool cache_missed = false;
   int64_t key = 0;
   if (active) {
@@ -77,27 +70,31 @@ __global__ void __launch_bounds__(kGatherWarps * 32) lookup_rows_kernel(const Ga
       const int way = p.key64 ? probe_set<int64_t>(p.cache, key, &set)
                               : probe_set<int32_t>(p.cache, static_cast<int32_t>(key), &set);
       if (way >= 0) {
-        row = p.cache.cache_ptr + (static_cast<uint64_t>(set) * 8u + way) * p.cache.row_size;
-        from_cache = true;
+        r.index = static_cast<int64_t>(static_cast<uint64_t>(set) * 8u + way);
+        r.row = p.cache.cache_ptr + static_cast<uint64_t>(r.index) * p.cache.row_size;
+        r.from_cache = true;
       } else {
         cache_missed = true;
       }
     }
-    if (row == nullptr && p.table != nullptr) {
+    if (r.row == nullptr && p.table != nullptr) {
       int64_t k = key;
       const bool in_range = static_cast<uint64_t>(k) < static_cast<uint64_t>(p.num_rows);
       if (!in_range && p.default_row >= 0) k = p.default_row;
-      if (in_range || p.default_row >= 0) row = p.table + k * p.row_stride;
+      if (in_range || p.default_row >= 0) {
+        r.row = p.table + k * p.row_stride;
+        r.index = k;
+      }
     }
   }
-  const bool resolved = row != nullptr;
-  const uint32_t m_cache = __ballot_sync(0xffffffffu, resolved && from_cache);
-  const uint32_t m_table = __ballot_sync(0xffffffffu, resolved && !from_cache);
+  const bool resolved = r.row != nullptr;
+  r.m_cache = __ballot_sync(0xffffffffu, resolved && r.from_cache);
+  r.m_table = __ballot_sync(0xffffffffu, resolved && !r.from_cache);
   const uint32_t m_unres = __ballot_sync(0xffffffffu, active && !resolved);
   const uint32_t m_cmiss = __ballot_sync(0xffffffffu, cache_missed);
   const uint32_t lt = (1u << lane) - 1u;
 
-  if (p.hit_mask && lane == 0) p.hit_mask[base >> 5] = in_word | m_cache | m_table;
+  if (p.hit_mask && lane == 0) p.hit_mask[base >> 5] = in_word | r.m_cache | r.m_table;
   if (p.cache.enabled && p.cache.misses && m_cmiss && lane == 0) {
     atomicAdd(reinterpret_cast<unsigned long long*>(p.cache.misses),
               static_cast<unsigned long long>(__popc(m_cmiss)));
@@ -124,6 +121,39 @@ __global__ void __launch_bounds__(kGatherWarps * 32) lookup_rows_kernel(const Ga
       }
     }
   }
+  return r;
+}
+
+constexpr int kGatherWarps = 4;
+
+// MODE: -1 raw byte copy, otherwise static_cast<int>(In) = decode and convert.
+template <int MODE, int VB, int GROUP, int VPL>
+__global__ void __launch_bounds__(kGatherWarps * 32) lookup_rows_kernel(const GatherKernelParams p) {
+  constexpr bool RAW = MODE < 0;
+  constexpr In IN = RAW ? In::F32 : static_cast<In>(RAW ? 0 : MODE);
+  constexpr bool QUANT = !RAW && (IN == In::I8 || IN == In::U8);
+  constexpr int EPV = RAW ? 1 : VB / InTraits<IN>::kElemBytes;
+  constexpr int R = 32 / GROUP;
+  constexpr int U = (VPL == 1) ? 8 : (VPL == 2 ? 4 : 2);
+
+  __shared__ uint64_t s_ptr[kGatherWarps][32];
+  __shared__ float s_scale[kGatherWarps][32];
+  __shared__ float s_qoff[kGatherWarps][32];
+  __shared__ uint8_t s_src[kGatherWarps][32];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t base = (static_cast<int64_t>(blockIdx.x) * kGatherWarps + warp) * 32;
+  if (base >= p.n) return;
+
+  // ---- phase 1: resolve
+  const ResolvedKey r = resolve_keys(p, base, lane);
+  const uint8_t* row = r.row;
+  const bool from_cache = r.from_cache;
+  const bool resolved = r.row != nullptr;
+  const uint32_t m_cache = r.m_cache;
+  const uint32_t m_table = r.m_table;
+  const uint32_t lt = (1u << lane) - 1u;
   if (p.out == nullptr) return;
 
   // ---- schedule: cache-served rows first, then table-served rows

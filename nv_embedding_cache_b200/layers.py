@@ -130,8 +130,11 @@ class GpuTable:
     def __init__(self, cache_size: int, row_size_in_bytes: int, value_dtype, *,
                  key_type: int = capi.KEY_INT64, device_id: int = 0, uvm_table=None,
                  uvm_num_rows: int = 0, count_misses: bool = True,
-                 max_modify_size: int = 1 << 20, invalid_key: int = -1):
+                 max_modify_size: int = 1 << 20, invalid_key: int = -1,
+                 kernel_mode_type: int = 0, kernel_mode_value: int = 0):
         cfg = capi.lib.nve_gpu_table_config_default()
+        cfg.kernel_mode_type = kernel_mode_type     # 0 dynamic, 1 fused lookup, 2 sort-gather, 3 pipeline
+        cfg.kernel_mode_value = kernel_mode_value
         cfg.device_id = device_id
         cfg.cache_size = cache_size
         cfg.row_size_in_bytes = row_size_in_bytes

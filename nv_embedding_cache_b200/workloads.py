@@ -119,7 +119,27 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
             "host_link_gbs": misses * row_bytes / sec / 1e9,
             "host_link_frac_of_probe": misses * row_bytes / sec / 1e9 / link,
             "frac_of_hbm_peak": batch * (8 + 2 * row_bytes) / sec / 1e9 / peak, "peak_kind": kind}
+    res["schedules"] = _c3_schedules(gt, ctx, table, rows, row_bytes, batch, stream, steps, warmup)
     ctx.destroy(); layer.destroy(); gt.destroy()
+    # the pipeline schedule (host threads gather the missed rows): its own table, warmed the same way
+    gt = GpuTable(cache_bytes, row_bytes, "float16", uvm_table=table, uvm_num_rows=rows, kernel_mode_type=3)
+    ctx = gt.create_execution_context(stream.cuda_stream, stream.cuda_stream)
+    for b in range(20):
+        k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+        capi.check(capi.lib.nve_b200_gpu_table_insert_from_backing(gt.handle, ctx.handle, batch, k.data_ptr()))
+    ctx.wait()
+    res["pipeline_schedule"] = {}
+    for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(batch, rows, 1.2, 320 + 2 * b)),
+                           ("uniform", lambda b: dg.uniform_keys(batch, rows, 321 + 2 * b))):
+        keys_np = gen_keys(0)
+        batches = [torch.from_numpy(gen_keys(b)).cuda() for b in range(4)]
+        gt.find(ctx, batch, batches[0], None, row_bytes, out)
+        ctx.wait()
+        ok = bool(torch.equal(out.cpu(), table[torch.from_numpy(keys_np)]))
+        sec = _time_loop(stream, lambda i: gt.find(ctx, batch, batches[i % 4], None, row_bytes, out),
+                         min(steps, 20), 3)
+        res["pipeline_schedule"][name] = {"us_per_lookup": sec * 1e6, "byte_exact": ok}
+    ctx.destroy(); gt.destroy()
     if ref_gpu is not None:
         # the reference cache, warmed with the same insert sequence, serving the same batches
         rc = ref_gpu.cache(cache_bytes, row_bytes, max_modify=batch)
@@ -144,6 +164,50 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     if block is not None:
         block.close()
     return res
+
+
+def _c3_schedules(gt, ctx, table, rows, row_bytes, batch, stream, steps, warmup):
+    """The fused lookup kernel and the sort-gather schedule through the kernel-level C ABI on the warmed
+    cache of the C3 run: the configuration's batch and one eight times larger, Zipf and uniform keys."""
+    view = capi.CacheData()
+    capi.check(capi.lib.nve_b200_gpu_table_get_cache_data(gt.handle, ctx.handle, C.byref(view)))
+    out = {}
+    nb = 4
+    for n in (batch, 8 * batch):
+        rows_out = torch.empty((n, row_bytes), dtype=torch.uint8, device="cuda")
+        for name, gen_keys in (("zipf1.2", lambda b: dg.zipf_keys(n, rows, 1.2, 340 + 2 * b)),
+                               ("uniform", lambda b: dg.uniform_keys(n, rows, 341 + 2 * b))):
+            batches = [torch.from_numpy(gen_keys(b)).cuda() for b in range(nb)]
+            g = capi.GatherArgs()
+            g.table, g.num_rows, g.row_stride = table.data_ptr(), rows, row_bytes
+            g.value_dtype = g.output_dtype = capi.DTYPE_FLOAT16
+            g.default_row_index, g.cache, g.key_type = -1, C.pointer(view), capi.KEY_INT64
+            g.num_keys, g.output, g.output_stride, g.row_copy_bytes = n, rows_out.data_ptr(), row_bytes, row_bytes
+            need = C.c_size_t(0)
+            g.keys = batches[0].data_ptr()
+            capi.check(capi.lib.nve_b200_gather_rows_sorted(C.byref(g), 0, None, C.byref(need), None))
+            scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+            s = stream.cuda_stream
+
+            def fused(i):
+                g.keys = batches[i % nb].data_ptr()
+                capi.check(capi.lib.nve_b200_gather_rows(C.byref(g), s))
+
+            def ordered(i):
+                g.keys = batches[i % nb].data_ptr()
+                capi.check(capi.lib.nve_b200_gather_rows_sorted(C.byref(g), 0, scratch.data_ptr(), C.byref(need), s))
+            ordered(0)
+            stream.synchronize()
+            first = rows_out.clone()
+            fused(0)
+            stream.synchronize()
+            identical = bool(torch.equal(first, rows_out))
+            out[f"{name}_{n}"] = {"us_fused": _time_loop(stream, fused, steps, warmup) * 1e6,
+                                  "us_sort_gather": _time_loop(stream, ordered, steps, warmup) * 1e6,
+                                  "identical": identical}
+            del scratch
+        del rows_out
+    return out
 
 
 def _quant_table(rows, width, stride, seed):
