@@ -344,6 +344,29 @@ def run_ours(args):
         ms_dev, keys_dev, _, clocks = timed(step_device, args.steps, args.warmup, False)
         ms_e2e, keys_e2e, h2d, _ = timed(step_host, args.steps, args.warmup, True)
 
+    # ---- per-launch times outside the timed region (this rank): back-to-back launches, and launches
+    # that each follow a 256 MB write, which leaves nothing of the tables or keys in L2
+    def launch_times(flush):
+        scrub = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+        pairs = []
+        for i in range(3):
+            for t in range(NUM_TABLES):
+                if scrub is not None:
+                    scrub.fill_(i)
+                k, o = dev_batches[t][i % NUM_BATCHES]
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                layers[t].lookup_pooled(ctxs[t], k.numel(), k, dev_out[t], ROW_BYTES, "mean", "float16",
+                                        csr_offsets=o, num_csr_offsets=o.numel())
+                b.record(stream)
+                pairs.append((a, b))
+        torch.cuda.synchronize()
+        us = sorted(a.elapsed_time(b) * 1e3 for a, b in pairs[NUM_TABLES:])    # first round: warm-up
+        return {"median_us": us[len(us) // 2], "min_us": us[0], "launches": len(us)}
+
+    with torch.cuda.stream(stream):
+        per_launch = {"back_to_back": launch_times(False), "cold_l2": launch_times(True)}
+
     # ---- max over ranks, whole-job totals
     def reduce_max(x):
         if world == 1:
@@ -394,6 +417,7 @@ def run_ours(args):
         "gpu_launches": 2 * launches + 2 * args.warmup * NUM_TABLES,
         "roofline": roofline,
         "algo_bw_gib_s": value * ROW_BYTES / 2**30,
+        "per_launch": per_launch,
     }
 
     # ---- CPU baseline beside it (rank 0, N=1 only): reference HostEmbeddingLayer on table 0

@@ -157,6 +157,12 @@ NVE_C_API nve_status_t nve_b200_update_rows(void* table, int64_t num_rows, int64
  * Replaces EmbedCacheBase::get_cache_data (include/ecache/embed_cache.h, used as in
  * samples/ecache/simple_sample/simple_sample.cu:60-200).  `misses` points at the miss counter of
  * `ctx`.  The view stays valid while the table lives; tags change under insert / erase.
+ * Ordering against cache modifications: the call also makes the lookup stream of `ctx` wait for the
+ * tag invalidation of every modification enqueued so far, and later modifications wait for the work
+ * already on that stream before they overwrite rows.  So fetch the view, then launch the kernel on
+ * the lookup stream of `ctx`, with no modification of this table enqueued in between (the span the
+ * reference brackets with start_custom_flow / end_custom_flow, include/ecache/embed_cache.h:852-853).
+ * Device-side helpers for such kernels: nve_b200_ecache.cuh.
  */
 NVE_C_API nve_status_t nve_b200_gpu_table_get_cache_data(nve_table_t table, nve_context_t ctx,
                                                          nve_b200_cache_data_t* out);

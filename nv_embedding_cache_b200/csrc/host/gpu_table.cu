@@ -743,6 +743,10 @@ void gpu_table_cache_data(Table& table, ExecutionContext& ctx, nve_b200_cache_da
   auto* t = dynamic_cast<GpuTable*>(&table);
   if (!t) throw InvalidArgument("not a GPU cache table");
   *out = t->cache_view(ctx);
+  // a kernel the caller launches next on the context's lookup stream must see the tag invalidation
+  // of every modification enqueued so far, as the library's own lookups do
+  ScopedDevice sd(t->get_device_id());
+  t->order_lookup(ctx.lookup_stream());
 }
 
 void gpu_table_policy_state(Table& table, const float** counters, const int64_t** set_ts) {
