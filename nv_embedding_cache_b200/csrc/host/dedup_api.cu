@@ -23,6 +23,7 @@ struct nve_b200_deduper_s {
   int64_t bp_bags = 0;
   float* bp_bag_sum = nullptr;
   void* heavy = nullptr;       // scratch of the block-per-chunk gradient kernel
+  nve_b200::GradOverlap overlap;  // side stream of that kernel
 };
 
 namespace nve_b200 {
@@ -65,6 +66,9 @@ nve_status_t nve_b200_deduper_create(nve_b200_deduper_t* out, nve_key_type_t key
     NVE_B200_CUDA(cudaMalloc(&d->workspace, nve_b200::dedup_workspace_bytes(key_type, max_keys)));
     NVE_B200_CUDA(cudaMallocHost(&d->pinned, 16));
     NVE_B200_CUDA(cudaMalloc(&d->heavy, nve_b200::grad_heavy_scratch_bytes(max_keys)));
+    NVE_B200_CUDA(cudaStreamCreateWithFlags(&d->overlap.side, cudaStreamNonBlocking));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&d->overlap.fork, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&d->overlap.join, cudaEventDisableTiming));
     *out = d.release();
   });
 }
@@ -75,6 +79,9 @@ nve_status_t nve_b200_deduper_destroy(nve_b200_deduper_t d) {
   (void)cudaFreeHost(d->pinned);
   if (d->partial) (void)cudaFree(d->partial);
   if (d->heavy) (void)cudaFree(d->heavy);
+  if (d->overlap.side) (void)cudaStreamDestroy(d->overlap.side);
+  if (d->overlap.fork) (void)cudaEventDestroy(d->overlap.fork);
+  if (d->overlap.join) (void)cudaEventDestroy(d->overlap.join);
   if (d->bp_arrays) (void)cudaFree(d->bp_arrays);
   if (d->bp_bag_sum) (void)cudaFree(d->bp_bag_sum);
   (void)cudaGetLastError();
@@ -147,7 +154,7 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
         dst_stride, apply_to_table != 0, table_rows, alpha, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
         /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/false, d->heavy,
-        nve_b200::grad_heavy_capacity(d->capacity), static_cast<cudaStream_t>(stream));
+        nve_b200::grad_heavy_capacity(d->capacity), &d->overlap, static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -171,7 +178,7 @@ nve_status_t nve_b200_dedup_grads_f16(nve_b200_deduper_t d, const void* d_grads,
         dst_stride, /*fused=*/false, 0, 1.0f, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
         /*streamed=*/true, /*pos_weight=*/nullptr, /*f16=*/true, d->heavy,
-        nve_b200::grad_heavy_capacity(d->capacity), static_cast<cudaStream_t>(stream));
+        nve_b200::grad_heavy_capacity(d->capacity), &d->overlap, static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -246,7 +253,7 @@ nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, c
         /*fused=*/false, 0, 1.0f, d->partial,
         d->partial ? d->partial_rows * (d->partial_row_bytes / row_bytes) : 0, num_keys,
         /*streamed=*/true, need_w ? pos_w : nullptr, /*f16=*/false, d->heavy,
-        nve_b200::grad_heavy_capacity(d->capacity), s);
+        nve_b200::grad_heavy_capacity(d->capacity), &d->overlap, s);
     NVE_B200_CUDA(cudaStreamSynchronize(s));   // the number of unique keys is part of the return value
     *h_num_unique = kb == 8 ? static_cast<const int64_t*>(d->pinned)[0]
                             : static_cast<const int32_t*>(d->pinned)[0];

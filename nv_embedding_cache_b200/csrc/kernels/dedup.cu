@@ -247,6 +247,7 @@ struct GradParams {
   int32_t heavy_threshold;
   unsigned long long* heavy_count;
   int64_t heavy_capacity;
+  bool heavy_listed;         // the list was made beforehand (list_heavy_kernel): the streamed pass only skips
   bool idx64;
   bool fused;
   bool f16;                  // rows hold fp16 values, added in fp16 (un-fused, un-weighted form only)
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
   // microsecond whatever the ring depth: the copy instructions of a warp issue ~140 cycles apart).
   if (p.heavy_list != nullptr &&
       static_cast<int64_t>(offsets[ce]) - static_cast<int64_t>(offsets[ce - 1]) > p.heavy_threshold) {
-    if (lane == 0) {
+    if (lane == 0 && !p.heavy_listed) {
       const unsigned long long at = atomicAdd(p.heavy_count, 1ull);
       if (static_cast<int64_t>(at) < p.heavy_capacity) static_cast<IdxT*>(p.heavy_list)[at] = static_cast<IdxT>(ce - 1);
     }
@@ -780,8 +781,22 @@ bool grad_stream_eligible(const GradParams& p, bool allow) {
          p.grad_stride > 0 && p.grad_stride < (int64_t{1} << 32);
 }
 
+// The chunks grad_heavy_kernel takes, listed before either pass runs, so that the two passes can
+// run side by side: one thread per chunk.
 template <typename IdxT>
-void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
+__global__ void __launch_bounds__(256) list_heavy_kernel(const GradParams p) {
+  const IdxT* __restrict__ offsets = static_cast<const IdxT*>(p.offsets);
+  const int64_t C = static_cast<const IdxT*>(p.num_runs_dev)[1];
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (static_cast<int64_t>(offsets[c + 1]) - static_cast<int64_t>(offsets[c]) > p.heavy_threshold) {
+    const unsigned long long at = atomicAdd(p.heavy_count, 1ull);
+    if (static_cast<int64_t>(at) < p.heavy_capacity) static_cast<IdxT*>(p.heavy_list)[at] = static_cast<IdxT>(c);
+  }
+}
+
+template <typename IdxT>
+void launch_grad_stream(GradParams p, int64_t n, const GradOverlap* overlap, cudaStream_t s) {
   // rows per stage: 4 (a ring of 16 rows per warp; default, measured best on skewed and on all-distinct
   // batches alike) or 8 (32 rows, half the warps per SM)
   static const int forced = [] {
@@ -801,6 +816,24 @@ void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
   const unsigned grid = blocks_for(warps, kGsWarps);
   const int block = kGsWarps * 32;
   if (p.heavy_list) NVE_B200_CUDA(cudaMemsetAsync(p.heavy_count, 0, sizeof(unsigned long long), s));
+  // at most n / kHvThreshold chunks can be that long; blocks beyond the listed count leave at once
+  const unsigned hgrid = static_cast<unsigned>(std::min<int64_t>(n / kHvThreshold + 1, p.heavy_capacity));
+  const size_t hsmem = static_cast<size_t>(kHvStages) * kHvBatch * (row_bytes + (p.pos_weight ? 4 : 0));
+  auto heavy_pass = [&](cudaStream_t hs) {
+    if (p.pos_weight) grad_heavy_kernel<IdxT, true><<<hgrid, kHvWarps * 32, hsmem, hs>>>(p);
+    else grad_heavy_kernel<IdxT, false><<<hgrid, kHvWarps * 32, hsmem, hs>>>(p);
+  };
+  // With a side stream the long chunks are listed first and their pass is enqueued there, ahead of
+  // the streamed pass: the two touch different groups and run side by side.
+  const bool side_by_side = p.heavy_list != nullptr && overlap != nullptr && overlap->side != nullptr;
+  if (side_by_side) {
+    p.heavy_listed = true;
+    list_heavy_kernel<IdxT><<<blocks_for(p.max_chunks, 256), 256, 0, s>>>(p);
+    NVE_B200_CUDA(cudaEventRecord(overlap->fork, s));
+    NVE_B200_CUDA(cudaStreamWaitEvent(overlap->side, overlap->fork, 0));
+    heavy_pass(overlap->side);
+    NVE_B200_CUDA(cudaEventRecord(overlap->join, overlap->side));
+  }
   if (p.pos_weight) {
     if (batch == 4) grad_stream_kernel<IdxT, 4, true><<<grid, block, smem, s>>>(p, window);
     else grad_stream_kernel<IdxT, 8, true><<<grid, block, smem, s>>>(p, window);
@@ -808,13 +841,8 @@ void launch_grad_stream(const GradParams& p, int64_t n, cudaStream_t s) {
     if (batch == 4) grad_stream_kernel<IdxT, 4, false><<<grid, block, smem, s>>>(p, window);
     else grad_stream_kernel<IdxT, 8, false><<<grid, block, smem, s>>>(p, window);
   }
-  if (p.heavy_list) {
-    // at most n / kHvThreshold chunks can be that long; blocks beyond the listed count leave at once
-    const unsigned hgrid = static_cast<unsigned>(std::min<int64_t>(n / kHvThreshold + 1, p.heavy_capacity));
-    const size_t hsmem = static_cast<size_t>(kHvStages) * kHvBatch * (row_bytes + (p.pos_weight ? 4 : 0));
-    if (p.pos_weight) grad_heavy_kernel<IdxT, true><<<hgrid, kHvWarps * 32, hsmem, s>>>(p);
-    else grad_heavy_kernel<IdxT, false><<<hgrid, kHvWarps * 32, hsmem, s>>>(p);
-  }
+  if (side_by_side) NVE_B200_CUDA(cudaStreamWaitEvent(s, overlap->join, 0));
+  else if (p.heavy_list) heavy_pass(s);
 }
 
 // Second pass: split groups.  A warp scans 32 chunks (one per lane) for first chunks of split
@@ -1021,7 +1049,8 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
                      int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
-                     void* heavy_scratch, int64_t heavy_capacity, cudaStream_t stream) {
+                     void* heavy_scratch, int64_t heavy_capacity, const GradOverlap* overlap,
+                     cudaStream_t stream) {
   NVE_B200_ARG(!f16 || (!fused && pos_weight == nullptr),
                "dedup_grads: fp16 gradients are summed un-weighted into a gradient buffer only");
   NVE_B200_ARG(row_bytes > 0 && row_bytes % 16 == 0, "dedup_grads: rows must be a multiple of 16 bytes");
@@ -1060,8 +1089,13 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
   }();
   p.heavy_threshold = threshold;
   if (grad_stream_eligible(p, streamed)) {
-    if (p.idx64) launch_grad_stream<int64_t>(p, num_keys, stream);
-    else launch_grad_stream<int32_t>(p, num_keys, stream);
+    static const bool no_overlap = [] {
+      const char* e = std::getenv("NVE_B200_GRAD_OVERLAP");   // tuning knob: 0 runs the two passes in turn
+      return e != nullptr && e[0] == '0';
+    }();
+    const GradOverlap* ov = no_overlap ? nullptr : overlap;
+    if (p.idx64) launch_grad_stream<int64_t>(p, num_keys, ov, stream);
+    else launch_grad_stream<int32_t>(p, num_keys, ov, stream);
   } else {
     p.heavy_list = nullptr;
     launch_grad_first(p, stream);
@@ -1138,6 +1172,6 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
                     max_run_size > 0 ? d_loc_map : nullptr, d_unique, d_num_runs, max_chunks, d_dst,
                     dst_stride, apply_to_table != 0, table_rows, alpha, partial, partial_rows,
                     num_keys, /*streamed=*/false, /*pos_weight=*/nullptr, /*f16=*/false,
-                    /*heavy_scratch=*/nullptr, 0, static_cast<cudaStream_t>(stream));
+                    /*heavy_scratch=*/nullptr, 0, /*overlap=*/nullptr, static_cast<cudaStream_t>(stream));
   });
 }

@@ -16,13 +16,21 @@ void dedup_run(nve_key_type_t key_type, void* workspace, int64_t capacity, const
 // Device copy of {U, C} inside the workspace, for kernels that follow without a host round trip.
 const void* dedup_device_num_runs(nve_key_type_t key_type, void* workspace, int64_t capacity);
 
+// A side stream and two events (no timing) with which the gradient reduction runs its pass over
+// long chunks beside the streamed pass; owned by the caller, used by one reduction at a time.
+struct GradOverlap {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr;
+  cudaEvent_t join = nullptr;
+};
+
 // dst[u] = sum of grads rows of group u (fused == false), or
 // table[unique[u]] += alpha * sum (fused == true; dst is the table, keys outside
 // [0, table_rows) are skipped).  fp32 rows (or, with f16, fp16 rows added in fp16), 16-byte aligned.
 // pos_weight: optional weight per position of `inverse`: rows are multiplied by it before they are
 // added (one rounding each: multiply, then add).
 // heavy_scratch: device scratch of grad_heavy_scratch_bytes() (streamed form only; null keeps long
-// chunks in the streamed pass).
+// chunks in the streamed pass).  overlap: optional; without it the two passes run in turn on `stream`.
 // streamed: let rows of up to 512 bytes take the first pass that streams them through shared
 // memory with asynchronous copies; false keeps the register form for every width.
 void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_stride,
@@ -31,7 +39,8 @@ void dedup_grads_run(nve_key_type_t key_type, const void* grads, int64_t grad_st
                      int64_t max_chunks, void* dst, int64_t dst_stride, bool fused,
                      int64_t table_rows, float alpha, float* partial, int64_t partial_rows,
                      int64_t num_keys, bool streamed, const float* pos_weight, bool f16,
-                     void* heavy_scratch, int64_t heavy_capacity, cudaStream_t stream);
+                     void* heavy_scratch, int64_t heavy_capacity, const GradOverlap* overlap,
+                     cudaStream_t stream);
 
 // Bytes of `heavy_scratch` for batches of up to `capacity` keys (a counter and the ids of the chunks
 // that the streamed pass leaves to the block-per-chunk kernel), and how many ids that holds.
