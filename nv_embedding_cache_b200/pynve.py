@@ -147,22 +147,43 @@ class NVEmbedBinding:
     def pooling_backprop(self, num_keys: int, keys: int, grads: int, unique_keys: int, output_grads: int,
                          pooling_type: int, num_offsets: int, offsets: int, data_type: int = 0,
                          weights: int = 0, stream: int = 0) -> int:
-        """Backward of a pooled lookup (binding_layers.hpp:191-250): ``grads`` holds one fp32 row
-        per bag, ``offsets`` the int64 CSR offsets of ``num_offsets`` bags (``num_offsets + 1``
-        entries), ``weights`` optional fp32 per-key weights.  Writes the unique keys and, per unique
-        key, the weighted sum of the gradients of the bags it occurs in; returns the number of
-        unique keys."""
-        if self._dtype != DataType_t.Float32:
-            raise NotImplementedError("pooling_backprop is provided for Float32 gradients")
-        if weights and data_type not in (0, int(DataType_t.Float32)):
-            raise NotImplementedError("pooling_backprop takes Float32 weights")
+        """Backward of a pooled lookup (binding_layers.hpp:191-250): ``grads`` holds one row per bag
+        in the layer's data type, ``offsets`` the int64 CSR offsets of ``num_offsets`` bags
+        (``num_offsets + 1`` entries), ``weights`` optional per-key weights (``data_type``: Float32
+        or Float16).  Writes the unique keys and, per unique key, the weighted sum of the gradients
+        of the bags it occurs in; returns the number of unique keys.
+
+        Float32 layers with Float32 weights run on the caller's buffers.  Float16 gradients or
+        weights are widened to fp32, summed in fp32 and rounded to fp16 once at the end (the
+        reference multiplies and adds them in fp16: its sums carry one rounding per addition)."""
         self._ensure_deduper(num_keys)
         n_unique = C.c_int64(0)
-        capi.check(capi.lib.nve_b200_pooling_backprop(
-            self._deduper, num_keys, keys, grads, self._row_bytes, self._row_bytes, int(pooling_type),
-            capi.SPARSE_CSR, offsets, num_offsets, 0, weights or None, unique_keys, output_grads,
-            self._row_bytes, C.byref(n_unique), stream or None))
-        return int(n_unique.value)
+        half_rows = self._dtype != DataType_t.Float32
+        half_weights = bool(weights) and int(data_type) == int(DataType_t.Float16)
+        if not half_rows and not half_weights:
+            capi.check(capi.lib.nve_b200_pooling_backprop(
+                self._deduper, num_keys, keys, grads, self._row_bytes, self._row_bytes, int(pooling_type),
+                capi.SPARSE_CSR, offsets, num_offsets, 0, weights or None, unique_keys, output_grads,
+                self._row_bytes, C.byref(n_unique), stream or None))
+            return int(n_unique.value)
+        import torch
+        dev = torch.device("cuda", self._device)
+        width = self._row_elems
+        with torch.cuda.stream(torch.cuda.ExternalStream(stream, device=dev) if stream else
+                               torch.cuda.default_stream(dev)):
+            g = device_tensor(grads, (num_offsets, width), torch.float16 if half_rows else torch.float32, dev).float()
+            w = None
+            if weights:
+                w = device_tensor(weights, (num_keys,), torch.float16 if half_weights else torch.float32, dev).float()
+            out32 = torch.empty((num_keys, width), dtype=torch.float32, device=dev)
+            capi.check(capi.lib.nve_b200_pooling_backprop(
+                self._deduper, num_keys, keys, g.data_ptr(), width * 4, width * 4, int(pooling_type),
+                capi.SPARSE_CSR, offsets, num_offsets, 0, w.data_ptr() if w is not None else None, unique_keys,
+                out32.data_ptr(), width * 4, C.byref(n_unique), stream or None))
+            u = int(n_unique.value)
+            out = device_tensor(output_grads, (num_keys, width), torch.float16 if half_rows else torch.float32, dev)
+            out[:u].copy_(out32[:u])
+        return u
 
     def close(self) -> None:
         for ctx in self._ctx.values():
@@ -173,6 +194,76 @@ class NVEmbedBinding:
             capi.check(capi.lib.nve_b200_deduper_destroy(self._deduper))
             self._deduper = None
         self._layer.destroy()
+
+
+class _DevicePointer:
+    """Raw device address described through the CUDA array interface, so torch can wrap it."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+def device_tensor(ptr: int, shape, dtype, device):
+    """A torch tensor over device-accessible memory at ``ptr`` (no copy; the memory must outlive it)."""
+    import torch
+    typestr = {torch.float32: "<f4", torch.float16: "<f2", torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+    t = torch.as_tensor(_DevicePointer(ptr, shape, typestr), device=device)
+    if t.data_ptr() != int(ptr):
+        raise RuntimeError("memory at this address belongs to another device than the one asked for")
+    return t
+
+
+class MemBlock:
+    """Storage handed to a layer (reference MemBlock, include/memblock.hpp): an address, a size and
+    a type name.  The owner of the memory keeps it alive for as long as the layer lives."""
+
+    TYPE = "User"
+
+    def __init__(self, ptr: int, size_in_bytes: int):
+        self._ptr = int(ptr)
+        self._size = int(size_in_bytes)
+
+    def get_ptr(self) -> int:
+        return self._ptr
+
+    def get_handle(self) -> int:
+        return self._ptr
+
+    def get_size_in_bytes(self) -> int:
+        return self._size
+
+    def get_type(self) -> str:
+        return self.TYPE
+
+    def data_ptr(self) -> int:
+        return self._ptr
+
+
+class UserMemBlock(MemBlock):
+    """Memory the caller owns: ``UserMemBlock(tensor.data_ptr(), tensor.nbytes)``."""
+
+
+class ManagedMemBlock(MemBlock):
+    """Managed memory kept on the host and mapped into the listed GPUs, with the reference binding's
+    signature: ``ManagedMemBlock(row_size, num_embeddings, data_type, gpu_ids)``."""
+
+    TYPE = "Managed"
+
+    def __init__(self, row_size: int, num_embeddings: int, data_type: DataType_t, gpu_ids=(0,)):
+        from .memblock import ManagedMemBlock as _Block
+        elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
+        self._block = _Block(row_size * num_embeddings * elem, tuple(gpu_ids))
+        super().__init__(self._block.get_ptr(), self._block.get_size_in_bytes())
+
+    def copy_from(self, src) -> None:
+        self._block.copy_from(src)
+
+    def as_tensor(self, shape, dtype):
+        return self._block.as_tensor(shape, dtype)
+
+    def close(self) -> None:
+        self._block.close()
 
 
 def _address(memblock) -> int:
@@ -205,10 +296,24 @@ class LinearUVMEmbedding(NVEmbedBinding):
         self._memblock = memblock
         self._table = GpuTable(gpu_cache_size, row_size * elem, int(data_type), device_id=device_id,
                                uvm_table=_address(memblock), uvm_num_rows=num_embeddings,
-                               max_modify_size=config.max_modify_size)
+                               max_modify_size=config.max_modify_size,
+                               kernel_mode_type=config.kernel_mode,
+                               kernel_mode_value=self._kernel_mode_value(config))
         layer = LinearUVMEmbeddingLayer(self._table, default_row_index=config.default_row_index,
                                         insert_heuristic=getattr(config, "insert_heuristic", "default"))
         super().__init__(layer, row_size, data_type, device_id)
+
+    def _kernel_mode_value(self, config: EmbedLayerConfig) -> int:
+        """kernel_mode_value of the table from the two config values (binding_layers.hpp:569-580):
+        sort-gather takes the tile size, pipeline gather the address of {task_size, aux streams}."""
+        if config.kernel_mode == 2:
+            return config.kernel_mode_value_1 if config.kernel_mode_value_1 > 0 else 1024
+        if config.kernel_mode == 3:
+            self._pipeline_params = (C.c_uint64 * 2)(
+                config.kernel_mode_value_1 if config.kernel_mode_value_1 > 0 else 1024,
+                config.kernel_mode_value_2 if config.kernel_mode_value_2 > 0 else 16)
+            return C.addressof(self._pipeline_params)
+        return config.kernel_mode_value_1
 
     def close(self) -> None:
         super().close()

@@ -1,0 +1,337 @@
+"""torch.nn modules over the lookup path, with the names and arguments of the reference's
+``pynve.torch.nve_layers`` (python/pynve/torch/nve_layers.py:110-556): ``LayerType``,
+``NVEmbedding`` (torch.nn.Embedding-like) and ``NVEmbeddingBag`` (torch.nn.EmbeddingBag-like, CSR
+offsets with the trailing sentinel), trainable with any torch optimizer that handles sparse
+gradients.  Forward and backward run through the pynve-named edge (``pynve.py``) and so through the
+C ABI of the library; the autograd functions are those of the reference's plain-Python path
+(``CacheEmbeddingOp`` / ``CacheEmbeddingBagOp``, python/pynve/torch/nve_ops.py:229-316).
+
+Provided layer types: ``GPULayer`` (dense table in HBM) and ``LinearUVM`` (GPU cache in front of a
+host-resident table).  ``Hierarchical`` and ``HostLayer`` need host tables and parameter servers,
+which are outside this library: they raise NotImplementedError.
+"""
+from __future__ import annotations
+
+import builtins
+from enum import Enum
+from typing import Optional
+
+import torch
+
+from . import pynve as nve
+
+
+def nve_type_to_torch_type(nve_type):
+    if nve_type == nve.DataType_t.Float32:
+        return torch.float32
+    if nve_type == nve.DataType_t.Float16:
+        return torch.float16
+    raise ValueError(f"Invalid data type: {nve_type}")
+
+
+def torch_type_to_nve_type(torch_type: torch.dtype):
+    if torch_type == torch.float32:
+        return nve.DataType_t.Float32
+    if torch_type == torch.float16:
+        return nve.DataType_t.Float16
+    raise ValueError(f"Invalid data type: {torch_type}")
+
+
+def pooling_type_from_mode(mode: str, weighted: bool):
+    """'sum' / 'mean' (weighted forms with per-sample weights); 'concat' is handled by the caller
+    and 'max' does not exist (reference nve_ops.py:32-48)."""
+    if mode == "sum":
+        return nve.PoolingType_t.WeightedSum if weighted else nve.PoolingType_t.Sum
+    if mode == "mean":
+        return nve.PoolingType_t.WeightedMean if weighted else nve.PoolingType_t.Mean
+    raise ValueError(f"Unsupported pooling mode {mode!r}; expected 'sum' or 'mean' "
+                     "('concat' is handled separately). 'max' pooling is not implemented.")
+
+
+def _check_forward_inputs(keys, offsets=None, per_sample_weights=None):
+    """The binding takes raw addresses, so wrong dtypes or strided views would be misread
+    (reference nve_layers.py:42-71)."""
+    if keys.dtype != torch.int64:
+        raise TypeError(f"keys must be an int64 tensor, got {keys.dtype}")
+    if not keys.is_contiguous():
+        raise ValueError("keys must be contiguous")
+    if offsets is not None:
+        if offsets.dtype != torch.int64:
+            raise TypeError(f"offsets must be an int64 tensor, got {offsets.dtype}")
+        if not offsets.is_contiguous():
+            raise ValueError("offsets must be contiguous")
+        if offsets.numel() < 2:
+            raise ValueError("offsets must have at least two entries (num_bags + 1, "
+                             "include_last_offset=True convention)")
+    if per_sample_weights is not None:
+        if per_sample_weights.dtype not in (torch.float32, torch.float16):
+            raise TypeError(f"per_sample_weights must be a float32 or float16 tensor, "
+                            f"got {per_sample_weights.dtype}")
+        if not per_sample_weights.is_contiguous():
+            raise ValueError("per_sample_weights must be contiguous")
+        if per_sample_weights.numel() != keys.numel():
+            raise ValueError(f"per_sample_weights must have one element per key: "
+                             f"got {per_sample_weights.numel()} weights for {keys.numel()} keys")
+
+
+def _stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def config_to_nve_config(config: Optional[dict]):
+    cfg = nve.EmbedLayerConfig()
+    if config is None:
+        return cfg
+    for name in ("kernel_mode", "logging_interval", "kernel_mode_value_1", "kernel_mode_value_2",
+                 "max_modify_size", "default_row_index", "insert_heuristic"):
+        if name in config:
+            setattr(cfg, name, config[name])
+    if "default_embedding" in config:
+        raise ValueError("config['default_embedding'] is only supported for HostLayer and Hierarchical layers")
+    return cfg
+
+
+class LayerType(Enum):
+    GPULayer = 1
+    LinearUVM = 2
+    Hierarchical = 3
+    HostLayer = 4
+
+
+class CachedTable(torch.nn.parameter.Parameter):
+    """The weight of a layer: a Parameter that carries the layer object, so that an optimizer's
+    in-place sparse update goes to the cache and the table through the layer
+    (reference nve_tensors.py:19-76)."""
+
+    def __new__(cls, *args, **kwargs):
+        if "cache" not in kwargs:
+            raise Exception("building a CachedTable Tensor require a viable cache argument")
+        cache = kwargs.pop("cache")
+        instance = super().__new__(cls, *args, **kwargs)
+        instance.emb_layer = cache
+        return instance
+
+    def __getstate__(self):
+        state = dict(self.__dict__)
+        state["emb_layer"] = None        # a native handle: not part of a pickled state
+        return state
+
+    def add_(self, other: torch.Tensor, *, alpha: float = 1):
+        """What SGD calls with the sparse gradient: rows ``other * alpha`` are accumulated into
+        the table (and the cached copies) by the layer."""
+        factored = (other * alpha).coalesce() if other.is_sparse else None
+        if factored is None:
+            raise TypeError("CachedTable.add_ takes a sparse gradient")
+        values = factored._values().contiguous()
+        keys = factored._indices().reshape(-1).contiguous()
+        self.emb_layer.accumulate(keys.numel(), keys.data_ptr(), values.data_ptr(),
+                                  _stream_handle(values.device))
+        return self
+
+
+class CacheEmbeddingOp(torch.autograd.Function):
+    """Un-pooled lookup; backward = unique keys + per-key gradient sums as a sparse gradient."""
+
+    @staticmethod
+    def forward(keys: torch.Tensor, weight: CachedTable):
+        result = torch.empty(keys.numel(), weight.shape[-1], dtype=weight.dtype, device=keys.device)
+        weight.emb_layer.lookup(keys.numel(), keys.data_ptr(), result.data_ptr(), _stream_handle(keys.device))
+        return result
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        keys, weight = inputs
+        ctx.save_for_backward(keys, weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        keys, weight = ctx.saved_tensors
+        num_keys = keys.numel()
+        grad_output = grad_output.contiguous()
+        unique_keys = torch.empty(num_keys, dtype=torch.int64, device=keys.device)
+        result = torch.empty(num_keys, grad_output.shape[-1], dtype=grad_output.dtype, device=keys.device)
+        num_unique = weight.emb_layer.concat_backprop(num_keys, keys.data_ptr(), grad_output.data_ptr(),
+                                                      unique_keys.data_ptr(), result.data_ptr(),
+                                                      _stream_handle(keys.device))
+        # unique keys come out sorted and distinct: the gradient is coalesced as built
+        return None, torch.sparse_coo_tensor(unique_keys[:num_unique].reshape(1, -1), result[:num_unique],
+                                             weight.shape, device=weight.device, check_invariants=False,
+                                             is_coalesced=True)
+
+
+def _weight_type(per_sample_weights):
+    if per_sample_weights is None or per_sample_weights.dtype == torch.float32:
+        return nve.DataType_t.Float32
+    return nve.DataType_t.Float16
+
+
+class CacheEmbeddingBagOp(torch.autograd.Function):
+    """Pooled lookup over CSR bags; backward = pooled backward as a sparse gradient."""
+
+    @staticmethod
+    def forward(keys, weight: CachedTable, offsets, mode: str, per_sample_weights):
+        result = torch.empty(offsets.numel() - 1, weight.shape[-1], dtype=weight.dtype, device=keys.device)
+        pool = pooling_type_from_mode(mode, weighted=per_sample_weights is not None)
+        weight.emb_layer.lookup_with_pooling(
+            keys.numel(), keys.data_ptr(), result.data_ptr(), int(pool), offsets.numel(), offsets.data_ptr(),
+            int(_weight_type(per_sample_weights)),
+            per_sample_weights.data_ptr() if per_sample_weights is not None else 0, _stream_handle(keys.device))
+        return result
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        keys, weight, offsets, mode, per_sample_weights = inputs
+        ctx.mode = mode
+        ctx.save_for_backward(keys, weight, offsets, per_sample_weights)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        keys, weight, offsets, per_sample_weights = ctx.saved_tensors
+        num_keys = keys.numel()
+        grad_output = grad_output.contiguous()
+        unique_keys = torch.empty(num_keys, dtype=torch.int64, device=keys.device)
+        result = torch.empty(num_keys, grad_output.shape[-1], dtype=grad_output.dtype, device=keys.device)
+        pool = pooling_type_from_mode(ctx.mode, weighted=per_sample_weights is not None)
+        num_unique = weight.emb_layer.pooling_backprop(
+            num_keys, keys.data_ptr(), grad_output.data_ptr(), unique_keys.data_ptr(), result.data_ptr(),
+            int(pool), offsets.numel() - 1, offsets.data_ptr(), int(_weight_type(per_sample_weights)),
+            per_sample_weights.data_ptr() if per_sample_weights is not None else 0, _stream_handle(keys.device))
+        grad = torch.sparse_coo_tensor(unique_keys[:num_unique].reshape(1, -1), result[:num_unique],
+                                       weight.shape, device=weight.device, check_invariants=False,
+                                       is_coalesced=True)
+        return None, grad, None, None, None
+
+
+class NVEmbeddingBase(torch.nn.Module):
+    """Common part of NVEmbedding / NVEmbeddingBag (reference NVEmbeddingBase, nve_layers.py:124-401):
+    builds the storage, the layer object and the ``weight`` Parameter that ties them together.
+
+    Arguments as in the reference.  ``storage``: a ``pynve.MemBlock`` (``UserMemBlock`` around memory
+    the caller owns, ``ManagedMemBlock``) or None, in which case a CUDA tensor (GPULayer) or a
+    managed block (LinearUVM) is allocated.  ``weight`` must not be used after the module is gone."""
+
+    def __init__(self, num_embeddings: int, embedding_size: int, data_type: torch.dtype, layer_type: LayerType, *,
+                 gpu_cache_size: int = 0, host_cache_size: int = 0, storage=None,
+                 weight_init: Optional[torch.Tensor] = None, optimize_for_training: bool = True,
+                 device: Optional[torch.device] = None, id: Optional[int] = None, config: Optional[dict] = None):
+        super().__init__()
+        self.config = config_to_nve_config(config)
+        self.layer_type = layer_type
+        self.num_embeddings = num_embeddings
+        self.embedding_size = embedding_size
+        self.data_type = data_type
+        self.layer_data_type = torch_type_to_nve_type(data_type)
+        self.gpu_cache_size = gpu_cache_size
+        self.host_cache_size = host_cache_size
+        self.optimize_for_training = optimize_for_training
+        self.device = torch.device(device) if device is not None else torch.device("cuda")
+        if self.device.type != "cuda":
+            raise ValueError(f"NV Embedding layers of this library run on cuda devices, got {self.device.type}")
+        self.device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.device = torch.device("cuda", self.device_index)
+        self.id = id if id is not None else builtins.id(self)
+        if storage is not None and not isinstance(storage, nve.MemBlock):
+            raise ValueError(f"{layer_type.name} requires storage to be a MemBlock or None")
+
+        if layer_type == LayerType.GPULayer:
+            if storage is None:
+                if weight_init is not None:
+                    tensor_storage = weight_init.detach().clone().to(device=self.device, dtype=data_type).contiguous()
+                else:
+                    tensor_storage = torch.empty(num_embeddings, embedding_size, dtype=data_type, device=self.device)
+                storage = nve.UserMemBlock(tensor_storage.data_ptr(), tensor_storage.nbytes)
+            else:
+                tensor_storage = nve.device_tensor(storage.get_ptr(), (num_embeddings, embedding_size), data_type,
+                                                   self.device)
+                if weight_init is not None:
+                    tensor_storage.copy_(weight_init)
+            self._keep = tensor_storage
+            self.emb_layer = nve.GPUEmbedding(embedding_size, num_embeddings, self.layer_data_type, storage,
+                                              self.device_index, self.config)
+            self.table_ids = {0: "gpu"}
+        elif layer_type == LayerType.LinearUVM:
+            if gpu_cache_size == 0:
+                raise ValueError("GPU cache size > 0 is required for UVM embedding")
+            if storage is None:
+                storage = nve.ManagedMemBlock(embedding_size, num_embeddings, self.layer_data_type, [self.device_index])
+            # the table lives in host-resident memory that the GPU maps: seen from torch as a CUDA tensor
+            tensor_storage = nve.device_tensor(storage.get_ptr(), (num_embeddings, embedding_size), data_type,
+                                               self.device)
+            if weight_init is not None:
+                tensor_storage.copy_(weight_init)
+                torch.cuda.synchronize(self.device)
+            self.emb_layer = nve.LinearUVMEmbedding(embedding_size, num_embeddings, self.layer_data_type, storage,
+                                                    gpu_cache_size, optimize_for_training, self.device_index,
+                                                    self.config)
+            self.table_ids = {0: "gpu_cache"}
+        elif layer_type in (LayerType.Hierarchical, LayerType.HostLayer):
+            raise NotImplementedError(f"{layer_type.name}: host tables and parameter servers are outside this library")
+        else:
+            raise ValueError(f"Unknown layer_type: {layer_type}")
+        self.storage = storage
+        self.memblock_type = storage.get_type()
+        self.weight = CachedTable(tensor_storage, cache=self.emb_layer)
+
+    def __del__(self):
+        layer = getattr(self, "emb_layer", None)
+        if layer is not None:
+            try:
+                layer.close()
+            except Exception:
+                pass
+            self.emb_layer = None
+
+    def to(self, *args, **kwargs):
+        """The table and its cache stay where they were built; other parameters and buffers move."""
+        device, dtype, non_blocking, _ = torch._C._nn._parse_to(*args, **kwargs)
+        for name, param in self.named_parameters():
+            if name != "weight":
+                param.data = param.data.to(device, dtype if dtype else param.dtype, non_blocking)
+        for _, buf in self.named_buffers():
+            buf.data = buf.data.to(device, dtype if dtype else buf.dtype, non_blocking)
+        return self
+
+    def update(self, keys: torch.Tensor, updates: torch.Tensor):
+        """Overwrite rows (asynchronous on the current stream)."""
+        self.emb_layer.update(keys.numel(), keys.data_ptr(), updates.data_ptr(), _stream_handle(self.device))
+
+    def insert(self, keys: torch.Tensor, values: torch.Tensor, table_id: int):
+        """Best-effort insert of rows into the cache table ``table_id``."""
+        self.emb_layer.insert(keys.numel(), keys.data_ptr(), values.data_ptr(), table_id, _stream_handle(self.device))
+
+    def clear(self):
+        self.emb_layer.clear(_stream_handle(self.device))
+
+    def erase(self, keys: torch.Tensor, table_id: int):
+        self.emb_layer.erase(keys.numel(), keys.data_ptr(), table_id, _stream_handle(self.device))
+
+    def load_from_stream(self, stream):
+        raise NotImplementedError("weight files are outside this library")
+
+
+class NVEmbedding(NVEmbeddingBase):
+    """torch.nn.Embedding-like layer (reference NVEmbedding, nve_layers.py:403-461)."""
+
+    def forward(self, keys: torch.Tensor):
+        _check_forward_inputs(keys)
+        return CacheEmbeddingOp.apply(keys, self.weight)
+
+
+class NVEmbeddingBag(NVEmbeddingBase):
+    """torch.nn.EmbeddingBag-like layer with mode 'sum', 'mean' or 'concat' (reference NVEmbeddingBag,
+    nve_layers.py:463-556).  Offsets follow ``include_last_offset=True``: num_bags + 1 entries that
+    start at 0 and end with ``len(input)``."""
+
+    def __init__(self, num_embeddings: int, embedding_size: int, data_type: torch.dtype, layer_type: LayerType,
+                 mode: str, **kwargs):
+        if mode != "concat":
+            pooling_type_from_mode(mode, weighted=False)      # fail fast on unsupported modes
+        super().__init__(num_embeddings, embedding_size, data_type, layer_type, **kwargs)
+        self.mode = mode
+
+    def forward(self, input: torch.Tensor, offsets: torch.Tensor,
+                per_sample_weights: Optional[torch.Tensor] = None):
+        _check_forward_inputs(input, offsets, per_sample_weights)
+        if self.mode == "concat":
+            return CacheEmbeddingOp.apply(input, self.weight)
+        return CacheEmbeddingBagOp.apply(input, self.weight, offsets, self.mode, per_sample_weights)
