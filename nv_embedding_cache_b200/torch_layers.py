@@ -306,7 +306,25 @@ class NVEmbeddingBase(torch.nn.Module):
         self.emb_layer.erase(keys.numel(), keys.data_ptr(), table_id, _stream_handle(self.device))
 
     def load_from_stream(self, stream):
-        raise NotImplementedError("weight files are outside this library")
+        """Loads this layer's table (the tensor named ``self.id``) from a ``.nve`` stream opened for
+        binary reading (reference load_tensor_from_stream); cached copies of the old rows are dropped."""
+        import numpy as np
+        from . import weight_files
+        host = np.empty((self.num_embeddings, self.embedding_size),
+                        dtype=np.float32 if self.data_type == torch.float32 else np.float16)
+        if not weight_files.read_tensor(stream, self.id, host):
+            raise KeyError(f"the file holds no tensor named {self.id}")
+        with torch.no_grad():
+            self.weight.data.copy_(torch.from_numpy(host))
+        if self.layer_type == LayerType.LinearUVM:
+            self.clear()
+        torch.cuda.synchronize(self.device)
+
+    def save_to_stream(self, stream):
+        """Appends this layer's table to a ``.nve`` stream (after ``weight_files.write_header``)."""
+        from . import weight_files
+        torch.cuda.synchronize(self.device)
+        weight_files.write_tensor(stream, self.id, self.weight.detach().cpu().numpy())
 
 
 class NVEmbedding(NVEmbeddingBase):

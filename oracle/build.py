@@ -1,6 +1,6 @@
 """Build recipe for the parity checker (test infrastructure, not the product).
 
-Three artefacts, all written under ``oracle/_ref/`` (git-ignored, shipped to the GPU box as built):
+Four artefacts, all written under ``oracle/_ref/`` (git-ignored, shipped to the GPU box as built):
 
 * ``libnve_oracle.so``  – the plain-C restatement in ``oracle/nve_oracle.c`` (always built).
 * ``libnve_ref.so``     – the UNMODIFIED reference CPU path (HostEmbeddingLayer, LinearHostTable,
@@ -10,6 +10,10 @@ Three artefacts, all written under ``oracle/_ref/`` (git-ignored, shipped to the
   modify, GPU histogram, Deduper, gradient de-duplication, find_and_combine) compiled by nvcc for
   sm_100a from the reference checkout, wrapped by ``oracle/ref_gpu_driver.cu``.  Same rule: built
   only where the checkout is present.
+
+* ``libnve_ref_ser.so`` – the UNMODIFIED reference weight-file code (``src/serialization.cpp``: the
+  .nve container, the numpy and raw-binary table loaders), wrapped by
+  ``oracle/ref_serialization_driver.cpp``.  Same rule.
 
 No reference source is copied: the compiler reads the files where they lie.
 """
@@ -137,13 +141,37 @@ def build_reference_gpu(verbose: bool = False) -> Path | None:
     return out
 
 
+def build_reference_serialization(verbose: bool = False) -> Path | None:
+    """Compile the reference weight-file code (src/serialization.cpp) with g++ behind
+    ``oracle/ref_serialization_driver.cpp`` (only where the checkout exists)."""
+    OUT.mkdir(exist_ok=True)
+    out = OUT / "libnve_ref_ser.so"
+    if not (REFERENCE / "src" / "serialization.cpp").exists():
+        return out if out.exists() else None
+    driver = HERE / "ref_serialization_driver.cpp"
+    if _newer(out, [driver]):
+        return out
+    nl, shim = _shim_and_json()
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-w", *REF_DEFINES,
+           f"-I{REFERENCE}", f"-I{REFERENCE / 'include'}", f"-I{cuda_inc}", f"-I{nl}", f"-I{shim}",
+           str(driver), str(REFERENCE / "src" / "serialization.cpp"), str(REFERENCE / "src" / "common.cpp"),
+           "-o", str(out)]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return out
+
+
 def build_all(verbose: bool = False):
-    return build_oracle(verbose), build_reference(verbose), build_reference_gpu(verbose)
+    return (build_oracle(verbose), build_reference(verbose), build_reference_gpu(verbose),
+            build_reference_serialization(verbose))
 
 
 if __name__ == "__main__":
-    o, r, g = build_all(verbose=True)
+    o, r, g, w = build_all(verbose=True)
     print("oracle:", o)
     print("reference:", r)
     print("reference (GPU):", g)
+    print("reference (weight files):", w)
     sys.exit(0)

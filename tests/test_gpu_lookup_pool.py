@@ -19,8 +19,10 @@ CONCAT = sorted(n for n, c in CASES.items() if c["op"] == "pooled" and c["poolin
 
 
 def run_pool_kernel(capi, torch, case, *, key_dtype=np.int64, off_dtype=np.int64, out=None,
-                    default_row=-1, table_dev=None):
+                    default_row=-1, table_dev=None, gathered=False):
     table = case["table"]
+    if gathered:            # rows already gathered in key order: pooled with keys == NULL
+        table = np.ascontiguousarray(table[case["keys"]])
     t_dev = to_dev(torch, table) if table_dev is None else table_dev
     keys = to_dev(torch, case["keys"].astype(key_dtype))
     offs = None if case["offsets"] is None else to_dev(torch, case["offsets"].astype(off_dtype))
@@ -39,7 +41,7 @@ def run_pool_kernel(capi, torch, case, *, key_dtype=np.int64, off_dtype=np.int64
     a.default_row_index = default_row
     a.cache = None
     a.key_type = capi.KEY_INT64 if key_dtype == np.int64 else capi.KEY_INT32
-    a.keys = ptr(keys)
+    a.keys = None if gathered else ptr(keys)
     a.num_keys = case["keys"].size
     a.pooling_type = POOL[case["pooling"]]
     a.sparse_type = capi.SPARSE_CSR if offs is not None else capi.SPARSE_FIXED
@@ -66,6 +68,16 @@ def test_kernel_matches_golden_bit_for_bit(capi, torch_cuda, name):
     want = GOLDEN[name]
     assert rel_err(got, want) <= 1e-5  # the stated tolerance
     assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+@pytest.mark.parametrize("name", POOLED)
+def test_pooling_of_gathered_rows(capi, torch_cuda, name):
+    """keys == NULL pools rows that an earlier step gathered (the last step of a multi-tier lookup,
+    the reference's pool_gathered_device): same bits as the fused lookup."""
+    got = run_pool_kernel(capi, torch_cuda, CASES[name], gathered=True)
+    assert np.array_equal(got.view(np.uint8), GOLDEN[name].view(np.uint8))
+    got = run_pool_kernel(capi, torch_cuda, CASES[name], gathered=True, key_dtype=np.int32, off_dtype=np.int32)
+    assert np.array_equal(got.view(np.uint8), GOLDEN[name].view(np.uint8))
 
 
 @pytest.mark.parametrize("name", POOLED[:6])

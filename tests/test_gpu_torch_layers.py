@@ -145,3 +145,33 @@ def test_bag_fp16_concat_and_modify_calls(torch_cuda):
     with pytest.raises(ValueError):
         L.NVEmbedding(n, d, torch.float32, L.LayerType.LinearUVM)
     del bag, cat, layer
+
+
+@pytest.mark.gpu
+def test_layers_save_and_load_weight_files(torch_cuda, tmp_path):
+    """Two layers written to one .nve file and read back into fresh layers by id, as the reference's
+    multi-layer load test does; the cached layer must not serve rows it cached before the load."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200 import torch_layers as L, weight_files
+    n, d = 3000, 8
+    a = L.NVEmbedding(n, d, torch.float32, L.LayerType.GPULayer, weight_init=torch.randn(n, d), id=1)
+    b = L.NVEmbedding(n, d, torch.float16, L.LayerType.LinearUVM, gpu_cache_size=1 << 20,
+                      weight_init=torch.randn(n, d).half(), id=2, optimize_for_training=False)
+    path = tmp_path / "model.nve"
+    with open(path, "wb+") as f:
+        weight_files.write_header(f)
+        a.save_to_stream(f)
+        b.save_to_stream(f)
+    a2 = L.NVEmbedding(n, d, torch.float32, L.LayerType.GPULayer, id=1)
+    b2 = L.NVEmbedding(n, d, torch.float16, L.LayerType.LinearUVM, gpu_cache_size=1 << 20, id=2,
+                       weight_init=torch.zeros(n, d).half(), optimize_for_training=False)
+    keys = torch.arange(0, n, 7, dtype=torch.int64, device="cuda")
+    b2.insert(keys, b2(keys), 0)                  # stale rows (zeros) in the cache before the load
+    with open(path, "rb") as f:
+        b2.load_from_stream(f)
+        a2.load_from_stream(f)
+    assert torch.equal(a2(keys), a(keys)) and torch.equal(b2(keys), b(keys))
+    assert torch.equal(a2.weight.detach(), a.weight.detach())
+    with open(path, "rb") as f, pytest.raises(KeyError):
+        L.NVEmbedding(n, d, torch.float32, L.LayerType.GPULayer, id=3).load_from_stream(f)
+    del a, b, a2, b2
