@@ -36,6 +36,41 @@ import torch.distributed as dist
 from . import capi
 
 
+class PeerLeft(RuntimeError):
+    """A rank of the group announced that it left: lookups that need it are refused."""
+
+
+class ExchangeFailed(RuntimeError):
+    """A collective of the exchange form ended with an error (a peer died, a timeout ran out).  The
+    table refuses further lookups: its process group is no longer usable."""
+
+
+class PeerMonitor:
+    """Membership of the ranks serving a sharded table, kept on the host in a torch.distributed
+    store (TCPStore, FileStore, HashStore).  A rank that leaves between two steps, with none of
+    its kernels or collectives in flight, calls :meth:`announce_leave`; the others call
+    :meth:`check` before they launch their next lookup and get :class:`PeerLeft` instead of a
+    collective that can never complete or a read of memory that is gone.  A rank that dies without
+    announcing it is caught by the process group's timeout (see :class:`ExchangeFailed`)."""
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "nve_b200/sharded"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def _key(self, rank: int) -> str:
+        return f"{self.prefix}/left/{rank}"
+
+    def announce_leave(self) -> None:
+        self.store.set(self._key(self.rank), b"1")
+
+    def departed(self):
+        return [r for r in range(self.world) if r != self.rank and self.store.check([self._key(r)])]
+
+    def check(self) -> None:
+        gone = self.departed()
+        if gone:
+            raise PeerLeft(f"rank(s) {gone} left the group that serves this table")
+
+
 def _split_list(t: torch.Tensor):
     return [int(x) for x in t.cpu().tolist()]
 
@@ -161,8 +196,10 @@ class ShardedEmbeddingTable:
     POOLING = {"sum": capi.POOL_SUM, "mean": capi.POOL_MEAN}
 
     def __init__(self, local_shard: torch.Tensor, *, max_keys: int, group=None, stages=None,
-                 mode: str = "alltoall", cache_bytes: int = 0):
+                 mode: str = "alltoall", cache_bytes: int = 0, monitor: PeerMonitor | None = None):
         self.group = group
+        self.monitor = monitor       # optional host-side membership check before every lookup
+        self.failed = None           # the error that ended the exchange form, once one has
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.shard = local_shard
@@ -260,8 +297,23 @@ class ShardedEmbeddingTable:
 
     def lookup_pooled(self, keys: torch.Tensor, pooling: str = "sum", *, fixed_hotness: int = 0,
                       csr_offsets: torch.Tensor | None = None, out: torch.Tensor | None = None):
+        if self.monitor is not None:
+            self.monitor.check()
         if self.mode == "peer":
             return self._lookup_peer(keys, pooling, fixed_hotness, csr_offsets, out)
+        if self.failed is not None:
+            raise ExchangeFailed(f"an earlier exchange failed: {self.failed}")
+        try:
+            return self._lookup_exchange(keys, pooling, fixed_hotness, csr_offsets, out)
+        except (PeerLeft, ExchangeFailed, capi.NveError):
+            raise
+        except RuntimeError as e:        # torch.distributed reports dead peers and timeouts this way
+            if self.world == 1:
+                raise
+            self.failed = str(e).splitlines()[0] if str(e) else type(e).__name__
+            raise ExchangeFailed(f"exchange with the other ranks failed: {self.failed}") from e
+
+    def _lookup_exchange(self, keys, pooling, fixed_hotness, csr_offsets, out):
         n = keys.numel()
         w = self.world
         send_keys, send_counts = self.stages.dedup_and_route(keys)

@@ -136,3 +136,65 @@ def test_two_ranks_nccl(torch_cuda, tmp_path, mode):
                           "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port",
                           str(port), str(script)], env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+LEAVER = r'''
+import os, sys
+from datetime import timedelta
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["NVE_ROOT"])
+from nv_embedding_cache_b200 import datagen as dg
+from nv_embedding_cache_b200.sharded import PeerLeft, PeerMonitor, ShardedEmbeddingTable
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+store = dist.TCPStore("127.0.0.1", int(os.environ["NVE_STORE_PORT"]), world, rank == 0, timeout=timedelta(seconds=60))
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank), timeout=timedelta(seconds=60))
+rows_per_rank, dim = 20000, 32
+total = rows_per_rank * world
+table = dg.dyadic_table(total, dim, 3, np.float16)
+monitor = PeerMonitor(store, rank, world)
+t = ShardedEmbeddingTable(torch.from_numpy(table[rank::world].copy()).cuda(), max_keys=1 << 14, mode="alltoall",
+                          monitor=monitor)
+keys = torch.from_numpy(dg.zipf_keys(1024 * 8, total, 1.05, 9 + rank, dg.permutation(total))).cuda()
+out = t.lookup_pooled(keys, "sum", fixed_hotness=8)
+torch.cuda.synchronize()
+want = table[keys.cpu().numpy()].astype(np.float32).reshape(1024, 8, dim).sum(1).astype(np.float16)
+ok = bool(np.array_equal(out.cpu().numpy(), want))
+dist.barrier()
+torch.cuda.synchronize()                 # the step is over: nothing of this rank is in flight
+if rank == world - 1:
+    monitor.announce_leave()
+    os._exit(0 if ok else 3)
+store.wait([monitor._key(world - 1)], timedelta(seconds=30))
+try:
+    t.lookup_pooled(keys, "sum", fixed_hotness=8)
+    code = 4                              # a lookup that needs the departed rank must not be attempted
+except PeerLeft:
+    code = 0 if ok else 3
+os._exit(code)
+'''
+
+
+def test_rank_leaves_between_steps_nccl(torch_cuda, tmp_path):
+    """A rank leaves between two steps with nothing in flight and says so on the store; the other
+    rank learns of it on the host and refuses its next lookup before any kernel or collective is
+    launched.  NVLS is off and the exchange form is used (no peer-mapped memory involved)."""
+    torch = torch_cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "leaver.py"
+    script.write_text(LEAVER)
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, NVE_ROOT=str(ROOT), NCCL_NVLS_ENABLE="0", RANK=str(rank), WORLD_SIZE="2",
+                   LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(ports[0]),
+                   NVE_STORE_PORT=str(ports[1]))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert [p.returncode for p in procs] == [0, 0], "\n".join(o[-1500:] for o in outs)

@@ -93,3 +93,70 @@ def test_sharded_lookup_matches_unsharded(world):
     assert all(r[1] and r[2] for r in results), results
     # every unique key requested by some rank is served by exactly one owner
     assert sum(r[3] for r in results) == sum(r[4] for r in results)
+
+
+def _leaver_worker(rank, world, pg_port, store_port, announce, q):
+    """Every rank does one lookup; the last rank then leaves (announced on the store, or silently);
+    the others try a second lookup and report how it ended."""
+    from datetime import timedelta
+    store = dist.TCPStore("127.0.0.1", store_port, world, rank == 0, timeout=timedelta(seconds=60))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(pg_port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=8))
+    from nv_embedding_cache_b200.sharded import ExchangeFailed, PeerLeft, PeerMonitor, ShardedEmbeddingTable
+    total, dim = 300 * world, 8
+    table = dg.dyadic_table(total, dim, 3, np.float32)
+    monitor = PeerMonitor(store, rank, world)
+    t = ShardedEmbeddingTable(torch.from_numpy(table[rank::world].copy()), max_keys=1024,
+                              stages=HostStages(world), monitor=monitor)
+    keys = torch.from_numpy(dg.uniform_keys(64, total, 7 + rank))
+    out = t.lookup_pooled(keys, "sum", fixed_hotness=8)
+    first_ok = bool(np.array_equal(out.numpy(), table[keys.numpy()].reshape(8, 8, dim).sum(1)))
+    dist.barrier()                                   # the step is over on every rank
+    leaver = world - 1
+    if rank == leaver:
+        if announce:
+            monitor.announce_leave()
+        q.put((rank, first_ok, "left"))
+        q.close()
+        q.join_thread()
+        os._exit(0)                                  # gone, without tearing the group down
+    if announce:
+        store.wait([monitor._key(leaver)], timedelta(seconds=30))    # the news arrives on the host
+    outcome = "completed"
+    try:
+        t.lookup_pooled(keys, "sum", fixed_hotness=8)
+    except PeerLeft:
+        outcome = "peer_left"
+    except ExchangeFailed:
+        outcome = "exchange_failed"
+        try:
+            t.lookup_pooled(keys, "sum", fixed_hotness=8)       # refused at once from now on
+            outcome = "second_lookup_completed"
+        except ExchangeFailed:
+            pass
+    q.put((rank, first_ok, outcome))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+@pytest.mark.parametrize("announce,expected", [(True, "peer_left"), (False, "exchange_failed")])
+def test_a_rank_that_leaves_between_steps(announce, expected):
+    """Failure detection without any device fault: a rank leaves between two steps.  Announced on
+    the store, the others refuse their next lookup on the host before any collective; unannounced,
+    the process group's short timeout (or the closed connection) ends the collective with an error
+    that the table reports and remembers."""
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ports = (_free_port(), _free_port())
+    procs = [ctx.Process(target=_leaver_worker, args=(r, world, ports[0], ports[1], announce, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert all(r[1] for r in results), results
+    assert results[world - 1][2] == "left"
+    assert [r[2] for r in results[:world - 1]] == [expected] * (world - 1), results
