@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
         if (WEIGHTED) w = __shfl_sync(gmask, my_w, min(s + u, n - 1), GROUP);
         if constexpr (QUANT) {
           scale = __shfl_sync(gmask, my_scale, min(s + u, n - 1), GROUP);
-          qoff = __shfl_sync(gmask, my_qoff, min(s + u, n - 1), GROUP);
+          // symmetric int8 rows carry no offset: nothing to hand round
+          if constexpr (IN == In::U8) qoff = __shfl_sync(gmask, my_qoff, min(s + u, n - 1), GROUP);
         }
         if (s + u < n) {
           if (WEIGHTED) wsum = __fadd_rn(wsum, w);
