@@ -46,6 +46,66 @@ __device__ __forceinline__ void accumulate_vec16(float* acc, const uint4& raw, f
   }
 }
 
+// Two fp32 values per instruction: sm_100's packed add and sub (one rounding per element, the same
+// values as the scalar instructions).  The quantised path is bound by instruction issue; its
+// subtract and its add per value become one instruction per pair.  The multiply between them stays
+// scalar on purpose: a packed multiply feeding a packed add was measured to come out as ONE fused
+// multiply-add (one rounding instead of two, last-bit differences from the reference arithmetic),
+// whether the add was written as add.rn.f32x2 or as fma(x, 1, acc); a scalar mul.rn.f32 is not
+// contracted into the packed add.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// acc += decode(raw) for 16 one-byte values, accumulators kept as 8 packed pairs (pair i holds
+// values 2i and 2i+1).  Per value, in this order and with one rounding each, exactly as
+// decode_vec + accumulate_vec16 do: q = byte (through the 2^23 placement), x = q * scale,
+// x = x + offset (asymmetric uint8 rows only), x = x * w (weighted only), acc = acc + x.
+template <In IN, bool WEIGHTED>
+__device__ __forceinline__ void accumulate_bytes_packed(uint64_t* acc, const uint4& raw, float w, float scale,
+                                                        float qoff) {
+  constexpr float kMagic = (IN == In::I8) ? 8388736.0f : 8388608.0f;   // 2^23 (+128)
+  const uint64_t magic2 = pack_f32x2(kMagic, kMagic);
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    uint32_t word = words[j];
+    if constexpr (IN == In::I8) word ^= 0x80808080u;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t m0 = __byte_perm(word, 0x4B000000u, 0x7540u + 2 * h);
+      const uint32_t m1 = __byte_perm(word, 0x4B000000u, 0x7541u + 2 * h);
+      float q0, q1;
+      unpack_f32x2(sub_f32x2(pack_f32x2(__uint_as_float(m0), __uint_as_float(m1)), magic2), q0, q1);
+      float x0 = __fmul_rn(q0, scale), x1 = __fmul_rn(q1, scale);
+      if constexpr (IN == In::U8) {
+        x0 = __fadd_rn(x0, qoff);
+        x1 = __fadd_rn(x1, qoff);
+      }
+      if constexpr (WEIGHTED) {
+        x0 = __fmul_rn(x0, w);
+        x1 = __fmul_rn(x1, w);
+      }
+      acc[2 * j + h] = add_f32x2(acc[2 * j + h], pack_f32x2(x0, x1));
+    }
+  }
+}
+
 // WORDS: rows that are only 4-byte aligned (quantised rows stored back to back: 256 values + a
 // 4-byte scale = 260 bytes).  A lane still owns 16 values, but fetches them as four 32-bit words,
 // word j of lane l being word j * nvec + l of the row, so that each of the four loads of a lane
@@ -74,9 +134,13 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   const uint8_t* lane_base = p.table + gl * (WORDS ? 4 : 16);
   const uint32_t stride = static_cast<uint32_t>(p.row_stride);
 
-  float acc[EPV];
+  // quantised rows accumulate in packed pairs (8 x two fp32), the others in EPV scalars
+  float acc[QUANT ? 1 : EPV];
+  uint64_t acc2[QUANT ? EPV / 2 : 1];
 #pragma unroll
-  for (int e = 0; e < EPV; e++) acc[e] = 0.f;
+  for (int e = 0; e < (QUANT ? 1 : EPV); e++) acc[e] = 0.f;
+#pragma unroll
+  for (int e = 0; e < (QUANT ? EPV / 2 : 1); e++) acc2[e] = 0ull;
   float wsum = 0.f;
 
 #pragma unroll 1
@@ -132,7 +196,10 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
         }
         if (s + u < n) {
           if (WEIGHTED) wsum = __fadd_rn(wsum, w);
-          if (lane_on) accumulate_vec16<IN, WEIGHTED>(acc, raw[u], w, scale, qoff);
+          if (lane_on) {
+            if constexpr (QUANT) accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, scale, qoff);
+            else accumulate_vec16<IN, WEIGHTED>(acc, raw[u], w, scale, qoff);
+          }
         }
       }
     }
@@ -145,8 +212,18 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   }
   if (lane_on) {
     float v[EPV];
+    if constexpr (QUANT) {
 #pragma unroll
-    for (int e = 0; e < EPV; e++) v[e] = __fmul_rn(acc[e], inv);
+      for (int e = 0; e < EPV / 2; e++) {
+        float lo, hi;
+        unpack_f32x2(acc2[e], lo, hi);
+        v[2 * e] = __fmul_rn(lo, inv);
+        v[2 * e + 1] = __fmul_rn(hi, inv);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPV; e++) v[e] = __fmul_rn(acc[e], inv);
+    }
     const int out_eb = p.out_f16 ? 2 : 4;
     if constexpr (WORDS) {
       static_assert(!WORDS || EPV == 16, "word loads are for one-byte elements");
