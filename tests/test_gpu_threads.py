@@ -11,14 +11,19 @@ from nv_embedding_cache_b200 import datagen as dg
 pytestmark = pytest.mark.gpu
 
 
-def test_concurrent_lookups_and_inserts(torch_cuda):
+@pytest.mark.parametrize("kernel_mode", [0, 2, 3], ids=["fused", "sort_gather", "pipeline"])
+def test_concurrent_lookups_and_inserts(torch_cuda, kernel_mode):
+    """Every lookup schedule: the sort-gather and pipeline schedules spread one lookup over several
+    kernels (the pipeline one over auxiliary streams and host threads as well), so an insert that
+    lands between them must not change what the lookup copies."""
     torch = torch_cuda
     from nv_embedding_cache_b200.layers import GpuTable, LinearUVMEmbeddingLayer
     rows, dim = 50_000, 64
     table = dg.normal_table(rows, dim, 0.02, 1, np.float16)
     backing = torch.from_numpy(table).pin_memory()
     tb = table.view(np.uint8).reshape(rows, -1)
-    gt = GpuTable((8000 // 8) * (64 + 8 * dim * 2 + 32), dim * 2, "float16", uvm_table=backing, uvm_num_rows=rows)
+    gt = GpuTable((8000 // 8) * (64 + 8 * dim * 2 + 32), dim * 2, "float16", uvm_table=backing, uvm_num_rows=rows,
+                  kernel_mode_type=kernel_mode)
     layer = LinearUVMEmbeddingLayer(gt)
     perm = dg.permutation(rows)
     errors = []
