@@ -11,6 +11,7 @@
 //   * the backing-table write-through of update / update_accumulate always runs as a GPU kernel.
 #include <algorithm>
 #include <mutex>
+#include <shared_mutex>
 #include <random>
 
 #include "../kernels/cache_modify.cuh"
@@ -109,6 +110,17 @@ class GpuTable : public Table {
   }
 
   // Every lookup must see the tag invalidation of the modifies enqueued before it.
+  // Brackets the enqueueing of one lookup (all of its kernels, on whatever streams): taken shared
+  // by lookups and exclusively by cache modifications, so that a modification is never assembled
+  // between a lookup's wait for earlier invalidations and the launch of its last kernel.  A
+  // modification enqueued afterwards waits for everything the lookup put on its stream; one enqueued
+  // before is waited for here.  (The reference brackets the same span with its custom-flow lock.)
+  std::shared_lock<std::shared_mutex> begin_lookup(cudaStream_t lookup_stream) {
+    std::shared_lock<std::shared_mutex> flow(flow_mu_);
+    order_lookup(lookup_stream);
+    return flow;
+  }
+
   void order_lookup(cudaStream_t lookup_stream) {
     std::lock_guard<std::mutex> lock(order_mu_);
     NVE_B200_CUDA(cudaStreamWaitEvent(lookup_stream, invalidate_done_, 0));
@@ -156,13 +168,14 @@ class GpuTable : public Table {
     g.output_dtype = cfg_.value_dtype;   // raw rows
     g.row_copy_bytes = cfg_.row_size_in_bytes;
     g.hit_mask = d_hit_mask;
-    order_lookup(s);
+    const auto flow = begin_lookup(s);
     if (cfg_.uvm_table != nullptr && d_values != nullptr &&
         cfg_.kernel_mode_type == NVE_KERNEL_PIPELINE_GATHER) {
       // Part of this lookup runs on auxiliary streams that join the lookup stream only at the end
-      // of the call, so no cache modification may be assembled meanwhile (the reference brackets
-      // the same span with its ScopedCustomFlow, cuda_ops/pipeline_gather.cuh:349-398).
-      std::lock_guard<std::mutex> gate(modify_mu_);
+      // of the call; `flow` keeps cache modifications out for all of it (the reference brackets the
+      // same span with its ScopedCustomFlow, cuda_ops/pipeline_gather.cuh:349-398).  The streams
+      // and events are shared by the contexts of the table: one pipeline lookup at a time.
+      std::lock_guard<std::mutex> one(pipeline_mu_);
       ensure_pipeline_resources();
       const PipelineBufferFn buffer = [&c](const char* name, size_t bytes, bool pinned) {
         return c.scratch(name, bytes, pinned);
@@ -264,7 +277,7 @@ class GpuTable : public Table {
 
   void clear(context_ptr_t& ctx) override {
     ScopedDevice sd(cfg_.device_id);
-    std::lock_guard<std::mutex> lock(modify_mu_);
+    std::unique_lock<std::shared_mutex> lock(flow_mu_);
     const cudaStream_t s = ctx->modify_stream();
     contexts_->order_after_lookups(s);
     cache_clear(cs_, key_type_, num_sets_, s);
@@ -316,7 +329,7 @@ class GpuTable : public Table {
     auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(n) * sizeof(ModifyEntry), false));
     auto* count = static_cast<uint32_t*>(c.scratch("cache_entry_count", 256, false));
 
-    std::lock_guard<std::mutex> lock(modify_mu_);
+    std::unique_lock<std::shared_mutex> lock(flow_mu_);
     // an earlier modify of another context must be complete before this one reads the tags
     NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
     cache_insert_select(cs_, hash_, key_type_, d_keys.device, n, src, value_stride, from_table,
@@ -343,7 +356,7 @@ class GpuTable : public Table {
     auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(cap) * sizeof(ModifyEntry), false));
     auto* count = static_cast<uint32_t*>(c.scratch("cache_entry_count", 256, false));
 
-    std::lock_guard<std::mutex> lock(modify_mu_);
+    std::unique_lock<std::shared_mutex> lock(flow_mu_);
     NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
     cache_find_resident(cs_, hash_, key_type_, d_keys.device, n, d_vals, stride, entries, count,
                         cap, s);
@@ -389,7 +402,8 @@ class GpuTable : public Table {
   SetHash hash_{};
   CacheStorage cs_{};
   std::shared_ptr<ContextRegistry> contexts_;
-  std::mutex modify_mu_;   // one cache modification is assembled at a time
+  std::shared_mutex flow_mu_;   // exclusive: one cache modification is assembled at a time; shared: lookups
+  std::mutex pipeline_mu_;      // the pipeline schedule's streams and events
   std::mutex order_mu_;    // guards invalidate_done_
   cudaEvent_t invalidate_done_ = nullptr;
   cudaEvent_t modify_done_ = nullptr;
@@ -516,7 +530,7 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
         g.output = d_out.device;
         g.output_stride = output_stride;
         g.output_dtype = out_dtype;
-        table_->order_lookup(s);
+        const auto flow = table_->begin_lookup(s);
         gather_rows(g, tc.invalid_key, s);
       } else {
         nve_b200_pool_args_t a{};
@@ -547,7 +561,7 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
         a.output = d_out.device;
         a.output_stride = output_stride;
         a.output_dtype = out_dtype;
-        table_->order_lookup(s);
+        const auto flow = table_->begin_lookup(s);
         lookup_pool(a, tc.invalid_key, s);
       }
     } else {
