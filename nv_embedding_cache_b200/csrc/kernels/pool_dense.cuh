@@ -131,7 +131,13 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   }
   const int len = static_cast<int>(end - start);
   const bool lane_on = gl < p.nvec;
-  const uint8_t* lane_base = p.table + gl * (WORDS ? 4 : 16);
+  // Symmetric int8 rows, un-weighted: the inner loops run without branches.  A lane past the end of
+  // the row re-reads the row's last vector and sums it into accumulators it never stores, and a
+  // row slot past the end of the chunk is added with scale 0, i.e. as +-0, which leaves every
+  // accumulator as it is (they start at +0 and a sum with a zero term cannot become -0).
+  constexpr bool BRANCHLESS = (IN == In::I8) && !WEIGHTED;
+  const int gc = (BRANCHLESS && !WORDS) ? min(gl, p.nvec - 1) : gl;
+  const uint8_t* lane_base = p.table + gc * (WORDS ? 4 : 16);
   const uint32_t stride = static_cast<uint32_t>(p.row_stride);
 
   // quantised rows accumulate in packed pairs (8 x two fp32), the others in EPV scalars
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
       for (int u = 0; u < U; u++) {
         {
           const uint32_t k = __shfl_sync(gmask, my_key, min(s + u, n - 1), GROUP);
-          if (lane_on) {
+          if ((BRANCHLESS && !WORDS) || lane_on) {
             if constexpr (WORDS) {
               const uint32_t* w = reinterpret_cast<const uint32_t*>(lane_base + static_cast<uint64_t>(k) * stride);
               raw[u].x = __ldg(w);
@@ -194,7 +200,9 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
           // symmetric int8 rows carry no offset: nothing to hand round
           if constexpr (IN == In::U8) qoff = __shfl_sync(gmask, my_qoff, min(s + u, n - 1), GROUP);
         }
-        if (s + u < n) {
+        if constexpr (BRANCHLESS) {
+          accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, (s + u < n) ? scale : 0.f, qoff);
+        } else if (s + u < n) {
           if (WEIGHTED) wsum = __fadd_rn(wsum, w);
           if (lane_on) {
             if constexpr (QUANT) accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, scale, qoff);
