@@ -131,11 +131,12 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
   }
   const int len = static_cast<int>(end - start);
   const bool lane_on = gl < p.nvec;
-  // Symmetric int8 rows, un-weighted: the inner loops run without branches.  A lane past the end of
-  // the row re-reads the row's last vector and sums it into accumulators it never stores, and a
-  // row slot past the end of the chunk is added with scale 0, i.e. as +-0, which leaves every
-  // accumulator as it is (they start at +0 and a sum with a zero term cannot become -0).
-  constexpr bool BRANCHLESS = (IN == In::I8) && !WEIGHTED;
+  // The inner loops run without branches.  A row slot past the end of a chunk is added as zeros
+  // (quantised rows: scale and offset 0; other rows: a zero vector; weight 0), which leaves every
+  // accumulator as it is: they start at +0, and a sum with a +-0 term cannot become -0.  A lane past
+  // the end of the row works on the row's last vector into accumulators it never stores (the
+  // word-load form keeps the lane test on its loads: without it that form measured slower).
+  constexpr bool BRANCHLESS = true;
   const int gc = (BRANCHLESS && !WORDS) ? min(gl, p.nvec - 1) : gl;
   const uint8_t* lane_base = p.table + gc * (WORDS ? 4 : 16);
   const uint32_t stride = static_cast<uint32_t>(p.row_stride);
@@ -200,14 +201,20 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
           // symmetric int8 rows carry no offset: nothing to hand round
           if constexpr (IN == In::U8) qoff = __shfl_sync(gmask, my_qoff, min(s + u, n - 1), GROUP);
         }
-        if constexpr (BRANCHLESS) {
-          accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, (s + u < n) ? scale : 0.f, qoff);
-        } else if (s + u < n) {
-          if (WEIGHTED) wsum = __fadd_rn(wsum, w);
-          if (lane_on) {
-            if constexpr (QUANT) accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, scale, qoff);
-            else accumulate_vec16<IN, WEIGHTED>(acc, raw[u], w, scale, qoff);
-          }
+        const bool valid = s + u < n;
+        if (WEIGHTED) {
+          w = valid ? w : 0.f;
+          wsum = __fadd_rn(wsum, w);
+        }
+        if constexpr (QUANT) {
+          accumulate_bytes_packed<IN, WEIGHTED>(acc2, raw[u], w, valid ? scale : 0.f, valid ? qoff : 0.f);
+        } else {
+          uint4 r = raw[u];
+          r.x = valid ? r.x : 0u;
+          r.y = valid ? r.y : 0u;
+          r.z = valid ? r.z : 0u;
+          r.w = valid ? r.w : 0u;
+          accumulate_vec16<IN, WEIGHTED>(acc, r, w, scale, qoff);
         }
       }
     }
