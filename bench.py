@@ -473,7 +473,7 @@ def run_other_workload(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     fn = {"c3": workloads.run_c3, "c4a": workloads.run_c4a, "c4b": workloads.run_c4b,
-          "c5": workloads.run_c5}[args.workload]
+          "c5": workloads.run_c5, "published": workloads.run_published_gpulayer}[args.workload]
     steps = min(args.steps, 50)
     kw = {}
     if args.rows > 0:   # smaller table for profiling runs (the configuration's size is the default)
@@ -495,7 +495,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["c2", "c3", "c4a", "c4b", "c5"], default="c2",
+    ap.add_argument("--workload", choices=["c2", "c3", "c4a", "c4b", "c5", "published"], default="c2",
                     help="c2 is the headline benchmark; the others print one JSON line for that "
                          "configuration (see nv_embedding_cache_b200/workloads.py)")
     ap.add_argument("--rows", type=int, default=0,

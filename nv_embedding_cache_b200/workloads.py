@@ -166,6 +166,47 @@ def run_c3(root, steps=50, warmup=5, rows=100_000_000, dim=128, batch=262_144, c
     return res
 
 
+def run_published_gpulayer(root, steps=50, warmup=5, rows=250_000_000, dim=128, batch=262_144):
+    """The shape of the reference's own published GPULayer benchmark (docs/benchmarks.md: fp32, dim 128,
+    128 GB table in HBM, 256 x 1024 keys per step, power-law keys alpha 1.05, un-pooled lookups,
+    device-resident keys): one un-pooled lookup of `batch` keys per step through the dense layer."""
+    stream = torch.cuda.current_stream()
+    row_bytes = dim * 4
+    table = torch.empty((rows, dim), dtype=torch.float32, device="cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(70)
+    chunk = 1 << 22
+    for r0 in range(0, rows, chunk):
+        r1 = min(rows, r0 + chunk)
+        table[r0:r1].normal_(0, 0.02, generator=gen)
+    layer = GPUEmbeddingLayer(table, rows, row_bytes, "float32")
+    ctx = layer.create_execution_context(stream.cuda_stream, stream.cuda_stream)
+    nb = 8
+    # power-law ranks spread over the table by a multiplicative bijection of Z_rows (the multiplier is a
+    # prime that does not divide `rows`), standing in for the reference's random permutation, which
+    # at this size would take gigabytes of host memory to build
+    def spread(ranks):
+        return ((ranks.astype(np.uint64) * np.uint64(2654435761)) % np.uint64(rows)).astype(np.int64)
+    batches = [torch.from_numpy(spread(dg.zipf_keys(batch, rows, 1.05, 700 + b))).cuda() for b in range(nb)]
+    out = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    layer.lookup(ctx, batch, batches[0], out, row_bytes)
+    ctx.wait()
+    ok = bool(torch.equal(out, table[batches[0]]))
+    sec = _time_loop(stream, lambda i: layer.lookup(ctx, batch, batches[i % nb], out, row_bytes), steps, warmup)
+    peak, kind = _hbm_peak(root)
+    alg = batch * (8 + 2 * row_bytes)
+    res = {"workload": f"published GPULayer shape: {rows} x {dim} fp32 in HBM ({rows * row_bytes / 1e9:.0f} GB), "
+                       f"{batch} keys per step, power-law 1.05, un-pooled",
+           "keys_per_s": batch / sec, "mkps": batch / sec / 1e6, "us_per_lookup": sec * 1e6,
+           "algo_bw_gib_s": batch / sec * row_bytes / 2**30, "algorithmic_gbs": alg / sec / 1e9,
+           "frac_of_hbm_peak": alg / sec / 1e9 / peak, "peak_kind": kind, "byte_exact": ok,
+           "reference_published": {"mkps": 2910.36, "algo_bw_gib_s": 1387.77, "hardware": "1x GB200",
+                                   "source": "docs/benchmarks.md:40-42"}}
+    ctx.destroy()
+    layer.destroy()
+    return res
+
+
 def _c3_schedules(gt, ctx, table, rows, row_bytes, batch, stream, steps, warmup):
     """The fused lookup kernel and the sort-gather schedule through the kernel-level C ABI on the warmed
     cache of the C3 run: the configuration's batch and one eight times larger, Zipf and uniform keys."""
