@@ -340,12 +340,14 @@ def run_ours(args):
         ms = e0.elapsed_time(e1)
         return ms, keys, extra, clk.summary()
 
-    # One step of the device-resident leg is eight short launches issued from Python; with several
-    # ranks on one host the launch rate, not the GPU, can become the limit.  Each of the four cycled
-    # steps is therefore captured once as a CUDA graph and replayed (same kernels, same arguments);
-    # --no-graph, or a capture that fails, keeps the direct launches.
+    # One step of the device-resident leg is eight short launches issued from Python, about as long
+    # on the host as on the GPU.  Each of the four cycled steps is therefore captured once as a CUDA
+    # graph and replayed (same kernels, same arguments); --no-graph, or a capture that fails, keeps
+    # the direct launches.
     graphs = []
-    if not args.no_graph:
+    # Single-rank runs only: with a NCCL process group alive in the process the capture was seen not
+    # to complete on an 8-rank run, so multi-rank runs keep the direct launches.
+    if not args.no_graph and world == 1:
         try:
             with torch.cuda.stream(stream):
                 for b in range(NUM_BATCHES):
