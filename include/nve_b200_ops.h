@@ -180,7 +180,8 @@ NVE_C_API nve_status_t nve_b200_gpu_table_get_policy_state(nve_table_t table,
 /*
  * Insert keys whose rows are read from the table's backing (uvm) table, row = backing[key].
  * Replaces GpuTable::insert_from_uvm (src/gpu_table.cu:494-576), which the reference exposes to
- * C++ callers only.
+ * C++ callers only.  Keys outside [0, uvm_num_rows) are no rows of the backing table and are left
+ * out of the insert.
  */
 NVE_C_API nve_status_t nve_b200_gpu_table_insert_from_backing(nve_table_t table, nve_context_t ctx,
                                                               int64_t n, const void* keys);
@@ -279,9 +280,10 @@ NVE_C_API nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t deduper, int
  * that -- (2 * (num_keys / max_run_size + 1) + 2) * row_bytes bytes -- is rejected with
  * NVE_ERROR_INVALID_ARGUMENT.  With max_run_size == -1 no scratch is used at all.
  *
- * The call never calls cudaMalloc / cudaFree or any allocating routine.  The first call on a
- * device looks up the array's device address (cudaGetSymbolAddress, with that device current);
- * make that first call before starting a stream capture.  All calls on a device share the one
+ * The call never calls cudaMalloc / cudaFree or any allocating routine.  The array and the
+ * kernels are those of the device `stream` belongs to (the current device for the default stream).
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before starting a stream capture.  All calls on a device share the one
  * array: nothing in it has to be zero (every slot is written before it is read within a call),
  * but two calls that overlap on the GPU would overwrite each other's partial sums, so keep them
  * on one stream or otherwise ordered.
@@ -291,6 +293,15 @@ NVE_C_API nve_status_t nve_b200_dedup_grads_static(
     int64_t row_bytes, int64_t num_keys, const void* d_unique, const void* d_inverse,
     const void* d_offsets, const void* d_loc_map, const void* d_num_runs, void* d_dst,
     int64_t dst_stride, int32_t apply_to_table, int64_t table_rows, float alpha, void* stream);
+
+/*
+ * Whether a gradient reduction on the current device, since the last call of this function, found
+ * the scratch for the partial sums of split groups too small: *overflowed = 1 and the flag is
+ * cleared.  The library sizes that scratch from the batch, so this only happens when the chunk map
+ * passed in does not belong to the batch; the kernels skip such a write instead of doing it out of
+ * bounds, and the sums of the affected groups are incomplete.  Synchronises the device.
+ */
+NVE_C_API nve_status_t nve_b200_dedup_grads_status(int32_t* overflowed);
 
 /* Device copy of {U, C} of the deduper's last dedup() (two elements of the key type), for
  * kernels that follow without a host round trip. */

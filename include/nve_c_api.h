@@ -206,8 +206,10 @@ NVE_C_API nve_status_t nve_thread_pool_destroy(nve_thread_pool_t pool);
 NVE_C_API nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t pool, int64_t* out);
 NVE_C_API nve_status_t nve_configure_default_thread_pool(const char* json_config);
 
-/* ---- insert heuristics (reference :351-366): handles are accepted and kept; automatic cache
- * population is not part of the hot path, so neither kind triggers inserts here ---- */
+/* ---- insert heuristics (reference :351-366).  The default heuristic steers the automatic cache
+ * population of a LinearUVM layer (thresholds[0] is the hit rate below which inserts are frequent;
+ * the table must count misses); the never-insert heuristic switches it off.  A handle may be
+ * destroyed once the layer has been created. ---- */
 NVE_C_API nve_status_t nve_heuristic_create_default(nve_heuristic_t* out, const float* thresholds,
                                                     int64_t num_thresholds);
 NVE_C_API nve_status_t nve_heuristic_create_never(nve_heuristic_t* out);

@@ -161,6 +161,7 @@ PROTOTYPES = {
     "nve_b200_shard_expand_slots": (_i32, [C.c_int, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "nve_b200_dedup_grads_static": (_i32, [C.c_int, _i64, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
                                             _vp, _vp, _i64, _i32, _i64, C.c_float, _vp]),
+    "nve_b200_dedup_grads_status": (_i32, [C.POINTER(_i32)]),
     "nve_b200_update_rows": (_i32, [_vp, _i64, _i64, _i32, _i64, C.c_int, _vp, _i64, _vp, _i64,
                                      C.c_int, C.c_int, _vp]),
     "nve_b200_dedup_grads_f16": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),

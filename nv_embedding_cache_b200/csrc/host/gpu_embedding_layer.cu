@@ -236,10 +236,11 @@ void GPUEmbeddingLayer::modify(context_ptr_t& ctx, int64_t num_keys, const void*
   }
   ExecutionContext& c = *ctx;
   const cudaStream_t modify_stream = c.modify_stream();
-  const Staged d_keys = stage_in(c, "keys", keys,
+  // staging buffers of their own: a lookup of the same context may still be reading "keys"
+  const Staged d_keys = stage_in(c, "modify_keys", keys,
                                  static_cast<size_t>(num_keys) * key_bytes(key_type_), true,
                                  modify_stream);
-  const Staged d_vals = stage_in(c, "values", values,
+  const Staged d_vals = stage_in(c, "modify_values", values,
                                  static_cast<size_t>(num_keys) * value_stride, true, modify_stream);
 
   std::lock_guard<std::mutex> lock(launch_mutex_);

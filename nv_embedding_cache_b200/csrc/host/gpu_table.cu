@@ -236,15 +236,21 @@ class GpuTable : public Table {
     NVE_B200_ARG(keys != nullptr, "keys must not be null");
     NVE_B200_CHECK(values != nullptr, "Invalid cache insert params");
     NVE_B200_CHECK(value_size == cfg_.row_size_in_bytes, "Unsupported value_size");
-    insert_impl(ctx, n, keys, values, value_stride, false);
+    insert_impl(ctx, n, keys, values, value_stride, false, -1, nullptr);
   }
 
   // Rows come from the backing table (reference insert_from_uvm, src/gpu_table.cu:494-576).
-  void insert_from_table(context_ptr_t& ctx, int64_t n, const void* keys) {
+  // Keys that are no rows of the backing table are inserted as `default_row` when that is a row
+  // (what a lookup of such a key reads; the reference sanitises the keys of its automatic inserts
+  // the same way, src/linear_embedding_layer.cu:120-125) and dropped otherwise.  `keys_ready`:
+  // optional event the modify stream waits for before it reads `keys` (keys collected on other
+  // streams).
+  void insert_from_table(context_ptr_t& ctx, int64_t n, const void* keys, int64_t default_row = -1,
+                         cudaEvent_t keys_ready = nullptr) {
     if (n <= 0) return;
     NVE_B200_CHECK(cfg_.uvm_table != nullptr, "insert_from_uvm requires a UVM table");
     NVE_B200_ARG(keys != nullptr, "keys must not be null");
-    insert_impl(ctx, n, keys, nullptr, cfg_.row_size_in_bytes, true);
+    insert_impl(ctx, n, keys, nullptr, cfg_.row_size_in_bytes, true, default_row, keys_ready);
   }
 
   void update(context_ptr_t& ctx, int64_t n, const void* keys, int64_t stride, int64_t size,
@@ -315,15 +321,17 @@ class GpuTable : public Table {
   // into context scratch, device buffers belong to the caller (who must keep them until the
   // modify stream has run).
   void insert_impl(context_ptr_t& ctx, int64_t n, const void* keys, const void* values,
-                   int64_t value_stride, bool from_table) {
+                   int64_t value_stride, bool from_table, int64_t default_row,
+                   cudaEvent_t keys_ready) {
     ScopedDevice sd(cfg_.device_id);
     ExecutionContext& c = *ctx;
     const cudaStream_t s = c.modify_stream();
-    const Staged d_keys = stage_in(c, "keys", keys, size_t(n) * key_bytes(key_type_), true, s);
+    // staging buffers of their own: a lookup of the same context may still be reading "keys"
+    const Staged d_keys = stage_in(c, "modify_keys", keys, size_t(n) * key_bytes(key_type_), true, s);
     const uint8_t* src = static_cast<const uint8_t*>(cfg_.uvm_table);
     if (!from_table) {
       src = static_cast<const uint8_t*>(
-          stage_in(c, "values", values, size_t(n) * value_stride, true, s).device);
+          stage_in(c, "modify_values", values, size_t(n) * value_stride, true, s).device);
     }
     void* scratch = c.scratch("cache_insert", cache_insert_scratch_bytes(key_type_, n), false);
     auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(n) * sizeof(ModifyEntry), false));
@@ -332,10 +340,11 @@ class GpuTable : public Table {
     std::unique_lock<std::shared_mutex> lock(flow_mu_);
     // an earlier modify of another context must be complete before this one reads the tags
     NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
+    if (keys_ready != nullptr) NVE_B200_CUDA(cudaStreamWaitEvent(s, keys_ready, 0));
     cache_insert_select(cs_, hash_, key_type_, d_keys.device, n, src, value_stride, from_table,
                         std::max<int64_t>(cfg_.max_modify_size, 0), ++global_ts_, kDecayRate,
                         scratch, entries, count, s,
-                        /*key_bound=*/from_table ? cfg_.uvm_num_rows : 0);
+                        /*key_bound=*/from_table ? cfg_.uvm_num_rows : 0, default_row);
     const uint32_t cap = static_cast<uint32_t>(n);
     commit_entries(s, entries, count, cap, /*mode=*/0, value_stride, src);
   }
@@ -345,11 +354,11 @@ class GpuTable : public Table {
     ScopedDevice sd(cfg_.device_id);
     ExecutionContext& c = *ctx;
     const cudaStream_t s = c.modify_stream();
-    const Staged d_keys = stage_in(c, "keys", keys, size_t(n) * key_bytes(key_type_), true, s);
+    const Staged d_keys = stage_in(c, "modify_keys", keys, size_t(n) * key_bytes(key_type_), true, s);
     const uint8_t* d_vals = nullptr;
     if (values) {
       d_vals = static_cast<const uint8_t*>(
-          stage_in(c, "values", values, size_t(n) * stride, true, s).device);
+          stage_in(c, "modify_values", values, size_t(n) * stride, true, s).device);
     }
     // a key may sit in more than one way, so leave room for every way of every key
     const uint32_t cap = static_cast<uint32_t>(std::min<int64_t>(n * kWays, 0x7fffffff));
@@ -373,7 +382,7 @@ class GpuTable : public Table {
       contexts_->order_after_lookups(s);
       update_rows(cfg_.uvm_table, cfg_.uvm_num_rows, cfg_.row_size_in_bytes, dtype,
                   cfg_.row_size_in_bytes, key_type_, d_keys.device, n, d_vals, stride, mode != 0,
-                  /*keys_unique=*/true, s);
+                  /*keys_unique=*/false, s);
       NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
       contexts_->lookups_wait_event(modify_done_);
     }
@@ -446,6 +455,9 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
     int64_t pending_keys = 0;
     void* buf[2] = {nullptr, nullptr};              // collected keys (device), alternating
     cudaEvent_t buf_free[2] = {nullptr, nullptr};   // the insert that read the buffer is done
+    cudaEvent_t part_copied = nullptr;              // a part's copy on its lookup stream is enqueued
+    cudaEvent_t keys_ready = nullptr;               // every part of the collection has been copied
+    cudaStream_t join = nullptr;                    // waits for each part; keys_ready is recorded on it
     int cur = 0;
     int64_t capacity = 0, target = 0, collected = 0;
     bool collecting = false;
@@ -623,6 +635,9 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
   ~LinearUVMEmbeddingLayer() override {
     if (ai_.h_counts) (void)cudaFreeHost(ai_.h_counts);
     if (ai_.readback_done) (void)cudaEventDestroy(ai_.readback_done);
+    if (ai_.part_copied) (void)cudaEventDestroy(ai_.part_copied);
+    if (ai_.keys_ready) (void)cudaEventDestroy(ai_.keys_ready);
+    if (ai_.join) (void)cudaStreamDestroy(ai_.join);
     for (int i = 0; i < 2; i++) {
       if (ai_.buf[i]) (void)cudaFree(ai_.buf[i]);
       if (ai_.buf_free[i]) (void)cudaEventDestroy(ai_.buf_free[i]);
@@ -653,6 +668,9 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
     ScopedDevice sd(tc.device_id);
     NVE_B200_CUDA(cudaMallocHost(&ai_.h_counts, 2 * sizeof(int64_t)));
     NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.readback_done, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.part_copied, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.keys_ready, cudaEventDisableTiming));
+    NVE_B200_CUDA(cudaStreamCreateWithFlags(&ai_.join, cudaStreamNonBlocking));
     for (int i = 0; i < 2; i++) {
       NVE_B200_CUDA(cudaEventCreateWithFlags(&ai_.buf_free[i], cudaEventDisableTiming));
     }
@@ -702,9 +720,16 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
       const int64_t part = std::min(num_keys, ai_.target - ai_.collected);
       NVE_B200_CUDA(cudaMemcpyAsync(static_cast<char*>(ai_.buf[ai_.cur]) + size_t(ai_.collected) * kb, d_keys,
                                     size_t(part) * kb, cudaMemcpyDeviceToDevice, s));
+      // the parts of one collection may come from contexts with different lookup streams, and the
+      // insert reads them on a modify stream: an internal stream waits for every part's copy, and
+      // the insert waits for that stream (the reference synchronises the lookup stream while it
+      // collects, src/layer_utils.cpp:196-198)
+      NVE_B200_CUDA(cudaEventRecord(ai_.part_copied, s));
+      NVE_B200_CUDA(cudaStreamWaitEvent(ai_.join, ai_.part_copied, 0));
       ai_.collected += part;
       if (ai_.collected >= ai_.target || ai_.collected >= ai_.min_size) {
-        table_->insert_from_table(ctx, ai_.collected, ai_.buf[ai_.cur]);
+        NVE_B200_CUDA(cudaEventRecord(ai_.keys_ready, ai_.join));
+        table_->insert_from_table(ctx, ai_.collected, ai_.buf[ai_.cur], default_row_, ai_.keys_ready);
         NVE_B200_CUDA(cudaEventRecord(ai_.buf_free[ai_.cur], ctx->modify_stream()));
         ai_.cur ^= 1;
         ai_.collecting = false;

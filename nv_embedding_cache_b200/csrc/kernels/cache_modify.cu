@@ -50,6 +50,23 @@ __global__ void iota_kernel(uint32_t* out, int64_t n) {
   if (i < n) out[i] = static_cast<uint32_t>(i);
 }
 
+// Keys of an insert whose rows come from a linear backing table: positions 0..n-1 as the sort's
+// payload, and the keys with every key outside [0, bound) replaced -- by `replacement` when that is
+// a row (the layer's default row, which a lookup of such a key reads), else by `bound` itself, one
+// past the last row: those sort behind every real key (the sort covers the bits of `bound`), fall
+// into one bin and are never made candidates.  Without this an out-of-range key would be read as a
+// row address, and, sorted on the low bits only, could split the run of a real key.
+template <typename KeyT>
+__global__ void bound_keys_kernel(const KeyT* keys, int64_t n, int64_t bound, int64_t replacement,
+                                  KeyT* clean, uint32_t* pos) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  pos[i] = static_cast<uint32_t>(i);
+  const int64_t k = static_cast<int64_t>(keys[i]);
+  const bool inside = k >= 0 && k < bound;
+  clean[i] = static_cast<KeyT>(inside ? k : (replacement >= 0 && replacement < bound ? replacement : bound));
+}
+
 template <typename KeyT>
 __global__ void mark_heads_kernel(const KeyT* sorted, uint32_t* head, int64_t n) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -92,7 +109,7 @@ __global__ void make_candidates_kernel(const uint32_t* count_sorted, const uint3
                                        const KeyT* bin_key, const uint32_t* bin_first,
                                        const uint32_t* num_bins, int64_t n, int64_t max_modify,
                                        float norm, const uint8_t* values, int64_t value_stride,
-                                       bool from_table, SetHash hash, KeyT* cand_key,
+                                       bool from_table, int64_t key_bound, SetHash hash, KeyT* cand_key,
                                        float* cand_prio, const uint8_t** cand_src,
                                        uint32_t* cand_set, uint32_t* cand_id) {
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -105,6 +122,10 @@ __global__ void make_candidates_kernel(const uint32_t* count_sorted, const uint3
   }
   const uint32_t u = order_sorted[j];
   const KeyT key = bin_key[u];
+  if (from_table && static_cast<uint64_t>(key) >= static_cast<uint64_t>(key_bound)) {
+    cand_set[j] = hash.num_sets;     // the bin of the keys that are no rows of the backing table
+    return;
+  }
   cand_key[j] = key;
   cand_prio[j] = __fmul_rn(static_cast<float>(count_sorted[j]), norm);
   cand_src[j] = from_table ? values + static_cast<int64_t>(key) * value_stride
@@ -340,20 +361,28 @@ __global__ void __launch_bounds__(128) apply_rows_kernel(const ModifyEntry* entr
     if constexpr (MODE == 0) {
       *reinterpret_cast<decltype(RawVec<VB>::v)*>(d) = r.v;
     } else if constexpr (MODE == 1) {
-      float* f = reinterpret_cast<float*>(d);
-#pragma unroll
-      for (int k = 0; k < VB / 4; k++) f[k] = __fadd_rn(f[k], __uint_as_float(raw_word<VB>(r, k)));
+      // duplicate keys of one batch target the same line: sum them, as the reference's
+      // mem_update_accumulate_kernel does (include/ecache/ec_set_associative.cuh:166-184)
+      if constexpr (VB == 16) {
+        atomicAdd(reinterpret_cast<float4*>(d),
+                  make_float4(__uint_as_float(r.v.x), __uint_as_float(r.v.y),
+                              __uint_as_float(r.v.z), __uint_as_float(r.v.w)));
+      } else if constexpr (VB == 8) {
+        atomicAdd(reinterpret_cast<float2*>(d),
+                  make_float2(__uint_as_float(r.v.x), __uint_as_float(r.v.y)));
+      } else {
+        atomicAdd(reinterpret_cast<float*>(d), __uint_as_float(raw_word<VB>(r, 0)));
+      }
     } else {
       if constexpr (VB >= 4) {
         __half2* h = reinterpret_cast<__half2*>(d);
 #pragma unroll
         for (int k = 0; k < VB / 4; k++) {
           const uint32_t w = raw_word<VB>(r, k);
-          h[k] = __hadd2(h[k], *reinterpret_cast<const __half2*>(&w));
+          atomicAdd(h + k, *reinterpret_cast<const __half2*>(&w));
         }
       } else {
-        __half* h = reinterpret_cast<__half*>(d);
-        *h = __hadd(*h, __ushort_as_half(r.v));
+        atomicAdd(reinterpret_cast<__half*>(d), __ushort_as_half(r.v));
       }
     }
   }
@@ -378,7 +407,7 @@ int bits_for(uint64_t max_value) {
 template <typename KeyT>
 struct Layout {
   // carve-up of the scratch buffer for n keys
-  KeyT *keys_sorted, *bin_key, *cand_key;
+  KeyT *keys_sorted, *bin_key, *cand_key, *keys_clean;
   uint32_t *pos, *pos_sorted, *head, *rank, *bin_first, *bin_start, *count, *count_sorted, *order,
       *order_sorted, *cand_set, *cand_set_sorted, *cand_id, *cand_id_sorted, *num_bins;
   float* cand_prio;
@@ -402,6 +431,7 @@ Layout<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
   L.keys_sorted = static_cast<KeyT*>(take(N * sizeof(KeyT)));
   L.bin_key = static_cast<KeyT*>(take(N * sizeof(KeyT)));
   L.cand_key = static_cast<KeyT*>(take(N * sizeof(KeyT)));
+  L.keys_clean = static_cast<KeyT*>(take(N * sizeof(KeyT)));
   uint32_t** u32s[] = {&L.pos, &L.pos_sorted, &L.head, &L.rank, &L.bin_first, &L.count,
                        &L.count_sorted, &L.order, &L.order_sorted, &L.cand_set,
                        &L.cand_set_sorted, &L.cand_id, &L.cand_id_sorted};
@@ -433,7 +463,8 @@ template <typename KeyT>
 void insert_typed(const CacheStorage& cs, const SetHash& hash, const void* keys_v, int64_t n,
                   const uint8_t* values, int64_t value_stride, bool from_table,
                   int64_t max_modify, int64_t global_ts, float decay_rate, void* scratch,
-                  ModifyEntry* entries, uint32_t* num_entries, cudaStream_t s, int64_t key_bound) {
+                  ModifyEntry* entries, uint32_t* num_entries, cudaStream_t s, int64_t key_bound,
+                  int64_t out_of_bound_key) {
   const KeyT* keys = static_cast<const KeyT*>(keys_v);
   const size_t cub_bytes = cub_temp_bytes<KeyT>(n);
   Layout<KeyT> L = carve<KeyT>(scratch, n, cub_bytes);
@@ -441,7 +472,13 @@ void insert_typed(const CacheStorage& cs, const SetHash& hash, const void* keys_
   const int N = static_cast<int>(n);
   size_t tmp = L.cub_bytes;
 
-  iota_kernel<<<blocks_for(n, T), T, 0, s>>>(L.pos, n);
+  if (key_bound > 0) {
+    bound_keys_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(keys, n, key_bound, out_of_bound_key,
+                                                           L.keys_clean, L.pos);
+    keys = L.keys_clean;
+  } else {
+    iota_kernel<<<blocks_for(n, T), T, 0, s>>>(L.pos, n);
+  }
   // keys known to lie in [0, key_bound) (rows of a linear backing table) need only that many sort
   // bits; the order among them, hence every result, is the same as with the full key width
   const int sort_bits = key_bound > 0 ? std::min<int>(bits_for(static_cast<uint64_t>(key_bound)),
@@ -462,7 +499,7 @@ void insert_typed(const CacheStorage& cs, const SetHash& hash, const void* keys_
       bits_for(static_cast<uint64_t>(n)), s));
   make_candidates_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(
       L.count_sorted, L.order_sorted, L.bin_key, L.bin_first, L.num_bins, n, max_modify,
-      1.0f / static_cast<float>(n), values, value_stride, from_table, hash, L.cand_key,
+      1.0f / static_cast<float>(n), values, value_stride, from_table, key_bound, hash, L.cand_key,
       L.cand_prio, L.cand_src, L.cand_set, L.cand_id);
   tmp = L.cub_bytes;
   NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(L.cub_tmp, tmp, L.cand_set, L.cand_set_sorted,
@@ -487,14 +524,16 @@ void cache_insert_select(const CacheStorage& cs, const SetHash& hash, nve_key_ty
                          const void* keys, int64_t n, const uint8_t* values, int64_t value_stride,
                          bool from_table, int64_t max_modify, int64_t global_ts, float decay_rate,
                          void* scratch, ModifyEntry* entries, uint32_t* num_entries,
-                         cudaStream_t stream, int64_t key_bound) {
+                         cudaStream_t stream, int64_t key_bound, int64_t out_of_bound_key) {
   NVE_B200_ARG(n > 0 && n < (int64_t{1} << 31), "cache insert: batch size out of range");
   if (key_type == NVE_KEY_INT64) {
     insert_typed<int64_t>(cs, hash, keys, n, values, value_stride, from_table, max_modify,
-                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound);
+                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound,
+                          out_of_bound_key);
   } else {
     insert_typed<int32_t>(cs, hash, keys, n, values, value_stride, from_table, max_modify,
-                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound);
+                          global_ts, decay_rate, scratch, entries, num_entries, stream, key_bound,
+                          out_of_bound_key);
   }
 }
 

@@ -39,7 +39,8 @@ void cache_insert_select(const CacheStorage& cs, const SetHash& hash, nve_key_ty
                          const void* keys, int64_t n, const uint8_t* values, int64_t value_stride,
                          bool from_table, int64_t max_modify, int64_t global_ts, float decay_rate,
                          void* scratch, ModifyEntry* entries, uint32_t* num_entries,
-                         cudaStream_t stream, int64_t key_bound = 0);
+                         cudaStream_t stream, int64_t key_bound = 0,
+                         int64_t out_of_bound_key = -1);
 
 // One entry per (key, way holding it); `values` may be null (invalidate).
 void cache_find_resident(const CacheStorage& cs, const SetHash& hash, nve_key_type_t key_type,

@@ -29,6 +29,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "../host/context.hpp"
 #include "device_common.cuh"
 
 namespace nve_b200 {
@@ -226,6 +227,18 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
 }
 
 // ---- gradient reduction ------------------------------------------------------------------
+// Set when a kernel found no room for a partial sum in the scratch it was given (the write is
+// skipped, never done out of bounds).  The host sizes the scratch from the batch, so this says that
+// the chunk map handed in does not belong to the batch.  Read and cleared by
+// nve_b200_dedup_grads_status.
+static __device__ int g_partial_overflow = 0;
+
+__device__ __forceinline__ bool partial_slot_ok(int64_t slot, int64_t partial_rows) {
+  if (slot < partial_rows) return true;
+  g_partial_overflow = 1;
+  return false;
+}
+
 struct GradParams {
   const uint8_t* grads;      // [n] rows
   int64_t grad_stride;
@@ -343,7 +356,7 @@ __global__ void __launch_bounds__(128) grad_reduce_kernel(const GradParams p) {
         int64_t first = c;
         while (first > 0 && ld_idx(p.loc_map, p.idx64, first - 1) == u) first--;
         const int64_t slot = 2 * (first - u) + (c - first);
-        if (on && slot < p.partial_rows) {
+        if (on && partial_slot_ok(slot, p.partial_rows)) {
           reinterpret_cast<float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[v0] = acc;
         }
         continue;
@@ -574,7 +587,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grad_stream_kernel(const GradPa
         while (group_first > 0 && static_cast<int>(loc_map[group_first - 1]) == u) group_first--;
       }
       const int64_t slot = 2 * (group_first - u) + (c - group_first);
-      if (col && slot < p.partial_rows) {
+      if (col && partial_slot_ok(slot, p.partial_rows)) {
         reinterpret_cast<float4*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[lane] = acc;
       }
       if (flags & 2) group_first = -1;
@@ -769,7 +782,7 @@ __global__ void __launch_bounds__(kHvWarps * 32) grad_heavy_kernel(const GradPar
     int64_t group_first = c;
     while (group_first > 0 && static_cast<int64_t>(loc_map[group_first - 1]) == u) group_first--;
     const int64_t slot = 2 * (group_first - u) + (c - group_first);
-    if (slot < p.partial_rows) {
+    if (partial_slot_ok(slot, p.partial_rows)) {
       reinterpret_cast<uint32_t*>(p.partial + slot * static_cast<int64_t>(p.nvec) * 4)[tid] = acc;
     }
   }
@@ -1120,13 +1133,12 @@ std::mutex g_static_mu;
 float* g_static_partial_addr[64] = {nullptr};  // by device ordinal
 }  // namespace
 
-// Device address of g_static_partial on the CURRENT device.  In host code the array's name is a
-// handle the runtime understands, not a device pointer: handing it to a kernel would fault or,
-// where the GPU can reach host memory, quietly use the wrong bytes.  The runtime translates it per
-// device, so this is done once per device, with that device current, and kernels get the result.
-static float* static_partial_for_current_device() {
-  int dev = 0;
-  NVE_B200_CUDA(cudaGetDevice(&dev));
+// Device address of g_static_partial on device `dev`, which must be current.  In host code the
+// array's name is a handle the runtime understands, not a device pointer: handing it to a kernel
+// would fault or, where the GPU can reach host memory, quietly use the wrong bytes.  The runtime
+// translates it per device, so this is done once per device, with that device current, and kernels
+// get the result.
+static float* static_partial_for_device(int dev) {
   NVE_B200_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
   std::lock_guard<std::mutex> lock(g_static_mu);
   if (g_static_partial_addr[dev] == nullptr) {
@@ -1137,7 +1149,40 @@ static float* static_partial_for_current_device() {
   return g_static_partial_addr[dev];
 }
 
+// The device a stream belongs to (the current device for the default-stream handles).
+static int device_of_stream(cudaStream_t stream) {
+  int dev = 0;
+  NVE_B200_CUDA(cudaGetDevice(&dev));
+  if (stream == nullptr || stream == cudaStreamLegacy || stream == cudaStreamPerThread) return dev;
+  int sdev = dev;
+  if (cudaStreamGetDevice(stream, &sdev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return dev;
+  }
+  return sdev;
+}
+
+// Whether a gradient reduction since the last call found its partial-sum scratch too small
+// (reads and clears the flag of the current device; synchronises the device).
+bool dedup_grads_take_overflow() {
+  int v = 0;
+  NVE_B200_CUDA(cudaMemcpyFromSymbol(&v, g_partial_overflow, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    NVE_B200_CUDA(cudaMemcpyToSymbol(g_partial_overflow, &zero, sizeof(int)));
+  }
+  return v != 0;
+}
+
 }  // namespace nve_b200
+
+extern "C" nve_status_t nve_b200_dedup_grads_status(int32_t* overflowed) {
+  using namespace nve_b200;
+  return guarded([&] {
+    NVE_B200_ARG(overflowed != nullptr, "dedup_grads_status: NULL output");
+    *overflowed = dedup_grads_take_overflow() ? 1 : 0;
+  });
+}
 
 extern "C" nve_status_t nve_b200_dedup_grads_static(
     nve_key_type_t key_type, int64_t max_run_size, const void* d_grads, int64_t grad_stride,
@@ -1157,6 +1202,9 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
     int64_t partial_rows = 0;
     float* partial = nullptr;
     int64_t max_chunks = num_keys;
+    // the scratch array and the kernels belong to the device of `stream`, whatever device the
+    // calling thread has current
+    const ScopedDevice on_stream_device(device_of_stream(static_cast<cudaStream_t>(stream)));
     if (max_run_size > 0) {
       // split groups park one partial row per chunk; at most 2 * (n / max_run + 1) + 2 rows
       partial_rows = 2 * (num_keys / max_run_size + 1) + 2;
@@ -1165,7 +1213,7 @@ extern "C" nve_status_t nve_b200_dedup_grads_static(
                    "dedup_grads_static: ", num_keys, " keys with runs of ", max_run_size, " and rows of ",
                    row_bytes, " bytes need ", need, " bytes of scratch; the built-in scratch holds ",
                    kStaticPartialBytes, " (use nve_b200_dedup_grads, which allocates)");
-      partial = static_partial_for_current_device();
+      partial = static_partial_for_device(device_of_stream(static_cast<cudaStream_t>(stream)));
       max_chunks = num_keys + num_keys / max_run_size + 1;
     }
     dedup_grads_run(key_type, d_grads, grad_stride, row_bytes, d_inverse, d_offsets,

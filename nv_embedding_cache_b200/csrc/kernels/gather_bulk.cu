@@ -105,8 +105,11 @@ void launch_gather_bulk(const GatherKernelParams& p, int64_t row_copy_bytes, cud
   bp.g = p;
   bp.row_bytes = static_cast<uint32_t>(row_copy_bytes);
   const size_t smem = static_cast<size_t>(kBulkWarps) * 2 * kBulkRows * row_copy_bytes;
-  static std::atomic<bool> attr_set{false};
-  if (smem > 48 * 1024 && !attr_set.exchange(true)) {
+  // the attribute belongs to the device: set it once per device ordinal
+  static std::atomic<bool> attr_set[64];
+  int dev = 0;
+  NVE_B200_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !attr_set[dev].exchange(true))) {
     NVE_B200_CUDA(cudaFuncSetAttribute(gather_bulk_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kBulkWarps * 2 * kBulkRows * kBulkMaxRowBytes));
