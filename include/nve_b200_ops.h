@@ -343,6 +343,115 @@ NVE_C_API nve_status_t nve_b200_shard_expand_slots(nve_key_type_t key_type, cons
                                                    const void* d_num_unique, int64_t n,
                                                    void* d_slot_of_position, void* stream);
 
+/* ---- row-sharded table as one object ------------------------------------------------------------
+ * A table of `world * local_rows` rows, row r on rank r mod world at local index r / world, served
+ * by one object per rank.  Replaces the reference's sharded memory block under a lookup layer
+ * (include/distributed.hpp:30-74 DistributedEnv / CUDADistributedBuffer, src/distributed.cpp:89-346,
+ * src/memblock_nvl.cpp:40-119): the reference maps all shards into one address range and lets its
+ * gather kernel read the peers; this object offers that form and the exchange form in C++, with no
+ * Python or torch on the lookup path.
+ *
+ * mode NVE_B200_SHARD_PEER: `peer_shards` holds the world base addresses of the shards as mapped into
+ * this GPU's address space (entry `rank` is the local shard).  A lookup is ONE fused kernel that reads
+ * every row from its owner (plain loads over NVLink) and pools; no collective, no host wait.
+ *
+ * mode NVE_B200_SHARD_EXCHANGE: a lookup de-duplicates the batch by hashing, sends every distinct
+ * key once to its owner, the owners read their rows, the rows come back, and the batch is pooled
+ * from the received rows.  The two exchanges are ncclSend / ncclRecv groups on the lookup stream,
+ * issued by the library on a communicator of its own (`nccl_unique_id`: the 128 bytes of
+ * nve_b200_nccl_unique_id from one rank, handed to every rank; creation is collective), or the
+ * caller's transport (`exchange_ops`).  One host wait per lookup (the per-owner counts), bounded by
+ * `exchange_timeout_ms`: when it runs out, or NCCL reports an asynchronous error, the communicator
+ * is aborted, the call returns NVE_ERROR_RUNTIME and every later lookup is refused.  world == 1 needs
+ * no transport and no host wait.
+ *
+ * Hot rows (both modes, `hot_capacity` > 0): the rows a key stream asks for most are replicated into
+ * every GPU's own memory (nve_b200_sharded_table_set_hot_keys); a 32-byte bitmap block per 224 keys
+ * tells the kernels which keys have a local copy.  Such keys cost no NVLink read and take no part in
+ * the exchange.  The copies are a snapshot: call set_hot_keys again after the shards were written.
+ */
+typedef struct nve_b200_sharded_table_s* nve_b200_sharded_table_t;
+
+typedef enum { NVE_B200_SHARD_PEER = 0, NVE_B200_SHARD_EXCHANGE = 1 } nve_b200_shard_mode_t;
+
+/* Transport of the exchange form when the caller brings its own (tests run several ranks inside one
+ * process this way).  Both calls enqueue on `stream` or complete before they return; non-zero = error. */
+typedef struct {
+  void* user;
+  /* d_out[r * count + i] = d_in[i] of rank r, for every rank r */
+  int (*all_gather_u32)(void* user, const uint32_t* d_in, uint32_t* d_out, int64_t count, void* stream);
+  /* rank p gets send_counts[p] elements of elem_bytes, taken in rank order from d_send; d_recv gets
+   * recv_counts[p] elements from rank p, in rank order.  The count arrays are HOST memory. */
+  int (*all_to_all_v)(void* user, const void* d_send, const int64_t* send_counts, void* d_recv,
+                      const int64_t* recv_counts, int64_t elem_bytes, void* stream);
+} nve_b200_exchange_ops_t;
+
+typedef struct {
+  int32_t world;
+  int32_t rank;
+  int32_t device_id;
+  nve_b200_shard_mode_t mode;
+  void* local_shard;            /* [local_rows] rows at row_stride, device memory */
+  int64_t local_rows;
+  int64_t row_stride;           /* bytes, a multiple of 16 */
+  nve_data_type_t value_dtype;  /* FLOAT16 or FLOAT32 */
+  int64_t row_width;            /* values per row; row bytes a multiple of 16, at most 512 */
+  nve_key_type_t key_type;
+  int64_t default_row_index;    /* >= 0: keys outside [0, world * local_rows) read this (global) row */
+  int64_t max_keys;             /* most keys of one lookup */
+  const void* const* peer_shards;            /* PEER: world addresses */
+  const void* nccl_unique_id;                /* EXCHANGE, world > 1, built-in transport */
+  const nve_b200_exchange_ops_t* exchange_ops; /* EXCHANGE, world > 1, caller's transport (copied) */
+  int64_t hot_capacity;         /* rows of the replicated hot-row table; 0 = none */
+  int64_t exchange_timeout_ms;  /* 0 = 30 000 */
+} nve_b200_sharded_table_config_t;
+
+/* 128 bytes identifying a new NCCL communicator (ncclGetUniqueId); call on one rank and hand the
+ * bytes to every rank's nve_b200_sharded_table_create.  NCCL is looked up at run time
+ * (libnccl.so.2, the copy already in the process if there is one); NVE_ERROR_RUNTIME without it. */
+NVE_C_API nve_status_t nve_b200_nccl_unique_id(void* out_128_bytes);
+
+NVE_C_API nve_status_t nve_b200_sharded_table_create(nve_b200_sharded_table_t* out,
+                                                     const nve_b200_sharded_table_config_t* config);
+NVE_C_API nve_status_t nve_b200_sharded_table_destroy(nve_b200_sharded_table_t table);
+
+typedef struct {
+  const void* keys;             /* device, global row ids */
+  int64_t num_keys;
+  nve_pooling_type_t pooling_type; /* SUM, MEAN, WEIGHTED_SUM, WEIGHTED_MEAN */
+  nve_sparse_type_t sparse_type;
+  const void* csr_offsets;      /* device, num_bags + 1 entries */
+  int32_t offset_bytes;         /* 4 or 8 */
+  int64_t num_bags;
+  int64_t fixed_hotness;
+  const void* weights;          /* device, per key */
+  nve_data_type_t weight_dtype;
+  void* output;                 /* device, [num_bags][row_width] */
+  int64_t output_stride;
+  nve_data_type_t output_dtype; /* FLOAT32 or FLOAT16 */
+} nve_b200_sharded_lookup_t;
+
+/* Pooled lookup; results are those of nve_b200_lookup_pool on the unsharded table (same order of
+ * additions, same roundings).  EXCHANGE with world > 1 is collective: every rank calls it, in the
+ * same order. */
+NVE_C_API nve_status_t nve_b200_sharded_table_lookup_pooled(nve_b200_sharded_table_t table,
+                                                            const nve_b200_sharded_lookup_t* lookup,
+                                                            void* stream);
+
+/* Chooses the hot rows from a sample of the key stream (device, n keys, repeats welcome: the keys
+ * seen most often win when there are more distinct keys than hot_capacity), copies their rows into
+ * the local hot table and builds the index.  n == 0 empties the hot table.  Blocks until done; no
+ * lookup of this table may run meanwhile.  Collective in EXCHANGE mode with world > 1 (the rows
+ * come through the exchange).  *num_hot (optional) receives the number of hot rows. */
+NVE_C_API nve_status_t nve_b200_sharded_table_set_hot_keys(nve_b200_sharded_table_t table,
+                                                           const void* d_keys, int64_t n,
+                                                           int64_t* num_hot, void* stream);
+
+/* Figures of the last lookup of this rank: out[0] distinct keys sent (exchange) or -1, out[1] keys
+ * served to others and itself (exchange) or -1, out[2] hot rows in the table, out[3] bytes this rank
+ * sent over the fabric in the last exchange (keys out + rows out), out[4..7] reserved (0). */
+NVE_C_API nve_status_t nve_b200_sharded_table_stats(nve_b200_sharded_table_t table, int64_t out[8]);
+
 /*
  * Masked row copy, the merge step of a multi-tier lookup: d_dst[i] = d_src[i] (row_bytes each) for
  * every position i < num_rows whose bit in d_hit_mask is 0; positions whose bit is 1 were served by

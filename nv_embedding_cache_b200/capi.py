@@ -68,6 +68,33 @@ class GatherArgs(C.Structure):
                 ("miss_keys", _vp), ("miss_list_len", _vp)]
 
 
+SHARD_PEER, SHARD_EXCHANGE = 0, 1
+
+# transport callbacks of the exchange form (nve_b200_exchange_ops_t)
+ALL_GATHER_U32_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, _vp, _i64, _vp)
+ALL_TO_ALL_V_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, C.POINTER(_i64), _vp, C.POINTER(_i64), _i64, _vp)
+
+
+class ExchangeOps(C.Structure):
+    _fields_ = [("user", _vp), ("all_gather_u32", ALL_GATHER_U32_FN), ("all_to_all_v", ALL_TO_ALL_V_FN)]
+
+
+class ShardedTableConfig(C.Structure):
+    _fields_ = [("world", _i32), ("rank", _i32), ("device_id", _i32), ("mode", C.c_int),
+                ("local_shard", _vp), ("local_rows", _i64), ("row_stride", _i64), ("value_dtype", _i32),
+                ("row_width", _i64), ("key_type", C.c_int), ("default_row_index", _i64),
+                ("max_keys", _i64), ("peer_shards", C.POINTER(_vp)), ("nccl_unique_id", _vp),
+                ("exchange_ops", C.POINTER(ExchangeOps)), ("hot_capacity", _i64),
+                ("exchange_timeout_ms", _i64)]
+
+
+class ShardedLookup(C.Structure):
+    _fields_ = [("keys", _vp), ("num_keys", _i64), ("pooling_type", C.c_int), ("sparse_type", C.c_int),
+                ("csr_offsets", _vp), ("offset_bytes", _i32), ("num_bags", _i64), ("fixed_hotness", _i64),
+                ("weights", _vp), ("weight_dtype", _i32), ("output", _vp), ("output_stride", _i64),
+                ("output_dtype", _i32)]
+
+
 class NveError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"nve status {status}: {message}")
@@ -162,6 +189,12 @@ PROTOTYPES = {
     "nve_b200_dedup_grads_static": (_i32, [C.c_int, _i64, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
                                             _vp, _vp, _i64, _i32, _i64, C.c_float, _vp]),
     "nve_b200_dedup_grads_status": (_i32, [C.POINTER(_i32)]),
+    "nve_b200_nccl_unique_id": (_i32, [_vp]),
+    "nve_b200_sharded_table_create": (_i32, [C.POINTER(_vp), C.POINTER(ShardedTableConfig)]),
+    "nve_b200_sharded_table_destroy": (_i32, [_vp]),
+    "nve_b200_sharded_table_lookup_pooled": (_i32, [_vp, C.POINTER(ShardedLookup), _vp]),
+    "nve_b200_sharded_table_set_hot_keys": (_i32, [_vp, _vp, _i64, C.POINTER(_i64), _vp]),
+    "nve_b200_sharded_table_stats": (_i32, [_vp, C.POINTER(_i64)]),
     "nve_b200_update_rows": (_i32, [_vp, _i64, _i64, _i32, _i64, C.c_int, _vp, _i64, _vp, _i64,
                                      C.c_int, C.c_int, _vp]),
     "nve_b200_dedup_grads_f16": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp]),

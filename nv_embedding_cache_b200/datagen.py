@@ -34,9 +34,10 @@ def affine_permute(ranks: np.ndarray, num_rows: int, seed: int = PERM_SEED) -> n
     while np.gcd(a, num_rows) != 1:
         a += 2
     b = int(rng.integers(0, num_rows))
-    # 128-bit safe: split multiplication through Python ints only when it could overflow
-    if num_rows < (1 << 31):
-        return ((ranks.astype(np.uint64) * np.uint64(a) + np.uint64(b)) % np.uint64(num_rows)).astype(np.int64)
+    # a, r < 2^32 keeps a * r inside 64 bits; larger tables go through Python integers
+    if num_rows < (1 << 32):
+        n = np.uint64(num_rows)
+        return (((ranks.astype(np.uint64) * np.uint64(a)) % n + np.uint64(b)) % n).astype(np.int64)
     out = np.empty_like(ranks)
     for i, r in enumerate(ranks.tolist()):
         out[i] = (a * r + b) % num_rows
@@ -48,6 +49,53 @@ def zipf_keys(n: int, num_rows: int, alpha: float, seed: int, perm: np.ndarray |
     if perm is not None:
         return perm[ranks]
     return affine_permute(ranks, num_rows)
+
+
+_MASK64 = (1 << 64) - 1
+
+
+def hashed_rows_f16(row_ids: np.ndarray, width: int, seed: int, scale: float = 0.08) -> np.ndarray:
+    """Rows of a table too large to generate with a sequential generator: element (r, c) is a
+    function of (seed, r, c) alone -- an 11-bit field of a splitmix64 hash, centred and scaled to
+    [-scale/2, scale/2) -- so any subset of rows can be produced anywhere.  The device-side twin is
+    fill_hashed_rows_f16 (torch); both give the same bytes."""
+    r = np.asarray(row_ids, dtype=np.uint64).reshape(-1, 1)
+    c = np.arange(width, dtype=np.uint64).reshape(1, -1)
+    with np.errstate(over="ignore"):
+        x = r * np.uint64(width) + c + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        x = x ^ (x >> np.uint64(31))
+    f = (x >> np.uint64(53)).astype(np.float32) * np.float32(2.0 ** -11) - np.float32(0.5)
+    return (f * np.float32(scale)).astype(np.float16)
+
+
+def fill_hashed_rows_f16(dst, first_row: int, row_step: int, seed: int, scale: float = 0.08,
+                         chunk_rows: int = 1 << 21):
+    """dst[i] = hashed_rows_f16([first_row + i * row_step]) for a torch fp16 tensor [rows, width] on
+    any device, computed chunk-wise on dst's device with 64-bit integer tensor arithmetic (which
+    wraps like the numpy form; logical shifts are arithmetic shifts with the sign bits masked)."""
+    import torch
+    rows, width = dst.shape
+    dev = dst.device if dst.device.type == "cuda" else torch.device("cuda", torch.cuda.current_device())
+
+    def wrap(v):      # Python int -> the int64 with the same low 64 bits
+        v &= _MASK64
+        return v - (1 << 64) if v >= (1 << 63) else v
+
+    def shr(x, k):
+        return (x >> k) & ((1 << (64 - k)) - 1)
+    c = torch.arange(width, dtype=torch.int64, device=dev).reshape(1, -1)
+    salt = wrap(seed * 0x9E3779B97F4A7C15)
+    for r0 in range(0, rows, chunk_rows):
+        r1 = min(rows, r0 + chunk_rows)
+        r = (torch.arange(r0, r1, dtype=torch.int64, device=dev) * row_step + first_row).reshape(-1, 1)
+        x = r * width + c + salt
+        x = (x ^ shr(x, 30)) * wrap(0xBF58476D1CE4E5B9)
+        x = (x ^ shr(x, 27)) * wrap(0x94D049BB133111EB)
+        x = x ^ shr(x, 31)
+        f = shr(x, 53).to(torch.float32) * (2.0 ** -11) - 0.5
+        dst[r0:r1].copy_((f * scale).to(torch.float16))
 
 
 def uniform_keys(n: int, num_rows: int, seed: int) -> np.ndarray:

@@ -1,5 +1,7 @@
 """GPU checks of the row-sharded table: the routing kernels against numpy, the full lookup at
-world size 1 against the oracle, and (when the box has at least 2 GPUs) a 2-rank NCCL run."""
+world size 1 against the oracle, and (when the box has at least 2 GPUs) 2-rank runs of every form:
+the exchange form over the library's own NCCL communicator, the peer form over symmetric memory,
+each with and without hot rows, and the peer form with the cache in front."""
 import ctypes as C
 import os
 import socket
@@ -93,10 +95,13 @@ if mode.startswith("peer"):
 else:
     shard = torch.from_numpy(table[rank::world].copy()).cuda()
 cached = mode == "peer_cached"
-if cached:
-    mode = "peer"
-t = ShardedEmbeddingTable(shard, max_keys=1 << 16, mode=mode,
+hot = mode.endswith("_hot")
+mode = mode.split("_")[0]
+t = ShardedEmbeddingTable(shard, max_keys=1 << 16, mode=mode, hot_rows=3000 if hot else 0,
                           cache_bytes=(2000 // 8) * (64 + 8 * dim * 2 + 32) if cached else 0)
+if hot:     # the rows a sample of the key stream asks for most are replicated on every rank
+    sample = np.concatenate([dg.zipf_keys(8192, total, 1.05, 300 + b + rank, dg.permutation(total)) for b in range(3)])
+    assert 0 < t.set_hot_keys(torch.from_numpy(sample).cuda()) <= 3000
 ok = True
 hits = 0
 for step in range(3):
@@ -121,7 +126,7 @@ sys.exit(0 if int(flag.item()) == 1 else 3)
 '''
 
 
-@pytest.mark.parametrize("mode", ["alltoall", "peer", "peer_cached"])
+@pytest.mark.parametrize("mode", ["alltoall", "alltoall_hot", "peer", "peer_hot", "peer_cached"])
 def test_two_ranks_nccl(torch_cuda, tmp_path, mode):
     torch = torch_cuda
     if torch.cuda.device_count() < 2:
