@@ -3,24 +3,29 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config "GPULayer, fully HBM-resident"): 8 independent tables of 4,000,000 rows x
-128 fp16 (N(0, 0.02)); per table 65,536 bags of 1..32 int64 keys, Zipf(1.1) over a permuted row
-order, CSR offsets, mean pooling accumulated in fp32, output [65536,128] fp16.  One *step* is one
-pooled lookup of every table (8 launches of the fused gather+pool kernel).  Tables and key batches
-are seeded synthetic data.  With N > 1 every rank serves its own 8 tables (independent tables: no
-data-path collective, weak scaling).
+Headline workload (BASELINE config "GPULayer, fully HBM-resident"): 8 independent tables of
+4,000,000 rows x 128 fp16 (N(0, 0.02)); per table 65,536 bags of 1..32 int64 keys, Zipf(1.1) over a
+permuted row order, CSR offsets, mean pooling accumulated in fp32, output [65536,128] fp16.  One
+*step* is one pooled lookup of every table (8 launches of the fused gather+pool kernel).  Tables and
+key batches are seeded synthetic data.  With N > 1 every rank serves its own 8 tables (independent
+tables: no data-path collective, weak scaling).
 
-Prints ONE JSON line (rank 0).
+The JSON line (rank 0) also carries, measured in the same run:
+  sharded    the NVLink-sharded table (250M x W rows x 64 fp16, 32 GB per GPU) at this world size: the
+             peer form, the peer form behind the replicated hot-row table and the exchange form, each
+             with keys/s, NVLink GB/s per rank, a parity flag against the oracle and its clock record
+  workloads  (one GPU) int8 dequantise + pool, gradient de-duplication + update, and the cached gather
+             from a 25.6 GB host table, each with roofline, clocks, end-to-end and CPU figures
+  low_reuse  (one GPU) the headline kernel on key streams that really reach HBM
+  copy_probe (several GPUs) what the host side gives all ranks' pinned copies at once
 """
 from __future__ import annotations
 
 import argparse
-import ctypes as C
 import json
 import os
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -36,146 +41,34 @@ ROW_BYTES = WIDTH * 2
 NUM_BAGS = 65_536
 ALPHA = 1.1
 NUM_BATCHES = 4          # distinct key batches per table, cycled over the steps
+REPEATS = 5              # timed regions per leg; the median one is reported
 METRIC = "embedding keys/sec (find-and-combine)"
 WORKLOAD = "C2 GPULayer HBM-resident: 8 tables x 4M x 128 fp16, 65536 CSR bags len U[1,32], Zipf(1.1), mean pool fp32 acc"
 
 
-def make_batch(table_idx: int, batch_idx: int, rank: int, perm: np.ndarray):
+def bench_config(world: int) -> dict:
+    """The workload both arms measure (identical keys and values in both JSON lines)."""
+    return {"workload": WORKLOAD, "tables_per_gpu": NUM_TABLES, "rows_per_table": NUM_ROWS,
+            "bags_per_table": NUM_BAGS, "key_batches_cycled": NUM_BATCHES,
+            "l2": "inputs larger than L2 (8.2 GB of tables, 4 key batches cycled)",
+            "parallelism": f"replicas x{world} (independent tables, no collective)"}
+
+
+def make_batch(table_idx: int, batch_idx: int, rank: int, perm: np.ndarray, alpha: float = ALPHA,
+               num_rows: int = NUM_ROWS):
     from nv_embedding_cache_b200 import datagen as dg
     seed = 1000 + 200 + 10 * table_idx + batch_idx + 1000 * rank
     _, offsets = dg.csr_bags(NUM_BAGS, 1, 32, seed)
-    keys = dg.zipf_keys(int(offsets[-1]), NUM_ROWS, ALPHA, seed + 5000, perm)
+    if alpha is None:
+        keys = dg.uniform_keys(int(offsets[-1]), num_rows, seed + 5000)
+    else:
+        keys = dg.zipf_keys(int(offsets[-1]), num_rows, alpha, seed + 5000, perm)
     return keys, offsets
 
 
 def algorithmic_bytes(num_keys: int) -> int:
     """Bytes one pooled lookup must move: keys + rows read, offsets read, pooled rows written."""
     return num_keys * (8 + ROW_BYTES) + (NUM_BAGS + 1) * 8 + NUM_BAGS * ROW_BYTES
-
-
-class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs: a background
-    thread polls continuously and `sample_now()` takes one more reading while the queued work of
-    the region is still executing."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int, uuid: str | None = None):
-        self.gpu_index = gpu_index
-        self.rows = []
-        self._lock = threading.Lock()
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        # NVML in-process when the binding is there (a query is a few microseconds and touches one
-        # device); otherwise one nvidia-smi process per sample.
-        self._nvml = None
-        self._handle = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            if uuid:
-                try:
-                    self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
-                except Exception:
-                    self._handle = None
-            if self._handle is None:
-                self._handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
-            self._nvml = pynvml
-        except Exception:
-            self._nvml = None
-
-    def _sample_nvml(self):
-        n, h = self._nvml, self._handle
-        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
-        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
-        try:
-            power = n.nvmlDeviceGetPowerUsage(h) / 1000.0
-        except Exception:
-            power = 0.0
-        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-            n.nvmlDeviceGetCurrentClocksThrottleReasons
-        bits = int(get(h))
-        flag = lambda mask: "Active" if bits & mask else "Not Active"   # NVML reason bits
-        return [str(sm), str(mx), f"{power:.1f}", flag(0x8), flag(0x40), flag(0x20), flag(0x4)]
-
-    def sample_now(self):
-        try:
-            if self._nvml is not None:
-                row = self._sample_nvml()
-                with self._lock:
-                    self.rows.append(row)
-                return
-            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}",
-                                  "--format=csv,noheader,nounits", "-i", str(self.gpu_index)],
-                                 capture_output=True, text=True, timeout=10).stdout.strip()
-            if out:
-                with self._lock:
-                    self.rows.append([x.strip() for x in out.splitlines()[0].split(",")])
-        except Exception:
-            pass
-
-    def _run(self):
-        while not self._stop.is_set():
-            self.sample_now()
-            self._stop.wait(0.2)
-
-    def __enter__(self):
-        self._thread.start()
-        return self
-
-    def __exit__(self, *a):
-        self._stop.set()
-        self._thread.join(timeout=15)
-
-    def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, val in zip(names, r[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
-
-
-def measured_hbm_peak():
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
-
-
-def cpu_reference_run(table_host: np.ndarray, batches, seconds_budget: float, min_calls: int = 3):
-    """Times the reference CPU implementation (HostEmbeddingLayer over a LinearHostTable, the
-    unmodified reference sources built into oracle/_ref) on one table's pooled lookups."""
-    from oracle.pyoracle import Reference
-    ref = Reference()
-    layer = ref.layer(table_host.view(np.uint8).reshape(NUM_ROWS, ROW_BYTES), "f16")
-    workers = layer.num_workers
-    out = np.zeros((NUM_BAGS, WIDTH), dtype=np.float16)
-    keys, offsets = batches[0]
-    layer.lookup_pooled(keys, "mean", WIDTH, offsets=offsets, out_dtype="f16", out=out)  # warm-up
-    times, total_keys, i = [], 0, 0
-    t_end = time.perf_counter() + seconds_budget
-    while len(times) < min_calls or time.perf_counter() < t_end:
-        keys, offsets = batches[i % len(batches)]
-        t0 = time.perf_counter()
-        layer.lookup_pooled(keys, "mean", WIDTH, offsets=offsets, out_dtype="f16", out=out)
-        times.append(time.perf_counter() - t0)
-        total_keys += keys.size
-        i += 1
-        if len(times) >= 200:
-            break
-    layer.close()
-    return total_keys / sum(times), workers, len(times), float(np.median(times))
 
 
 def load_reference_gpu():
@@ -188,17 +81,20 @@ def load_reference_gpu():
         return None
 
 
+# ---- reference arm: the reference's own CPU path on this box's host cores ----------------------------
 def run_reference_arm(args):
-    """--impl reference: the reference's own CPU path on this box's host cores."""
+    """--impl reference: HostEmbeddingLayer over a LinearHostTable (the unmodified reference sources
+    built into oracle/_ref, with the SIMD flags its own build picks on this host), one table's pooled
+    lookup per step, default thread pool."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from nv_embedding_cache_b200 import datagen as dg
+    from oracle.pyoracle import Reference
     perm = dg.permutation(NUM_ROWS)
     table = dg.normal_table(NUM_ROWS, WIDTH, 0.02, 20, np.float16)
     batches = [make_batch(0, b, 0, perm) for b in range(NUM_BATCHES)]
-    from oracle.pyoracle import Reference
-    ref = Reference()
+    ref = Reference(for_timing=True)
     layer = ref.layer(table.view(np.uint8).reshape(NUM_ROWS, ROW_BYTES), "f16")
     workers = layer.num_workers
     out = np.zeros((NUM_BAGS, WIDTH), dtype=np.float16)
@@ -208,44 +104,75 @@ def run_reference_arm(args):
         layer.lookup_pooled(keys, "mean", WIDTH, offsets=offsets, out_dtype="f16", out=out)
         return keys.size
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 1)):
         step(i)
-    t0 = time.perf_counter()
-    nkeys = 0
-    for i in range(args.steps):
+    times, nkeys = [], 0
+    t_end = time.perf_counter() + args.cpu_seconds
+    i = 0
+    while i < args.steps or (args.cpu_seconds > 0 and time.perf_counter() < t_end and i < 400):
+        t0 = time.perf_counter()
         nkeys += step(i)
-    dt = time.perf_counter() - t0
+        times.append(time.perf_counter() - t0)
+        i += 1
     layer.close()
+    dt = float(sum(times))
     value = nkeys / dt
-    sample = (f"each step = one table's pooled lookup ({batches[0][0].size} keys, 65536 bags) of the "
-              f"8-table workload, {args.steps} steps")
+    sample = (f"each step = one table's pooled lookup ({batches[0][0].size} keys, 65536 bags) of the 8-table "
+              f"workload; {len(times)} steps, median {np.median(times) * 1e3:.1f} ms, mean {np.mean(times) * 1e3:.1f} ms "
+              f"per step; reference CPU sources built with {ref.simd}")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "keys/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * dt / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": 1e3 * dt / max(1, len(times)), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "config": bench_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "keys/s", "cores": int(workers),
-                         "kind": "reference", "sample": sample, "host_cpus": os.cpu_count()},
+                         "kind": "reference", "sample": sample, "host_cpus": os.cpu_count(),
+                         "median_keys_per_s": batches[0][0].size / float(np.median(times))},
         "e2e": {"value": value, "unit": "keys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    from nv_embedding_cache_b200 import capi, datagen as dg
-    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+def cpu_baseline_in_child(seconds: float):
+    """The reference arm in a process of its own, before this process touches the GPU: the same code
+    and the same conditions as `--impl reference`, so the two figures of one box agree."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "5", "--warmup", "2",
+           "--cpu-seconds", str(seconds)]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    for line in reversed(res.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)["cpu_baseline"]
+    raise RuntimeError(f"reference arm gave no line: {res.stderr[-400:]}")
 
+
+# ---- this library --------------------------------------------------------------------------------------
+def run_ours(args):
+    skip = set(filter(None, args.skip.split(",")))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    # the CPU baseline first, in a child process, while this process holds no GPU memory, no pinned
+    # buffers and no sampler thread
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cpu_baseline = cpu_baseline_in_child(args.cpu_seconds)
+        except Exception as e:  # the checker library is absent: report, do not fake
+            cpu_baseline = {"value": None, "unit": "keys/s", "cores": 0, "kind": "reference",
+                            "sample": f"unavailable: {e}"}
+
+    import torch
+    import torch.distributed as dist
+    import bench_workloads as bw
+    from nv_embedding_cache_b200 import datagen as dg
+    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the lookup path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
 
     # ---- tables (seeded, generated on the device) and key batches (seeded numpy)
     gen = torch.Generator(device=dev)
@@ -286,68 +213,29 @@ def run_ours(args):
                for _ in range(NUM_TABLES)]
 
     def step_device(i):
-        n = 0
         for t in range(NUM_TABLES):
             k, o = dev_batches[t][i % NUM_BATCHES]
             layers[t].lookup_pooled(ctxs[t], k.numel(), k, dev_out[t], ROW_BYTES, "mean", "float16",
                                     csr_offsets=o, num_csr_offsets=o.numel())
-            n += k.numel()
-        return n
 
     def step_host(i):
-        n = hb = 0
         for t in range(NUM_TABLES):
             k, o = pin_batches[t][i % NUM_BATCHES]
             layers[t].lookup_pooled(ctxs_e2e[t], k.numel(), k, pin_out[t], ROW_BYTES, "mean",
                                     "float16", csr_offsets=o, num_csr_offsets=o.numel())
-            n += k.numel()
-            hb += k.numel() * 8 + o.numel() * 8
-        return n, hb
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup, fan_out):
-        for i in range(warmup):
-            fn(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank, str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or "")) as clk:
-            e0.record(stream)
-            if fan_out:
-                for ts in table_streams:
-                    ts.wait_event(e0)
-            keys = 0
-            extra = 0
-            for i in range(steps):
-                r = fn(warmup + i)
-                if isinstance(r, tuple):
-                    keys += r[0]
-                    extra += r[1]
-                else:
-                    keys += r
-            if fan_out:
-                for ts in table_streams:
-                    ev = torch.cuda.Event()
-                    ev.record(ts)
-                    stream.wait_event(ev)
-            e1.record(stream)
-            clk.sample_now()   # the queue of this region is still draining
-            barrier()
-        ms = e0.elapsed_time(e1)
-        return ms, keys, extra, clk.summary()
+    keys_of_step = [sum(dev_batches[t][b][0].numel() for t in range(NUM_TABLES)) for b in range(NUM_BATCHES)]
+    h2d_of_step = [sum((k.numel() + o.numel()) * 8 for k, o in (pin_batches[t][b] for t in range(NUM_TABLES)))
+                   for b in range(NUM_BATCHES)]
 
     # One step of the device-resident leg is eight short launches issued from Python, about as long
     # on the host as on the GPU.  Each of the four cycled steps is therefore captured once as a CUDA
     # graph and replayed (same kernels, same arguments); --no-graph, or a capture that fails, keeps
-    # the direct launches.
+    # the direct launches.  The capture runs BEFORE the process group of a multi-rank run exists, so
+    # every rank captures exactly as a single-rank run does, with no communicator and none of its
+    # threads in the process, and every world size measures the same launch mode.
     graphs = []
-    # Single-rank runs only: with a NCCL process group alive in the process the capture was seen not
-    # to complete on an 8-rank run, so multi-rank runs keep the direct launches.
-    if not args.no_graph and world == 1:
+    if not args.no_graph:
         try:
             with torch.cuda.stream(stream):
                 for b in range(NUM_BATCHES):
@@ -362,16 +250,51 @@ def run_ours(args):
             print(f"graph capture failed ({e!r}); launching directly", file=sys.stderr)
             graphs = []
             torch.cuda.synchronize()
-    keys_of_step = [sum(k.numel() for k, _ in (dev_batches[t][b] for t in range(NUM_TABLES)))
-                    for b in range(NUM_BATCHES)]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
 
     def step_replay(i):
         graphs[i % NUM_BATCHES].replay()
-        return keys_of_step[i % NUM_BATCHES]
 
+    def region(fn, steps, fan_out):
+        """One timed region of exactly `steps` steps: barrier + synchronize on both sides, CUDA events
+        on the launching stream, the maximum over the ranks."""
+        bw.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        if fan_out:
+            for ts in table_streams:
+                ts.wait_event(e0)
+        for i in range(steps):
+            fn(i)
+        if fan_out:
+            for ts in table_streams:
+                ev = torch.cuda.Event()
+                ev.record(ts)
+                stream.wait_event(ev)
+        e1.record(stream)
+        bw.barrier()
+        return bw.reduce_max(e0.elapsed_time(e1))
+
+    # steps cycle the four batches: a region of K steps looks up sum over i < K of keys_of_step[i % 4]
+    keys_region = sum(keys_of_step[i % NUM_BATCHES] for i in range(args.steps))
+    h2d_region = sum(h2d_of_step[i % NUM_BATCHES] for i in range(args.steps))
     with torch.cuda.stream(stream):
-        ms_dev, keys_dev, _, clocks = timed(step_replay if graphs else step_device, args.steps, args.warmup, False)
-        ms_e2e, keys_e2e, h2d, _ = timed(step_host, args.steps, args.warmup, True)
+        dev_fn = step_replay if graphs else step_device
+        for i in range(args.warmup):
+            dev_fn(i)
+        with bw.ClockSampler.for_current_device(period_s=0.004) as clk:
+            dev_regions = [region(dev_fn, args.steps, False) for _ in range(REPEATS)]
+            clk.sample_now()
+        clocks = clk.summary()
+        for i in range(args.warmup):
+            step_host(i)
+        e2e_regions = [region(step_host, args.steps, True) for _ in range(3)]
+    ms_dev = float(np.median(dev_regions))
+    ms_e2e = float(np.median(e2e_regions))
+    value = bw.reduce_sum(keys_region) / (ms_dev * 1e-3)
+    e2e_value = bw.reduce_sum(keys_region) / (ms_e2e * 1e-3)
 
     # ---- per-launch times outside the timed region (this rank): back-to-back launches, and launches
     # that each follow a 256 MB write, which leaves nothing of the tables or keys in L2
@@ -396,31 +319,11 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         per_launch = {"back_to_back": launch_times(False), "cold_l2": launch_times(True)}
 
-    # ---- max over ranks, whole-job totals
-    def reduce_max(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def reduce_sum(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    ms_dev_max, ms_e2e_max = reduce_max(ms_dev), reduce_max(ms_e2e)
-    keys_dev_all, keys_e2e_all = reduce_sum(keys_dev), reduce_sum(keys_e2e)
-    value = keys_dev_all / (ms_dev_max * 1e-3)
-    e2e_value = keys_e2e_all / (ms_e2e_max * 1e-3)
-
     # ---- roofline of the dominant kernel (this rank): algorithmic bytes per launch / mean launch time
     launches = args.steps * NUM_TABLES
     mean_launch_s = ms_dev * 1e-3 / launches
-    alg_bytes = algorithmic_bytes(keys_dev // launches)
-    peak, peak_kind = measured_hbm_peak()
+    alg_bytes = algorithmic_bytes(keys_region // launches)
+    peak, peak_kind = bw.hbm_peak()
     achieved = alg_bytes / mean_launch_s / 1e9
     roofline = {"bound": "hbm", "kernel": "pool_dense_kernel<F16,GROUP=16,U=4>",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -429,40 +332,31 @@ def run_ours(args):
     traffic_file = ROOT / "profiles" / "lookup_pool_f16_c2.traffic.json"
     if traffic_file.exists():
         roofline["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+        if roofline["traffic"]:
+            roofline["frac_on_dram_bytes"] = roofline["traffic"] / mean_launch_s / 1e9 / peak
 
     out = {
         "metric": METRIC, "value": value, "unit": "keys/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_dev_max / args.steps, "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tables_per_gpu": NUM_TABLES,
-                   "keys_per_step_per_gpu": keys_dev // args.steps,
-                   "l2": "inputs larger than L2 (8.2 GB of tables, 4 key batches cycled)",
-                   "launch": "CUDA graph of one step (8 kernels), replayed" if graphs else "direct launches",
-                   "parallelism": f"replicas x{world} (independent tables, no collective)"},
+        "config": bench_config(world),
+        "launch": "CUDA graph of one step (8 kernels), replayed" if graphs else "direct launches",
+        "keys_per_step_per_gpu": keys_region // args.steps,
+        "timing": {"regions": REPEATS, "reported": "median region; every region is exactly `steps` steps between "
+                   "barrier + synchronize, CUDA events on the launching stream, max over ranks",
+                   "region_ms": [round(r, 4) for r in dev_regions], "e2e_region_ms": [round(r, 4) for r in e2e_regions]},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "keys/s",
-                "h2d_bytes_per_step": h2d // args.steps,
+                "h2d_bytes_per_step": h2d_region // args.steps,
                 "d2h_bytes_per_step": NUM_TABLES * NUM_BAGS * ROW_BYTES,
-                "ms_per_step": ms_e2e_max / args.steps},
-        "gpu_launches": 2 * launches + 2 * args.warmup * NUM_TABLES,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": (REPEATS + 3) * launches,
         "roofline": roofline,
         "algo_bw_gib_s": value * ROW_BYTES / 2**30,
         "per_launch": per_launch,
     }
-
-    # ---- CPU baseline beside it (rank 0, N=1 only): reference HostEmbeddingLayer on table 0
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        try:
-            table_host = tables[0].cpu().numpy()
-            v, workers, calls, med = cpu_reference_run(table_host, host_batches[0], args.cpu_seconds)
-            out["cpu_baseline"] = {
-                "value": v, "unit": "keys/s", "cores": int(workers), "kind": "reference",
-                "host_cpus": os.cpu_count(),
-                "sample": f"{calls} pooled lookups of table 0 ({host_batches[0][0][0].size} keys, "
-                          f"65536 bags each; 1/8 of a step), median {med * 1e3:.1f} ms per lookup"}
-        except Exception as e:  # the checker library is absent: report, do not fake
-            out["cpu_baseline"] = {"value": None, "unit": "keys/s", "cores": 0, "kind": "reference",
-                                   "sample": f"unavailable: {e}"}
+    if cpu_baseline is not None:
+        out["cpu_baseline"] = cpu_baseline
 
     # ---- the reference's own GPU kernel for this lookup on the same GPU (rank 0, N=1 only):
     # find_and_combine reading the table directly, timed on table 0's four batches
@@ -482,21 +376,103 @@ def run_ours(args):
                 "us_per_launch": ms * 1e3, "value": nk / (ms * 1e-3), "unit": "keys/s",
                 "sample": "table 0, 4 batches cycled, 100 launches"}
 
+    # ---- the same kernel on key streams that reach HBM (one GPU): uniform keys over a 4M-row table,
+    # and Zipf(1.1) over a table ten times larger
+    if world == 1 and "low_reuse" not in skip:
+        with torch.cuda.stream(stream):
+            out["low_reuse"] = low_reuse_runs(args, torch, bw, dg, GPUEmbeddingLayer, tables[0], dev, stream)
+
     for c in ctxs + ctxs_e2e:
         c.wait()
         c.destroy()
     for layer in layers:
         layer.destroy()
+    del tables, dev_batches, pin_batches, dev_out, pin_out, graphs
+    torch.cuda.empty_cache()
+
+    if world > 1 and "copy_probe" not in skip:
+        out["copy_probe"] = bw.copy_probe()
+    if "sharded" not in skip:
+        kw = {"rows_per_rank": args.shard_rows} if args.shard_rows > 0 else {}
+        out["sharded"] = bw.sharded_record(steps=args.steps, warmup=args.warmup, repeats=REPEATS, **kw)
+    if world == 1 and "workloads" not in skip:
+        w = {}
+        for name, fn in (("c4a", bw.record_c4a), ("c4b", bw.record_c4b), ("c3", bw.record_c3)):
+            if name in skip:
+                continue
+            try:
+                w[name] = fn()
+            except Exception as e:  # noqa: BLE001 - one configuration must not take the line down
+                w[name] = {"error": f"{type(e).__name__}: {e}"}
+        out["workloads"] = w
+
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def low_reuse_runs(args, torch, bw, dg, GPUEmbeddingLayer, table0, dev, stream):
+    """pool_dense_kernel on the headline shape when few rows repeat: DRAM traffic then approaches the
+    algorithmic bytes, and the fraction of the HBM peak is a statement about HBM."""
+    res = {}
+    peak, kind = bw.hbm_peak()
+    cases = [("uniform_4M", table0, NUM_ROWS, None)]
+    big_rows = 40_000_000
+    try:
+        big = torch.empty((big_rows, WIDTH), dtype=torch.float16, device=dev)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(77)
+        chunk = 1 << 22
+        for r0 in range(0, big_rows, chunk):
+            r1 = min(big_rows, r0 + chunk)
+            big[r0:r1] = (torch.randn((r1 - r0, WIDTH), generator=gen, device=dev) * 0.02).half()
+        cases.append(("zipf1.1_40M", big, big_rows, ALPHA))
+        cases.append(("uniform_40M", big, big_rows, None))
+    except Exception as e:  # noqa: BLE001
+        res["zipf1.1_40M"] = {"error": str(e)}
+    for name, table, rows, alpha in cases:
+        batches = []
+        for b in range(NUM_BATCHES):
+            # perm None: the Zipf ranks go through the table-free affine permutation of the row ids
+            k, o = make_batch(0, b, 7, None, alpha=alpha, num_rows=rows)
+            batches.append((torch.from_numpy(k).to(dev), torch.from_numpy(o).to(dev)))
+        layer = GPUEmbeddingLayer(table, rows, ROW_BYTES, "float16", device_id=dev.index, layer_name=name)
+        ctx = layer.create_execution_context(stream.cuda_stream, stream.cuda_stream)
+        outb = torch.empty((NUM_BAGS, WIDTH), dtype=torch.float16, device=dev)
+
+        def step(i):
+            k, o = batches[i % NUM_BATCHES]
+            layer.lookup_pooled(ctx, k.numel(), k, outb, ROW_BYTES, "mean", "float16", csr_offsets=o,
+                                num_csr_offsets=o.numel())
+        ms, regions = bw.timed_repeats(stream, step, args.steps * NUM_TABLES, args.warmup, REPEATS)
+        sec = ms * 1e-3 / (args.steps * NUM_TABLES)
+        nk = float(np.mean([k.numel() for k, _ in batches]))
+        alg = algorithmic_bytes(int(nk))
+        # rows that are read once per launch come from DRAM: distinct keys * row bytes (+ keys, offsets, output)
+        distinct = float(np.mean([torch.unique(k).numel() for k, _ in batches]))
+        dram_est = distinct * ROW_BYTES + nk * 8 + (NUM_BAGS + 1) * 8 + NUM_BAGS * ROW_BYTES
+        entry = {"keys_per_s": nk / sec, "us_per_launch": sec * 1e6, "distinct_keys_per_launch": distinct,
+                 "algorithmic_gbs": alg / sec / 1e9, "frac": alg / sec / 1e9 / peak,
+                 "dram_bytes_estimate": int(dram_est), "frac_on_dram_estimate": dram_est / sec / 1e9 / peak,
+                 "peak_kind": kind, "region_ms": [round(r, 4) for r in regions]}
+        tf = ROOT / "profiles" / f"pool_dense_f16_{name}.traffic.json"
+        if tf.exists():
+            entry["traffic"] = json.loads(tf.read_text()).get("dram_bytes_per_launch")
+            if entry["traffic"]:
+                entry["frac_on_dram_bytes"] = entry["traffic"] / sec / 1e9 / peak
+        res[name] = entry
+        ctx.wait()
+        ctx.destroy()
+        layer.destroy()
+    return res
 
 
 def run_other_workload(args):
     import torch
     import torch.distributed as dist
-    from nv_embedding_cache_b200 import workloads
+    import bench_workloads as workloads
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
@@ -520,22 +496,31 @@ def run_other_workload(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--cpu-seconds", type=float, default=None,
+                    help="time budget of the CPU baseline (ours: 12 s in a child process; reference arm: "
+                         "0 = exactly --steps steps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the device-resident leg directly instead of replaying CUDA graphs")
     ap.add_argument("--workload", choices=["c2", "c3", "c4a", "c4b", "c5", "published"], default="c2",
                     help="c2 is the headline benchmark; the others print one JSON line for that "
-                         "configuration (see nv_embedding_cache_b200/workloads.py)")
+                         "configuration (see bench_workloads.py)")
     ap.add_argument("--rows", type=int, default=0,
                     help="table rows for --workload runs (0 = the configuration's own size)")
+    ap.add_argument("--shard-rows", type=int, default=0,
+                    help="rows per rank of the sharded record (0 = 250,000,000; profiling runs use fewer)")
+    ap.add_argument("--skip", default="",
+                    help="comma list of parts to leave out of the line: sharded, workloads, c4a, c4b, c3, "
+                         "low_reuse, copy_probe")
     ap.add_argument("--tables", type=int, default=NUM_TABLES,
                     help="tables per GPU (profiling runs use fewer; the benchmark config is 8)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    if args.cpu_seconds is None:
+        args.cpu_seconds = 12.0 if args.impl == "ours" else 0.0
     globals()["NUM_TABLES"] = max(1, min(8, args.tables))
     if args.impl == "reference":
         run_reference_arm(args)

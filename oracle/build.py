@@ -76,10 +76,30 @@ def build_oracle(verbose: bool = False) -> Path:
     return out
 
 
-def build_reference(verbose: bool = False) -> Path | None:
-    """Compile the reference CPU path from its own sources (only where the checkout exists)."""
+AVX512_FLAGS = ["-mavx512f", "-mavx512bw", "-mavx512vl", "-mavx512vbmi"]
+
+
+def host_has_avx512() -> bool:
+    """Whether this host has the AVX-512 subsets the reference's build asks for when it finds them
+    (cmake/nve_avx.cmake: F, BW, VL, VBMI)."""
+    try:
+        flags = set()
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                flags = set(line.split(":", 1)[1].split())
+                break
+        return {"avx512f", "avx512bw", "avx512vl", "avx512vbmi"} <= flags
+    except OSError:
+        return False
+
+
+def build_reference(verbose: bool = False, avx512: bool = False) -> Path | None:
+    """Compile the reference CPU path from its own sources (only where the checkout exists).
+    The -mavx2 build is the one the parity pins use (no fused multiply-add on any host); the
+    AVX-512 build (the flags the reference's cmake picks on a host that has them) exists for timing
+    the CPU baseline on such hosts."""
     OUT.mkdir(exist_ok=True)
-    out = OUT / "libnve_ref.so"
+    out = OUT / ("libnve_ref_avx512.so" if avx512 else "libnve_ref.so")
     if not (REFERENCE / "src" / "host_embedding_layer.cpp").exists():
         return out if out.exists() else None
     driver = HERE / "ref_driver.cpp"
@@ -92,7 +112,8 @@ def build_reference(verbose: bool = False) -> Path | None:
     shim.mkdir(parents=True, exist_ok=True)
     (shim / "json_fwd.hpp").write_text("#pragma once\n#include <nlohmann/json.hpp>\n")
     cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
-    cmd = ["g++", "-std=c++17", "-O3", "-mavx2", "-fPIC", "-shared", "-w", *REF_DEFINES,
+    cmd = ["g++", "-std=c++17", "-O3", *(AVX512_FLAGS if avx512 else ["-mavx2"]), "-fPIC", "-shared", "-w",
+           *REF_DEFINES,
            f"-I{REFERENCE}", f"-I{REFERENCE / 'include'}", f"-I{cuda_inc}", f"-I{nl}",
            f"-I{shim.parent}", str(driver),
            *[str(REFERENCE / "src" / f"{s}.cpp") for s in REF_SOURCES],
@@ -164,6 +185,7 @@ def build_reference_serialization(verbose: bool = False) -> Path | None:
 
 
 def build_all(verbose: bool = False):
+    build_reference(verbose, avx512=True)
     return (build_oracle(verbose), build_reference(verbose), build_reference_gpu(verbose),
             build_reference_serialization(verbose))
 

@@ -255,8 +255,19 @@ class OracleCache:
 class Reference:
     """The unmodified reference CPU path (HostEmbeddingLayer over a LinearHostTable)."""
 
-    def __init__(self):
-        path = _build.build_reference()
+    def __init__(self, for_timing: bool = False):
+        """for_timing: take the AVX-512 build when this host has the instructions (what the
+        reference's own build would pick here); parity checks always use the -mavx2 build."""
+        path = None
+        self.simd = "avx2"
+        if for_timing and _build.host_has_avx512():
+            path = _build.build_reference(avx512=True)
+            if path is not None and Path(path).exists():
+                self.simd = "avx512"
+            else:
+                path = None
+        if path is None:
+            path = _build.build_reference()
         if path is None or not Path(path).exists():
             raise FileNotFoundError("oracle/_ref/libnve_ref.so is not built and the reference "
                                     "checkout is absent")

@@ -54,7 +54,7 @@ def test_c4a_full_batch_dequant_sum_matches_oracle(torch_cuda, oracle):
     """32768 bags x 20 keys over int8 rows with fp32 scale (tight 260-byte rows and padded 272),
     table scaled to 5M rows to keep the test short; the batch has the full size."""
     torch = torch_cuda
-    from nv_embedding_cache_b200.workloads import _quant_table
+    from bench_workloads import _quant_table
     rows, width, bags, hot = 5_000_000, 256, 32_768, 20
     keys = dg.zipf_keys(bags * hot, rows, 1.05, 400)
     d_keys = to_dev(torch, keys)

@@ -160,6 +160,15 @@ def test_peer_form_with_and_without_hot_rows(torch_cuda, oracle, world, dtype, n
             torch.cuda.synchronize()
             want = expected(oracle, table, dtype, ckeys, "wsum", offsets=offs, default_row=5, weights=w)
             assert np.array_equal(out.cpu().numpy().view(np.uint8), want.view(np.uint8)), (rank, hot)
+            # fixed hotness below the lane-group size, mean and weighted mean (the pipelined kernel)
+            fkeys = keys[:2000 * 5]
+            fw = np.random.default_rng(9).uniform(0.1, 1, fkeys.size).astype(np.float32)
+            for pooling, ref_pool, weights in (("mean", "mean", None), ("weighted_mean", "wmean", fw)):
+                out = t.lookup_pooled(to_dev(torch, fkeys), pooling, fixed_hotness=5,
+                                      weights=None if weights is None else to_dev(torch, weights))
+                torch.cuda.synchronize()
+                want = expected(oracle, table, dtype, fkeys, ref_pool, hotness=5, default_row=5, weights=weights)
+                assert np.array_equal(out.cpu().numpy().view(np.uint8), want.view(np.uint8)), (rank, hot, pooling)
         t.close()
 
 
