@@ -419,7 +419,7 @@ def low_reuse_runs(args, torch, bw, dg, GPUEmbeddingLayer, table0, dev, stream):
     res = {}
     peak, kind = bw.hbm_peak()
     cases = [("uniform_4M", table0, NUM_ROWS, None)]
-    big_rows = 40_000_000
+    big_rows = args.low_reuse_rows if args.low_reuse_rows > 0 else 40_000_000
     try:
         big = torch.empty((big_rows, WIDTH), dtype=torch.float16, device=dev)
         gen = torch.Generator(device=dev)
@@ -428,8 +428,9 @@ def low_reuse_runs(args, torch, bw, dg, GPUEmbeddingLayer, table0, dev, stream):
         for r0 in range(0, big_rows, chunk):
             r1 = min(big_rows, r0 + chunk)
             big[r0:r1] = (torch.randn((r1 - r0, WIDTH), generator=gen, device=dev) * 0.02).half()
-        cases.append(("zipf1.1_40M", big, big_rows, ALPHA))
-        cases.append(("uniform_40M", big, big_rows, None))
+        tag = f"{big_rows // 1_000_000}M"
+        cases.append((f"zipf1.1_{tag}", big, big_rows, ALPHA))
+        cases.append((f"uniform_{tag}", big, big_rows, None))
     except Exception as e:  # noqa: BLE001
         res["zipf1.1_40M"] = {"error": str(e)}
     for name, table, rows, alpha in cases:
@@ -512,6 +513,8 @@ def main():
                     help="table rows for --workload runs (0 = the configuration's own size)")
     ap.add_argument("--shard-rows", type=int, default=0,
                     help="rows per rank of the sharded record (0 = 250,000,000; profiling runs use fewer)")
+    ap.add_argument("--low-reuse-rows", type=int, default=0,
+                    help="rows of the larger table of the low-reuse runs (0 = 40,000,000; profiler captures use fewer)")
     ap.add_argument("--skip", default="",
                     help="comma list of parts to leave out of the line: sharded, workloads, c4a, c4b, c3, "
                          "low_reuse, copy_probe")

@@ -2,11 +2,13 @@
 // choice of vector width from the alignments involved, kernel parameter packing and launch.
 #include "ops_internal.hpp"
 
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
 #include "../kernels/lookup_pool.cuh"
 #include "../kernels/pool_dense.cuh"
+#include "../kernels/shard_pool.cuh"
 #include "../kernels/lookup_rows.cuh"
 #include "../kernels/gather_bulk.cuh"
 #include "../kernels/gather_sorted.cuh"
@@ -197,6 +199,42 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
     if (dense_off || !pool_dense_eligible(p, vb)) {
       p.word_loads = false;
       p.nvec = static_cast<int32_t>(value_bytes / vb);
+    }
+  }
+  // A cache in front of a plain table of float rows: the lean coded kernel (cache line or table row
+  // behind one 32- or 64-bit code per key).  NVE_B200_NO_DENSE keeps everything on the general kernel.
+  if (!dense_off && p.cache.enabled && a.num_shards == 0 && a.table != nullptr && vb == 16 &&
+      (in == In::F16 || in == In::F32) && a.num_rows > 0) {
+    ShardPoolParams sp{};
+    sp.bases[0] = p.cache.cache_ptr;
+    sp.bases[1] = p.table;
+    sp.cache = p.cache;
+    sp.num_rows = a.num_rows;
+    sp.row_stride = a.row_stride;
+    sp.front_stride = static_cast<int64_t>(p.cache.row_size);
+    sp.default_row = a.default_row_index;
+    sp.num_shards = 1;
+    fast_div_params(1, &sp.shard_magic, &sp.shard_shift);
+    const uint64_t most = std::max<uint64_t>(static_cast<uint64_t>(a.num_rows), uint64_t{p.cache.num_sets} * 8u);
+    sp.row_bits = 1;
+    while (sp.row_bits < 62 && (most >> sp.row_bits) != 0) sp.row_bits++;
+    sp.keys = p.keys;
+    sp.offsets = p.offsets;
+    sp.weights = p.weights;
+    sp.out = p.out;
+    sp.out_stride = p.out_stride;
+    sp.num_bags = p.num_bags;
+    sp.hotness = p.hotness;
+    sp.nvec = p.nvec;
+    sp.key64 = p.key64;
+    sp.off64 = p.off64;
+    sp.w16 = p.w16;
+    sp.mean = p.mean;
+    sp.out_f16 = p.out_f16;
+    sp.out_vec_ok = p.out_vec_ok;
+    if (a.keys != nullptr && shard_pool_eligible(in, static_cast<int64_t>(value_bytes), a.row_stride, sp)) {
+      launch_shard_pool(sp, in, stream);
+      return;
     }
   }
   if (!dense_off && pool_dense_eligible(p, vb)) {

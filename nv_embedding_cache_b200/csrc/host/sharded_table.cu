@@ -296,6 +296,7 @@ ShardPoolParams base_params(const Table& t, bool use_hot) {
   p.hot.enabled = use_hot && t.hot_enabled && t.num_hot > 0;
   p.num_rows = t.global_rows;
   p.row_stride = c.row_stride;
+  p.front_stride = t.buf_stride;
   p.default_row = c.default_row_index;
   fast_div_params(static_cast<uint32_t>(c.world), &p.shard_magic, &p.shard_shift);
   p.num_shards = c.world;

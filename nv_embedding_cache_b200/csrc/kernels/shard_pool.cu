@@ -4,6 +4,7 @@
 
 #include <cub/cub.cuh>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "../host/ops_internal.hpp"
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(128) shard_gather_rows_kernel(const ShardPoolP
   const int gl = threadIdx.x & (GROUP - 1);
   const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP;
   if (i >= p.num_bags) return;
-  const uint64_t code = shard_row_code<uint64_t>(p, load_index(p.keys, p.key64, i));
+  const uint64_t code = shard_row_code<uint64_t, int64_t>(p, load_index(p.keys, p.key64, i));
   const uint8_t* src = shard_row_address<uint64_t>(p, code);
   uint8_t* d = dst + i * dst_stride;
   for (int v = gl; v < nvec; v += GROUP) {
@@ -114,13 +115,18 @@ __device__ __forceinline__ uint32_t mix_key(uint64_t k) {
 
 // One thread per position.  A position either takes the hot path (no exchange), finds its key in the
 // table, or claims a free slot for it; the claiming position numbers the key among the distinct keys
-// of its owner, one atomic per (warp, owner).
+// of its owner.  The numbering is block-wide: claimers count per owner in shared memory, one thread
+// per owner reserves the block's range with one global atomic (a counter per owner is one address:
+// an atomic per warp on it measured 65 us for 2^20 keys), and every claimer adds its rank in the block.
 __global__ void __launch_bounds__(256) exchange_insert_kernel(const ShardPoolParams p, const ExchangeState x,
                                                               int64_t n) {
+  __shared__ uint32_t block_count[kMaxShards];
+  __shared__ uint32_t block_base[kMaxShards];
+  if (threadIdx.x < kMaxShards) block_count[threadIdx.x] = 0;
+  __syncthreads();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int lane = threadIdx.x & 31;
   bool claimed = false;
-  uint32_t slot_in_table = 0, owner = 0;
+  uint32_t slot_in_table = 0, owner = 0, rank_in_block = 0;
   if (i < n) {
     int64_t key = load_index(p.keys, p.key64, i);
     if (static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) key = p.default_row >= 0 ? p.default_row : 0;
@@ -152,18 +158,15 @@ __global__ void __launch_bounds__(256) exchange_insert_kernel(const ShardPoolPar
       const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
       owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
       x.pos_code[i] = h | (claimed ? kCodeClaimed : 0u);
+      if (claimed) rank_in_block = atomicAdd(&block_count[owner], 1u);
     }
   }
-  // number the claimed keys per owner
-  const uint32_t claimers = __ballot_sync(0xffffffffu, claimed);
-  if (claimed) {
-    const uint32_t peers = __match_any_sync(claimers, owner);
-    const int leader = __ffs(peers) - 1;
-    uint32_t base = 0;
-    if (lane == leader) base = atomicAdd(x.counts + owner, static_cast<uint32_t>(__popc(peers)));
-    base = __shfl_sync(peers, base, leader);
-    x.table_slot[slot_in_table] = base + __popc(peers & ((1u << lane) - 1u));
+  __syncthreads();
+  if (threadIdx.x < p.num_shards && block_count[threadIdx.x] != 0) {
+    block_base[threadIdx.x] = atomicAdd(x.counts + threadIdx.x, block_count[threadIdx.x]);
   }
+  __syncthreads();
+  if (claimed) x.table_slot[slot_in_table] = block_base[owner] + rank_in_block;
 }
 
 __global__ void __launch_bounds__(256) exchange_emit_kernel(const ExchangeState x, int32_t num_shards, int64_t n,
@@ -195,6 +198,9 @@ __global__ void __launch_bounds__(256) exchange_emit_kernel(const ExchangeState 
   if (code & kCodeClaimed) send_keys[at] = key;
 }
 
+// A grid that just fills the GPU walks over the keys: the count may still be on the device (n_dev),
+// and launching a block per possible key only to have most of them leave at once cost more than the
+// copy itself.
 template <int GROUP>
 __global__ void __launch_bounds__(128) serve_rows_kernel(const int64_t* keys, int64_t n, uint64_t magic,
                                                          uint32_t shift, const uint8_t* shard,
@@ -202,13 +208,15 @@ __global__ void __launch_bounds__(128) serve_rows_kernel(const int64_t* keys, in
                                                          uint8_t* rows, int64_t rows_stride,
                                                          const uint32_t* n_dev) {
   const int gl = threadIdx.x & (GROUP - 1);
-  const int64_t j = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP;
-  if (j >= n || (n_dev != nullptr && j >= static_cast<int64_t>(*n_dev))) return;
-  uint64_t local = fast_div(static_cast<uint64_t>(keys[j]), magic, shift);
-  if (local >= static_cast<uint64_t>(local_rows)) local = 0;   // not a row of this shard: memory-safe answer
-  const uint4* src = reinterpret_cast<const uint4*>(shard + local * static_cast<uint64_t>(row_stride));
-  uint4* dst = reinterpret_cast<uint4*>(rows + j * rows_stride);
-  for (int v = gl; v < nvec; v += GROUP) dst[v] = __ldg(src + v);
+  if (n_dev != nullptr) n = min(n, static_cast<int64_t>(*n_dev));
+  const int64_t groups = static_cast<int64_t>(gridDim.x) * blockDim.x / GROUP;
+  for (int64_t j = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / GROUP; j < n; j += groups) {
+    uint64_t local = fast_div(static_cast<uint64_t>(keys[j]), magic, shift);
+    if (local >= static_cast<uint64_t>(local_rows)) local = 0;   // not a row of this shard: memory-safe answer
+    const uint4* src = reinterpret_cast<const uint4*>(shard + local * static_cast<uint64_t>(row_stride));
+    uint4* dst = reinterpret_cast<uint4*>(rows + j * rows_stride);
+    for (int v = gl; v < nvec; v += GROUP) dst[v] = __ldg(src + v);
+  }
 }
 
 template <int GROUP>
@@ -231,6 +239,7 @@ bool shard_pool_eligible(In in, int64_t value_bytes, int64_t row_stride, const S
   for (int s = 0; s <= p.num_shards; s++) {
     if (reinterpret_cast<uintptr_t>(p.bases[s]) % 16 != 0) return false;
   }
+  if ((p.hot.enabled || p.cache.enabled) && p.front_stride % 16 != 0) return false;
   return p.num_shards >= 1 && p.num_shards <= kMaxShards && p.row_bits >= 1 && p.row_bits <= 56;
 }
 
@@ -318,12 +327,15 @@ void launch_serve_rows(const int64_t* keys, int64_t n, int32_t num_shards, const
   uint32_t shift = 0;
   fast_div_params(static_cast<uint32_t>(num_shards), &magic, &shift);
   const int nvec = static_cast<int>(row_bytes / 16);
+  const unsigned resident = static_cast<unsigned>(sm_count()) * 16u;
   if (nvec <= 8) {
-    serve_rows_kernel<8><<<blocks_for(n * 8, 128), 128, 0, stream>>>(keys, n, magic, shift, shard, local_rows,
-                                                                     row_stride, nvec, rows, rows_stride, n_dev);
+    const unsigned grid = std::min(blocks_for(n * 8, 128), resident);
+    serve_rows_kernel<8><<<grid, 128, 0, stream>>>(keys, n, magic, shift, shard, local_rows, row_stride, nvec,
+                                                   rows, rows_stride, n_dev);
   } else {
-    serve_rows_kernel<32><<<blocks_for(n * 32, 128), 128, 0, stream>>>(keys, n, magic, shift, shard, local_rows,
-                                                                       row_stride, nvec, rows, rows_stride, n_dev);
+    const unsigned grid = std::min(blocks_for(n * 32, 128), resident);
+    serve_rows_kernel<32><<<grid, 128, 0, stream>>>(keys, n, magic, shift, shard, local_rows, row_stride, nvec,
+                                                    rows, rows_stride, n_dev);
   }
   NVE_B200_CUDA(cudaGetLastError());
 }

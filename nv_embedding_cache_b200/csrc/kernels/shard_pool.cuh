@@ -4,7 +4,8 @@
 // maps every rank's slice into one address range, src/distributed.cpp:155-256; here a kernel picks
 // the owner's base address from a small table).  Three groups of kernels:
 //
-//  * shard_pool_kernel — the fused gather + pool of a peer-mapped sharded table.  Lean form of
+//  * shard_pool_kernel — the fused gather + pool of a peer-mapped sharded table, and of a table with
+//    a set-associative cache in front (the cached layer's pooled lookup).  Lean form of
 //    lookup_pool_kernel (one sub-warp group per bag, U row loads in flight per lane, one shuffled
 //    32-bit code per row instead of a pointer), with a replicated HOT-ROW TABLE in front: rows that
 //    the key stream asks for most are copied into every GPU's own HBM, and a 32-byte bitmap block
@@ -56,11 +57,15 @@ __device__ __forceinline__ bool hot_probe(const HotIndex& h, uint64_t key, uint3
 }
 
 struct ShardPoolParams {
-  // bases[0]: the hot table; bases[1 + s]: shard s (this GPU's own shard or a peer mapping)
+  // bases[0]: rows held locally in front of the table -- the hot table, or the lines of a
+  // set-associative cache; bases[1 + s]: shard s (this GPU's own shard or a peer mapping; a plain
+  // table is one shard)
   const uint8_t* bases[kMaxShards + 1];
   HotIndex hot;
+  CacheProbe cache;        // set-associative cache in front (instead of hot rows); cache.misses counts
   int64_t num_rows;        // global rows
-  int64_t row_stride;
+  int64_t row_stride;      // of the shards
+  int64_t front_stride;    // of bases[0]
   int64_t default_row;     // >= 0: keys outside [0, num_rows) read this row; < 0: they read row 0
   uint64_t shard_magic;
   uint32_t shard_shift;
@@ -83,9 +88,17 @@ struct ShardPoolParams {
 };
 
 // key -> row code.  Keys that are no rows of the table read the default row, or row 0 when there
-// is none (a memory-safe answer; the caller's contract is that such keys do not occur).
-template <typename CodeT>
-__device__ __forceinline__ CodeT shard_row_code(const ShardPoolParams& p, int64_t key) {
+// is none (a memory-safe answer; the caller's contract is that such keys do not occur).  With a
+// cache in front the probe comes first, as in the general kernel: a resident key is served from its
+// cache line whatever its value; `missed` counts the keys the cache did not hold.
+template <typename CodeT, typename KeyT = int64_t>
+__device__ __forceinline__ CodeT shard_row_code(const ShardPoolParams& p, int64_t key, int* missed = nullptr) {
+  if (p.cache.enabled) {
+    uint32_t set;
+    const int way = probe_set<KeyT>(p.cache, static_cast<KeyT>(key), &set);
+    if (way >= 0) return static_cast<CodeT>(static_cast<uint64_t>(set) * 8u + static_cast<uint32_t>(way));
+    if (missed != nullptr) *missed += 1;
+  }
   if (static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
     key = p.default_row >= 0 ? p.default_row : 0;
   }
@@ -100,7 +113,7 @@ template <typename CodeT>
 __device__ __forceinline__ const uint8_t* shard_row_address(const ShardPoolParams& p, CodeT code) {
   const uint32_t base = static_cast<uint32_t>(code >> p.row_bits);
   const uint64_t row = static_cast<uint64_t>(code) & ((uint64_t{1} << p.row_bits) - 1u);
-  return p.bases[base] + row * static_cast<uint64_t>(p.row_stride);
+  return p.bases[base] + row * static_cast<uint64_t>(base == 0 ? p.front_stride : p.row_stride);
 }
 
 // Same accumulation order and arithmetic as pool_dense_kernel / lookup_pool_kernel: every output
@@ -132,6 +145,7 @@ __global__ void __launch_bounds__(128) shard_pool_kernel(const ShardPoolParams p
 #pragma unroll
   for (int e = 0; e < EPV; e++) acc[e] = 0.f;
   float wsum = 0.f;
+  int missed = 0;
 
 #pragma unroll 1
   for (int c = 0; c < len; c += GROUP) {
@@ -140,7 +154,9 @@ __global__ void __launch_bounds__(128) shard_pool_kernel(const ShardPoolParams p
     float my_w = 1.f;
     if (gl < n) {
       const int64_t k = start + c + gl;
-      my_code = shard_row_code<CodeT>(p, load_index(p.keys, p.key64, k));
+      const int64_t key = load_index(p.keys, p.key64, k);
+      my_code = p.key64 ? shard_row_code<CodeT, int64_t>(p, key, &missed)
+                        : shard_row_code<CodeT, int32_t>(p, key, &missed);
       if (WEIGHTED) my_w = load_weight(p.weights, p.w16, k);
     }
 #pragma unroll 1
@@ -169,6 +185,14 @@ __global__ void __launch_bounds__(128) shard_pool_kernel(const ShardPoolParams p
         r.w = valid ? r.w : 0u;
         accumulate_vec16<IN, WEIGHTED>(acc, r, w, 1.f, 0.f);
       }
+    }
+  }
+
+  // miss accounting of a cache in front: one atomic per lane group
+  if (p.cache.enabled && p.cache.misses != nullptr) {
+    const int total = __reduce_add_sync(gmask, missed);
+    if (gl == 0 && total > 0) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.cache.misses), static_cast<unsigned long long>(total));
     }
   }
 

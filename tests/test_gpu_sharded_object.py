@@ -207,6 +207,34 @@ def test_hot_rows_choice_and_refresh(torch_cuda, oracle):
     t.close()
 
 
+@pytest.mark.parametrize("mode", ["peer", "alltoall"])
+def test_padded_shard_rows_with_hot_rows(torch_cuda, oracle, mode):
+    """Shard rows stored with padding (128-byte rows at a 144-byte stride): the hot table and the
+    exchange buffers keep their own, packed stride."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.sharded import ShardedEmbeddingTable
+    world, rows_per_rank, dim = (3, 4000, 64) if mode == "peer" else (1, 12000, 64)
+    total = world * rows_per_rank
+    table = dg.normal_table(total, dim, 0.02, 5, np.float16)
+    shards = []
+    for r in range(world):
+        wide = torch.zeros((rows_per_rank, dim + 8), dtype=torch.float16, device="cuda")
+        wide[:, :dim] = to_dev(torch, table[r::world].copy())
+        shards.append(wide[:, :dim])                      # stride 72 elements = 144 bytes
+    assert shards[0].stride(0) == dim + 8
+    t = ShardedEmbeddingTable(shards[0], max_keys=1 << 14, mode=mode, world=world, rank=0,
+                              peer_shards=[s.data_ptr() for s in shards] if mode == "peer" else None,
+                              hot_rows=1500)
+    perm = dg.permutation(total)
+    assert t.set_hot_keys(to_dev(torch, dg.zipf_keys(20000, total, 1.05, 3, perm))) == 1500
+    keys = dg.zipf_keys(1500 * 8, total, 1.05, 4, perm)
+    out = t.lookup_pooled(to_dev(torch, keys), "sum", fixed_hotness=8)
+    torch.cuda.synchronize()
+    want = expected(oracle, table, "f16", keys, "sum", hotness=8)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    t.close()
+
+
 @pytest.mark.parametrize("hot_rows", [0, 2000])
 @pytest.mark.parametrize("dtype,npdt", [("f16", np.float16), ("f32", np.float32)])
 def test_exchange_form_world_one(torch_cuda, oracle, dtype, npdt, hot_rows):
