@@ -125,17 +125,30 @@ __global__ void __launch_bounds__(256) exchange_insert_kernel(const ShardPoolPar
   if (threadIdx.x < kMaxShards) block_count[threadIdx.x] = 0;
   __syncthreads();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  bool claimed = false;
+  const int lane = threadIdx.x & 31;
+  bool claimed = false, exchanged = false;
   uint32_t slot_in_table = 0, owner = 0, rank_in_block = 0;
+  int64_t key = 0;
   if (i < n) {
-    int64_t key = load_index(p.keys, p.key64, i);
+    key = load_index(p.keys, p.key64, i);
     if (static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) key = p.default_row >= 0 ? p.default_row : 0;
     uint32_t hot_slot;
     if (p.hot.enabled && hot_probe(p.hot, static_cast<uint64_t>(key), &hot_slot)) {
       x.pos_code[i] = kCodeHot | hot_slot;
     } else {
+      exchanged = true;
+    }
+  }
+  // Lanes of a warp that hold the same key send one of them to the table: a frequent key would
+  // otherwise be one address that thousands of compare-and-swaps queue up on.
+  const uint32_t takers = __ballot_sync(0xffffffffu, exchanged);
+  if (exchanged) {
+    const uint32_t same = __match_any_sync(takers, static_cast<unsigned long long>(key));
+    const int leader = __ffs(same) - 1;
+    uint32_t h = 0;
+    if (lane == leader) {
       const uint32_t mask = x.capacity - 1u;
-      uint32_t h = mix_key(static_cast<uint64_t>(key)) & mask;
+      h = mix_key(static_cast<uint64_t>(key)) & mask;
       bool placed = false;
       // the table holds at most half its capacity: a probe sequence is a handful of steps; the
       // bound only keeps a corrupted table from spinning a thread for ever
@@ -154,11 +167,14 @@ __global__ void __launch_bounds__(256) exchange_insert_kernel(const ShardPoolPar
         h = (h + 1u) & mask;
       }
       if (!placed) atomicAdd(x.probe_overrun, 1u);
-      slot_in_table = h;
+    }
+    h = __shfl_sync(same, h, leader);
+    slot_in_table = h;
+    x.pos_code[i] = h | (claimed ? kCodeClaimed : 0u);
+    if (claimed) {
       const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
       owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
-      x.pos_code[i] = h | (claimed ? kCodeClaimed : 0u);
-      if (claimed) rank_in_block = atomicAdd(&block_count[owner], 1u);
+      rank_in_block = atomicAdd(&block_count[owner], 1u);
     }
   }
   __syncthreads();

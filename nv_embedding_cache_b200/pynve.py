@@ -37,6 +37,7 @@ class EmbedLayerConfig:
         self.kernel_mode_value_2 = 0
         self.max_modify_size = 1 << 20
         self.default_row_index = -1
+        self.default_embedding = []     # host and hierarchical layers only (not provided here)
         # cached layer only: "default" = the reference's default insert heuristic (automatic cache
         # population, threshold 0.75), "never", or a float threshold
         self.insert_heuristic = "default"
@@ -266,6 +267,88 @@ class ManagedMemBlock(MemBlock):
         self._block.close()
 
 
+class MemBlockType:
+    """Type names that MemBlock.get_type() answers with (reference binding: a string-valued enum)."""
+    User, Managed, Linear, Host, NVL, MPI = "User", "Managed", "Linear", "Host", "NVL", "MPI"
+
+
+class Table:
+    """Host tables and parameter servers are outside this library; the name exists so that callers
+    written against the reference binding can still test ``isinstance(storage, Table)``."""
+
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("host tables and parameter servers are not part of this library")
+
+
+class PSType_t(enum.IntEnum):
+    """Kinds of parameter-server tables of the reference binding (names only: none is provided)."""
+    NVHashMap = 0
+    Abseil = 1
+    ParallelHash = 2
+    Redis = 3
+
+
+NVHashMap, Abseil, ParallelHash, Redis = PSType_t.NVHashMap, PSType_t.Abseil, PSType_t.ParallelHash, PSType_t.Redis
+
+
+class ParameterServerTable(Table):
+    """Parameter servers are outside this library (see Table)."""
+
+
+class HierarchicalEmbedding:
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("the hierarchical layer (host and remote tiers) is not part of this library")
+
+
+class HostEmbedding:
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("the host layer is not part of this library")
+
+
+def get_dl_tensor(layer: "NVEmbedBinding", data_type):
+    """DLPack capsule over the table memory of a layer, [num_embeddings, row_size] of `data_type` on
+    the layer's device (reference get_dl_tensor: how the torch layer sees a UVM table)."""
+    import torch
+    from torch.utils import dlpack
+    dt = {DataType_t.Float32: torch.float32, DataType_t.Float16: torch.float16}[DataType_t(data_type)]
+    t = device_tensor(_address(layer._memblock), (layer._num_rows, layer._row_elems), dt,
+                      torch.device("cuda", layer._device))
+    return dlpack.to_dlpack(t)
+
+
+_TORCH_REGISTRY: dict[int, "NVEmbedBinding"] = {}
+
+
+def register_for_torch(marker_ptr: int, layer: "NVEmbedBinding") -> None:
+    """Registry of layers by marker address, as the reference keeps for its torch custom ops.  No
+    custom ops are built here (callers see HAS_TORCH_OPS false and take the plain-Python path); the
+    registry only keeps the calls valid."""
+    _TORCH_REGISTRY[int(marker_ptr)] = layer
+
+
+def unregister_from_torch(marker_ptr: int) -> None:
+    _TORCH_REGISTRY.pop(int(marker_ptr), None)
+
+
+def load_tensor_from_stream(layer: "NVEmbedBinding", stream, name: int) -> None:
+    """Fills the table of `layer` with tensor `name` of a .nve container opened for binary reading
+    (reference load_tensor_from_stream as the binding exposes it); rows cached from the old table
+    are dropped."""
+    import numpy as np
+    import torch
+    from . import weight_files
+    host = np.empty((layer._num_rows, layer._row_elems),
+                    dtype=np.float32 if layer._dtype == DataType_t.Float32 else np.float16)
+    if not weight_files.read_tensor(stream, name, host):
+        raise KeyError(f"the file holds no tensor named {name}")
+    dt = torch.float32 if layer._dtype == DataType_t.Float32 else torch.float16
+    device = torch.device("cuda", layer._device)
+    device_tensor(_address(layer._memblock), host.shape, dt, device).copy_(torch.from_numpy(host))
+    torch.cuda.synchronize(device)
+    if isinstance(layer, LinearUVMEmbedding):
+        layer.clear(torch.cuda.current_stream(device).cuda_stream)
+
+
 def _address(memblock) -> int:
     return memblock if isinstance(memblock, int) else memblock.data_ptr()
 
@@ -279,6 +362,7 @@ class GPUEmbedding(NVEmbedBinding):
         config = config or EmbedLayerConfig()
         elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
         self._memblock = memblock
+        self._num_rows = num_embeddings
         layer = GPUEmbeddingLayer(_address(memblock), num_embeddings, row_size * elem, int(data_type),
                                   device_id=device_id, default_row_index=config.default_row_index)
         super().__init__(layer, row_size, data_type, device_id)
@@ -294,6 +378,7 @@ class LinearUVMEmbedding(NVEmbedBinding):
         config = config or EmbedLayerConfig()
         elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
         self._memblock = memblock
+        self._num_rows = num_embeddings
         self._table = GpuTable(gpu_cache_size, row_size * elem, int(data_type), device_id=device_id,
                                uvm_table=_address(memblock), uvm_num_rows=num_embeddings,
                                max_modify_size=config.max_modify_size,

@@ -21,20 +21,23 @@ import torch
 from . import pynve as nve
 
 
+# value types a layer can hold, both ways (the binding's enum <-> torch)
+_TORCH_OF_NVE = {nve.DataType_t.Float32: torch.float32, nve.DataType_t.Float16: torch.float16}
+_NVE_OF_TORCH = {t: n for n, t in _TORCH_OF_NVE.items()}
+
+
 def nve_type_to_torch_type(nve_type):
-    if nve_type == nve.DataType_t.Float32:
-        return torch.float32
-    if nve_type == nve.DataType_t.Float16:
-        return torch.float16
-    raise ValueError(f"Invalid data type: {nve_type}")
+    try:
+        return _TORCH_OF_NVE[nve.DataType_t(nve_type)]
+    except (KeyError, ValueError):
+        raise ValueError(f"no torch dtype for layer value type {nve_type!r}") from None
 
 
 def torch_type_to_nve_type(torch_type: torch.dtype):
-    if torch_type == torch.float32:
-        return nve.DataType_t.Float32
-    if torch_type == torch.float16:
-        return nve.DataType_t.Float16
-    raise ValueError(f"Invalid data type: {torch_type}")
+    try:
+        return _NVE_OF_TORCH[torch_type]
+    except KeyError:
+        raise ValueError(f"layers hold float32 or float16 rows, not {torch_type}") from None
 
 
 def pooling_type_from_mode(mode: str, weighted: bool):
@@ -48,30 +51,30 @@ def pooling_type_from_mode(mode: str, weighted: bool):
                      "('concat' is handled separately). 'max' pooling is not implemented.")
 
 
+def _flat_tensor(name: str, t: torch.Tensor, dtypes) -> None:
+    """The binding reads `t` through its address: it has to be of a type the kernels know and
+    dense in memory."""
+    if t.dtype not in dtypes:
+        wanted = " or ".join(str(d).replace("torch.", "") for d in dtypes)
+        raise TypeError(f"{name}: expected a {wanted} tensor, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: expected a contiguous tensor (a strided view would be misread)")
+
+
 def _check_forward_inputs(keys, offsets=None, per_sample_weights=None):
-    """The binding takes raw addresses, so wrong dtypes or strided views would be misread
-    (reference nve_layers.py:42-71)."""
-    if keys.dtype != torch.int64:
-        raise TypeError(f"keys must be an int64 tensor, got {keys.dtype}")
-    if not keys.is_contiguous():
-        raise ValueError("keys must be contiguous")
+    """Argument checks of a forward call, before any address is handed to the library (the same
+    conditions the reference checks, nve_layers.py:42-71)."""
+    _flat_tensor("keys", keys, (torch.int64,))
     if offsets is not None:
-        if offsets.dtype != torch.int64:
-            raise TypeError(f"offsets must be an int64 tensor, got {offsets.dtype}")
-        if not offsets.is_contiguous():
-            raise ValueError("offsets must be contiguous")
+        _flat_tensor("offsets", offsets, (torch.int64,))
         if offsets.numel() < 2:
-            raise ValueError("offsets must have at least two entries (num_bags + 1, "
-                             "include_last_offset=True convention)")
+            raise ValueError("offsets: at least two entries are needed, bag starts followed by the total "
+                             "number of keys (the include_last_offset=True layout)")
     if per_sample_weights is not None:
-        if per_sample_weights.dtype not in (torch.float32, torch.float16):
-            raise TypeError(f"per_sample_weights must be a float32 or float16 tensor, "
-                            f"got {per_sample_weights.dtype}")
-        if not per_sample_weights.is_contiguous():
-            raise ValueError("per_sample_weights must be contiguous")
+        _flat_tensor("per_sample_weights", per_sample_weights, (torch.float32, torch.float16))
         if per_sample_weights.numel() != keys.numel():
-            raise ValueError(f"per_sample_weights must have one element per key: "
-                             f"got {per_sample_weights.numel()} weights for {keys.numel()} keys")
+            raise ValueError(f"per_sample_weights: {per_sample_weights.numel()} weights for "
+                             f"{keys.numel()} keys (one weight per key is needed)")
 
 
 def _stream_handle(device: torch.device) -> int:
@@ -215,21 +218,18 @@ class NVEmbeddingBase(torch.nn.Module):
                  weight_init: Optional[torch.Tensor] = None, optimize_for_training: bool = True,
                  device: Optional[torch.device] = None, id: Optional[int] = None, config: Optional[dict] = None):
         super().__init__()
-        self.config = config_to_nve_config(config)
-        self.layer_type = layer_type
-        self.num_embeddings = num_embeddings
-        self.embedding_size = embedding_size
-        self.data_type = data_type
-        self.layer_data_type = torch_type_to_nve_type(data_type)
-        self.gpu_cache_size = gpu_cache_size
-        self.host_cache_size = host_cache_size
+        dev = torch.device(device) if device is not None else torch.device("cuda")
+        if dev.type != "cuda":
+            raise ValueError(f"NV Embedding layers of this library run on cuda devices, got {dev.type}")
+        index = dev.index if dev.index is not None else torch.cuda.current_device()
+        # what the caller asked for, under the attribute names users of the reference module read
+        self.layer_type, self.config = layer_type, config_to_nve_config(config)
+        self.num_embeddings, self.embedding_size = num_embeddings, embedding_size
+        self.data_type, self.layer_data_type = data_type, torch_type_to_nve_type(data_type)
+        self.gpu_cache_size, self.host_cache_size = gpu_cache_size, host_cache_size
         self.optimize_for_training = optimize_for_training
-        self.device = torch.device(device) if device is not None else torch.device("cuda")
-        if self.device.type != "cuda":
-            raise ValueError(f"NV Embedding layers of this library run on cuda devices, got {self.device.type}")
-        self.device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
-        self.device = torch.device("cuda", self.device_index)
-        self.id = id if id is not None else builtins.id(self)
+        self.device_index, self.device = index, torch.device("cuda", index)
+        self.id = builtins.id(self) if id is None else id
         if storage is not None and not isinstance(storage, nve.MemBlock):
             raise ValueError(f"{layer_type.name} requires storage to be a MemBlock or None")
 
