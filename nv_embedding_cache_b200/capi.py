@@ -8,7 +8,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "libnve_b200.so"
+import os
+
+# NVE_B200_LIBRARY: another build of the library to load, e.g. the checked one
+# (libnve_b200_checked.so, `python -m nv_embedding_cache_b200.build --bounds-check`)
+_LIB_PATH = Path(os.environ.get("NVE_B200_LIBRARY") or Path(__file__).resolve().parent / "libnve_b200.so")
 
 # ---- enums (include/nve_c_api.h) -------------------------------------------------------------
 NVE_SUCCESS, NVE_ERROR_INVALID_ARGUMENT, NVE_ERROR_CUDA, NVE_ERROR_RUNTIME = 0, 1, 2, 3

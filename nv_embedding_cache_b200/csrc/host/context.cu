@@ -1,5 +1,8 @@
 #include "context.hpp"
 
+#include <cstdlib>
+
+#include "../kernels/device_common.cuh"
 #include "../kernels/gather_bulk_api.hpp"
 
 namespace nve_b200 {
@@ -75,6 +78,79 @@ void ExecutionContext::wait() {
   if (gather_bulk_take_error()) {
     throw RuntimeFailure("a bulk-copy wait in the gather kernel ran out; output rows are incomplete");
   }
+  if (int* status = bounds_status_word()) {
+    const int what = *static_cast<volatile int*>(status);
+    if (what != 0) {
+      *static_cast<volatile int*>(status) = 0;
+      throw RuntimeFailure(cat("checked build: a lookup kernel left out accesses outside its inputs (",
+                               (what & kBoundsBadKey) ? "keys that are no rows of a table without a default row; " : "",
+                               (what & kBoundsBadOffsets) ? "CSR offsets outside the keys or out of order; " : "",
+                               "the affected bags or rows hold substitute values)"));
+    }
+  }
+}
+
+int* bounds_status_word() {
+  if constexpr (!kBoundsCheck) return nullptr;
+  static int* word = [] {
+    int* p = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) !=
+        cudaSuccess) {
+      (void)cudaGetLastError();
+      return static_cast<int*>(nullptr);
+    }
+    *p = 0;
+    return p;
+  }();
+  return word;
+}
+
+template <typename T>
+static void validate_csr_typed(const T* off, int64_t count, int64_t num_keys) {
+  NVE_B200_ARG(off[0] == 0, "CSR offsets must start at 0, got ", static_cast<int64_t>(off[0]));
+  T prev = 0;
+  T bad = 0;
+  for (int64_t i = 1; i < count; i++) {
+    bad |= static_cast<T>(off[i] < prev);
+    prev = off[i];
+  }
+  NVE_B200_ARG(bad == 0, "CSR offsets must not decrease");
+  NVE_B200_ARG(static_cast<int64_t>(prev) == num_keys, "the last CSR offset (", static_cast<int64_t>(prev),
+               ") must equal the number of keys (", num_keys, ")");
+}
+
+void validate_csr_offsets_host(const void* offsets, int elem_bytes, int64_t count, int64_t num_keys) {
+  NVE_B200_ARG(offsets != nullptr && count >= 2, "CSR offsets need at least two entries");
+  if (elem_bytes == 8) validate_csr_typed(static_cast<const int64_t*>(offsets), count, num_keys);
+  else validate_csr_typed(static_cast<const int32_t*>(offsets), count, num_keys);
+}
+
+bool host_key_checks_enabled() {
+  static const bool value = [] {
+    if (kBoundsCheck) return true;
+    const char* e = std::getenv("NVE_B200_CHECK_KEYS");
+    return e != nullptr && std::atoi(e) != 0;
+  }();
+  return value;
+}
+
+template <typename T>
+static void validate_keys_typed(const T* keys, int64_t n, int64_t num_rows) {
+  int64_t bad = -1;
+  for (int64_t i = 0; i < n; i++) {
+    if (static_cast<uint64_t>(static_cast<int64_t>(keys[i])) >= static_cast<uint64_t>(num_rows)) {
+      bad = i;
+      break;
+    }
+  }
+  NVE_B200_ARG(bad < 0, "key ", bad < 0 ? 0 : static_cast<int64_t>(keys[bad]), " at position ", bad,
+               " is no row of the table (", num_rows, " rows) and the layer has no default row");
+}
+
+void validate_keys_host(const void* keys, int elem_bytes, int64_t n, int64_t num_rows) {
+  if (n <= 0 || keys == nullptr) return;
+  if (elem_bytes == 8) validate_keys_typed(static_cast<const int64_t*>(keys), n, num_rows);
+  else validate_keys_typed(static_cast<const int32_t*>(keys), n, num_rows);
 }
 
 void ContextRegistry::add(ExecutionContext* ctx) {

@@ -92,6 +92,20 @@ struct Staged {
 Staged stage_in(ExecutionContext& ctx, const std::string& name, const void* user, size_t bytes,
                 bool copy_in, cudaStream_t stream);
 
+// Status word of the checked build (see kBoundsCheck): host memory the kernels of every device can
+// write; nullptr in the regular build.  ExecutionContext::wait() reports and clears it.
+int* bounds_status_word();
+
+// Host-side argument checks for buffers the caller keeps in host memory (they cost nothing on the
+// device and reject before any launch).  CSR offsets: at least two entries, first 0, never
+// decreasing, last == num_keys -- what the reference's CPU path enforces (src/layer_utils.cpp:468-477).
+// Throws InvalidArgument.
+void validate_csr_offsets_host(const void* offsets, int elem_bytes, int64_t count, int64_t num_keys);
+// Keys of a table without a default row must be rows of it.  A pass over every key on the calling
+// thread: done in the checked build and when NVE_B200_CHECK_KEYS=1, not otherwise.
+bool host_key_checks_enabled();
+void validate_keys_host(const void* keys, int elem_bytes, int64_t n, int64_t num_rows);
+
 // RAII device selection.
 class ScopedDevice {
  public:

@@ -177,6 +177,11 @@ void GPUEmbeddingLayer::lookup(context_ptr_t& ctx, int64_t num_keys, const void*
       d_off = stage_in(c, "offsets", pool_params->csr_offsets,
                        static_cast<size_t>(pool_params->num_csr_offsets) * kb, true, stream);
       a.csr_offsets = d_off.device;
+      // offsets the caller keeps in host memory are checked here, before anything is launched
+      if (d_off.staged) validate_csr_offsets_host(pool_params->csr_offsets, kb, pool_params->num_csr_offsets, num_keys);
+    }
+    if (d_keys.staged && config_.default_row_index < 0 && host_key_checks_enabled()) {
+      validate_keys_host(keys, kb, num_keys, config_.num_embeddings);
     }
     if (pool_params->weights != nullptr) {
       d_w = stage_in(c, "weights", pool_params->weights,

@@ -562,8 +562,15 @@ class LinearUVMEmbeddingLayer : public EmbeddingLayer {
         a.fixed_hotness = pool_params->fixed_hotness;
         a.num_bags = out_rows;
         if (pool_params->sparse_type == NVE_SPARSE_CSR) {
-          a.csr_offsets = stage_in(c, "offsets", pool_params->csr_offsets,
-                                   size_t(pool_params->num_csr_offsets) * kb, true, s).device;
+          const Staged d_off = stage_in(c, "offsets", pool_params->csr_offsets,
+                                        size_t(pool_params->num_csr_offsets) * kb, true, s);
+          a.csr_offsets = d_off.device;
+          if (d_off.staged) {
+            validate_csr_offsets_host(pool_params->csr_offsets, kb, pool_params->num_csr_offsets, num_keys);
+          }
+        }
+        if (d_keys.staged && default_row_ < 0 && host_key_checks_enabled()) {
+          validate_keys_host(keys, kb, num_keys, tc.uvm_num_rows);
         }
         if (pool_params->weights) {
           a.weights = stage_in(c, "weights", pool_params->weights,

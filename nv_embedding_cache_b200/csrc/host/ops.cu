@@ -158,6 +158,8 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
   p.w16 = a.weight_dtype == NVE_DTYPE_FLOAT16;
   p.mean = a.pooling_type == NVE_POOL_MEAN || a.pooling_type == NVE_POOL_WEIGHTED_MEAN;
   p.out_f16 = a.output_dtype == NVE_DTYPE_FLOAT16;
+  p.num_keys = a.num_keys;
+  p.status = bounds_status_word();
 
   uint64_t cache_base = 0, cache_row = 16;
   if (p.cache.enabled) {
@@ -232,6 +234,8 @@ void lookup_pool(const nve_b200_pool_args_t& a, int64_t sentinel_tag, cudaStream
     sp.mean = p.mean;
     sp.out_f16 = p.out_f16;
     sp.out_vec_ok = p.out_vec_ok;
+    sp.num_keys = a.num_keys;
+    sp.status = p.status;
     if (a.keys != nullptr && shard_pool_eligible(in, static_cast<int64_t>(value_bytes), a.row_stride, sp)) {
       launch_shard_pool(sp, in, stream);
       return;

@@ -349,6 +349,8 @@ void lookup_peer(Table& t, const nve_b200_sharded_lookup_t& l, cudaStream_t stre
   const int epv = t.in == In::F16 ? 8 : 4;
   const int store_bytes = std::min(16, epv * (p.out_f16 ? 2 : 4));
   p.out_vec_ok = reinterpret_cast<uintptr_t>(l.output) % store_bytes == 0 && l.output_stride % store_bytes == 0;
+  p.num_keys = l.num_keys;
+  p.status = bounds_status_word();
   if (shard_pool_eligible(t.in, t.row_bytes, t.cfg.row_stride, p)) {
     launch_shard_pool(p, t.in, stream);
     return;

@@ -10,6 +10,42 @@
 
 namespace nve_b200 {
 
+// Checked build (-DNVE_B200_BOUNDS_CHECK, `python -m nv_embedding_cache_b200.build --bounds-check`):
+// the pooled kernels, which otherwise trust CSR offsets and (without a default row) keys as the
+// reference's GPU path does, test them, leave out what would be an access outside the keys or the
+// table (such a bag pools to zeros, such a key reads row 0) and record it in a status word that
+// nve_context_wait reports.  It stands in for a memory checker on machines where none can run.
+#ifdef NVE_B200_BOUNDS_CHECK
+constexpr bool kBoundsCheck = true;
+#else
+constexpr bool kBoundsCheck = false;
+#endif
+constexpr int kBoundsBadKey = 1;
+constexpr int kBoundsBadOffsets = 2;
+__device__ __forceinline__ void bounds_report(int* status, int what) {
+  if (status != nullptr) atomicOr(status, what);
+}
+// Bag limits as the kernels use them; in the checked build limits outside [0, num_keys] or in the
+// wrong order give an empty bag.
+__device__ __forceinline__ void checked_bag(int64_t& start, int64_t& end, int64_t num_keys, int* status) {
+  if constexpr (kBoundsCheck) {
+    if (start < 0 || end < start || end > num_keys) {
+      bounds_report(status, kBoundsBadOffsets);
+      start = end = 0;
+    }
+  }
+}
+// A key about to be used as a row index of a table that has no default row.
+__device__ __forceinline__ int64_t checked_key(int64_t key, int64_t num_rows, int64_t default_row, int* status) {
+  if constexpr (kBoundsCheck) {
+    if (default_row < 0 && static_cast<uint64_t>(key) >= static_cast<uint64_t>(num_rows)) {
+      bounds_report(status, kBoundsBadKey);
+      return 0;
+    }
+  }
+  return key;
+}
+
 // Storage class of the values of a row.  Quantised rows carry [values][scale][offset?] with the
 // metadata directly after the values; its precision (fp32 / fp16) is a runtime field.
 enum class In : int { F32 = 0, F16 = 1, I8 = 2, U8 = 3 };

@@ -48,6 +48,8 @@ struct PoolKernelParams {
   uint64_t shard_magic;
   uint32_t shard_shift;
   int32_t num_shards;
+  int64_t num_keys;       // checked build: bag limits are tested against it
+  int* status;            // checked build: where kernels record what they left out (else unused)
 };
 
 template <int GROUP>
@@ -70,6 +72,7 @@ __device__ __forceinline__ const uint8_t* resolve_row(const PoolKernelParams& p,
   if (p.default_row >= 0 && static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
     key = p.default_row;
   }
+  if (p.table != nullptr || p.num_shards > 0) key = checked_key(key, p.num_rows, p.default_row, p.status);
   if (p.num_shards > 0) {
     const uint64_t local = fast_div(static_cast<uint64_t>(key), p.shard_magic, p.shard_shift);
     const uint32_t owner = static_cast<uint32_t>(static_cast<uint64_t>(key) - local * p.num_shards);
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(128) lookup_pool_kernel(const PoolKernelParams
     start = bag * p.hotness;
     end = start + p.hotness;
   }
+  if (p.keys != nullptr) checked_bag(start, end, p.num_keys, p.status);
   const bool weighted = p.weights != nullptr;
   uint8_t* out_row = p.out + bag * p.out_stride;
   constexpr int OUT_BYTES_F16 = EPV * 2;

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
     start = bag * p.hotness;
     end = start + p.hotness;
   }
+  if (p.keys != nullptr) checked_bag(start, end, p.num_keys, p.status);
   const int len = static_cast<int>(end - start);
   const bool lane_on = gl < p.nvec;
   // The inner loops run without branches.  A row slot past the end of a chunk is added as zeros
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams 
           static_cast<uint64_t>(key) >= static_cast<uint64_t>(p.num_rows)) {
         key = p.default_row;
       }
+      key = checked_key(key, p.num_rows, p.default_row, p.status);
       my_key = static_cast<uint32_t>(key);
       if (WEIGHTED) my_w = load_weight(p.weights, p.w16, k);
       if constexpr (QUANT) {

@@ -85,6 +85,8 @@ struct ShardPoolParams {
   bool mean;
   bool out_f16;
   bool out_vec_ok;
+  int64_t num_keys;        // checked build: bag limits are tested against it
+  int* status;             // checked build: where the kernel records what it left out
 };
 
 // key -> row code.  Keys that are no rows of the table read the default row, or row 0 when there
@@ -136,6 +138,7 @@ __global__ void __launch_bounds__(128) shard_pool_kernel(const ShardPoolParams p
     start = bag * p.hotness;
     end = start + p.hotness;
   }
+  checked_bag(start, end, p.num_keys, p.status);
   const int len = static_cast<int>(end - start);
   const bool lane_on = gl < p.nvec;
   // a lane past the end of the row works on the row's last vector into accumulators it never stores

@@ -139,3 +139,99 @@ def test_gradient_reduction_status_word(torch_cuda):
     capi.check(capi.lib.nve_b200_dedup_grads_status(C.byref(flag)))
     assert flag.value == 0
     capi.check(capi.lib.nve_b200_deduper_destroy(d))
+
+
+def test_host_resident_csr_offsets_are_validated_before_any_launch(torch_cuda):
+    """Offsets in host memory that do not start at 0, decrease, or do not end at the number of keys are
+    refused with INVALID_ARGUMENT (what the reference's CPU path enforces); the same offsets in device
+    memory are the caller's responsibility, as in the reference's GPU path."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+    rows, dim = 1000, 16
+    table = to_dev(torch, dg.normal_table(rows, dim, 0.02, 1, np.float16))
+    layer = GPUEmbeddingLayer(table, rows, dim * 2, "float16")
+    ctx = layer.create_execution_context()
+    keys = np.arange(40, dtype=np.int64)
+    out = np.zeros((4, dim), np.float16)
+    good = np.array([0, 10, 20, 30, 40], np.int64)
+    layer.lookup_pooled(ctx, 40, keys, out, dim * 2, "sum", "float16", csr_offsets=good, num_csr_offsets=5)
+    ctx.wait()
+    for bad, what in ((np.array([1, 10, 20, 30, 40], np.int64), "start at 0"),
+                      (np.array([0, 20, 10, 30, 40], np.int64), "decrease"),
+                      (np.array([0, 10, 20, 30, 41], np.int64), "last CSR offset")):
+        with pytest.raises(capi.NveError) as e:
+            layer.lookup_pooled(ctx, 40, keys, out, dim * 2, "sum", "float16", csr_offsets=bad, num_csr_offsets=5)
+        assert e.value.status == capi.NVE_ERROR_INVALID_ARGUMENT and what in e.value.message
+    ctx.wait()
+    ctx.destroy(); layer.destroy()
+
+
+CHECKED = r'''
+import os, sys
+import numpy as np, torch
+sys.path.insert(0, os.environ["NVE_ROOT"])
+from nv_embedding_cache_b200 import capi, datagen as dg
+from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+assert capi._LIB_PATH.name == "libnve_b200_checked.so"
+rows, dim = 5000, 64
+table_np = dg.normal_table(rows, dim, 0.02, 1, np.float16)
+# room behind the table, so that an index a few rows past the end stays inside the allocation even
+# if a check were missing
+store = torch.zeros((rows + 64, dim), dtype=torch.float16, device="cuda")
+store[:rows] = torch.from_numpy(table_np).cuda()
+layer = GPUEmbeddingLayer(store, rows, dim * 2, "float16")          # no default row
+ctx = layer.create_execution_context()
+keys = dg.uniform_keys(64 * 8, rows, 3)
+d_keys = torch.from_numpy(keys).cuda()
+out = torch.zeros((64, dim), dtype=torch.float16, device="cuda")
+layer.lookup_pooled(ctx, keys.size, d_keys, out, dim * 2, "sum", "float16", fixed_hotness=8)
+ctx.wait()                                                            # clean inputs: no report
+want = table_np[keys].astype(np.float32).reshape(64, 8, dim)
+acc = np.zeros((64, dim), np.float32)
+for j in range(8):
+    acc = acc + want[:, j]
+assert np.array_equal(out.cpu().numpy(), acc.astype(np.float16))
+codes = []
+# (a) keys that are no rows of the table: read as row 0, reported
+bad = keys.copy(); bad[5] = rows + 3; bad[77] = rows + 40
+layer.lookup_pooled(ctx, bad.size, torch.from_numpy(bad).cuda(), out, dim * 2, "sum", "float16", fixed_hotness=8)
+try:
+    ctx.wait(); codes.append("no report")
+except capi.NveError as e:
+    codes.append("keys" if "no rows of a table" in e.message else e.message)
+# (b) device-resident offsets that run past the keys: that bag pools to zeros, reported
+offs = torch.tensor([0, 8, 16, 24, keys.size + 100], dtype=torch.int64, device="cuda")
+out4 = torch.ones((4, dim), dtype=torch.float16, device="cuda")
+layer.lookup_pooled(ctx, keys.size, d_keys, out4, dim * 2, "sum", "float16", csr_offsets=offs, num_csr_offsets=5)
+try:
+    ctx.wait(); codes.append("no report")
+except capi.NveError as e:
+    codes.append("offsets" if "CSR offsets" in e.message else e.message)
+assert not out4[3].any().item() and out4[0].any().item()
+# (c) the report is one-shot: a clean lookup afterwards waits without error
+layer.lookup_pooled(ctx, keys.size, d_keys, out, dim * 2, "sum", "float16", fixed_hotness=8)
+ctx.wait()
+# (d) host-resident keys of a table without a default row are refused before the launch
+try:
+    layer.lookup_pooled(ctx, bad.size, bad, out, dim * 2, "sum", "float16", fixed_hotness=8); codes.append("launched")
+except capi.NveError as e:
+    codes.append("host keys" if e.status == capi.NVE_ERROR_INVALID_ARGUMENT else e.message)
+print(codes)
+sys.exit(0 if codes == ["keys", "offsets", "host keys"] else 3)
+'''
+
+
+def test_checked_build_reports_instead_of_reading_out_of_bounds(torch_cuda, tmp_path):
+    """libnve_b200_checked.so (the -DNVE_B200_BOUNDS_CHECK build, loaded through NVE_B200_LIBRARY in a
+    process of its own): keys outside a table without a default row and offsets outside the keys are
+    left out and reported at nve_context_wait."""
+    import os, subprocess, sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    lib = root / "nv_embedding_cache_b200" / "libnve_b200_checked.so"
+    assert lib.exists(), "build it with python -m nv_embedding_cache_b200.build --bounds-check"
+    script = tmp_path / "checked.py"
+    script.write_text(CHECKED)
+    env = dict(os.environ, NVE_ROOT=str(root), NVE_B200_LIBRARY=str(lib))
+    res = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-1500:]
