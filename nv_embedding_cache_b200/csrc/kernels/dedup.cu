@@ -31,6 +31,7 @@
 
 #include "../host/context.hpp"
 #include "device_common.cuh"
+#include "radix_sort.cuh"
 
 namespace nve_b200 {
 
@@ -64,6 +65,23 @@ __global__ void pack_kernel(const KeyT* __restrict__ keys, uint64_t* __restrict_
     packed[i] = (static_cast<uint64_t>(static_cast<uint32_t>(keys[i]) ^ flip) << 32) |
                 static_cast<uint32_t>(i);
   }
+}
+
+// Wide orderings (more than 32 key bits): the key itself is the sort word, with the sign bit flipped
+// when the ordering reaches it (signed order), and the position its payload (made by the sort's
+// first pass).
+// Sorted (word, position) pairs -> sorted keys, the inverse buffer and the group heads (full keys
+// compared, as the run-length encoding does).
+template <typename KeyT>
+__global__ void narrow_heads_kernel(const uint64_t* __restrict__ words, const uint32_t* __restrict__ pos,
+                                    uint64_t flip, KeyT* __restrict__ sorted, KeyT* __restrict__ inverse,
+                                    uint32_t* __restrict__ head, int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint64_t w = words[i];
+  sorted[i] = static_cast<KeyT>(static_cast<int64_t>(w ^ flip));
+  inverse[i] = static_cast<KeyT>(pos[i]);
+  head[i] = (i == 0 || words[i - 1] != w) ? 1u : 0u;
 }
 
 // Sorted packed words -> sorted full keys (fetched through the position), the inverse buffer and
@@ -137,7 +155,9 @@ template <typename KeyT>
 struct Workspace {
   KeyT *sorted, *pos, *group_start, *num_out;
   uint32_t *head, *rank, *chunks, *chunk_base;
-  uint64_t *packed_in, *packed_out;
+  uint64_t *packed_in, *packed_out, *packed_tmp;
+  uint32_t *pos_in, *pos_out, *pos_tmp;
+  void* radix_scratch;
   void* cub_tmp;
   size_t cub_bytes;
   size_t total;
@@ -164,6 +184,11 @@ Workspace<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
   w.chunk_base = static_cast<uint32_t*>(take(N * 4));
   w.packed_in = static_cast<uint64_t*>(take(N * 8));
   w.packed_out = static_cast<uint64_t*>(take(N * 8));
+  w.packed_tmp = static_cast<uint64_t*>(take(N * 8));
+  w.pos_in = static_cast<uint32_t*>(take(N * 4));
+  w.pos_out = static_cast<uint32_t*>(take(N * 4));
+  w.pos_tmp = static_cast<uint32_t*>(take(N * 4));
+  w.radix_scratch = take(radix_sort_scratch_bytes(n));
   w.cub_tmp = take(cub_bytes);
   w.cub_bytes = cub_bytes;
   w.total = off + 256;
@@ -198,10 +223,35 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
   size_t tmp = w.cub_bytes;
   if (end_bit <= 32) {
     const uint32_t flip = (sizeof(KeyT) == 4 && end_bit == 32) ? 0x80000000u : 0u;
-    pack_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(keys, w.packed_in, n, flip);
-    NVE_B200_CUDA(cub::DeviceRadixSort::SortKeys(w.cub_tmp, tmp, w.packed_in, w.packed_out, N, 32,
-                                                 32 + end_bit, s));
+    // this library's own stable radix sort, whose first pass packs (key bits, position) on the fly;
+    // batches beyond its range go to the toolkit's
+    static const bool library_sort = std::getenv("NVE_B200_DEDUP_LIBRARY_SORT") != nullptr;
+    if (n <= radix_sort_max_entries() && !library_sort) {
+      RadixSource from;
+      from.keys = keys;
+      from.key64 = sizeof(KeyT) == 8;
+      from.flip = flip;
+      from.form = RadixSource::kPacked;
+      radix_sort_u64(from, nullptr, w.packed_out, w.packed_tmp, n, 32, 32 + end_bit, w.radix_scratch, s);
+    } else {
+      pack_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(keys, w.packed_in, n, flip);
+      NVE_B200_CUDA(cub::DeviceRadixSort::SortKeys(w.cub_tmp, tmp, w.packed_in, w.packed_out, N, 32,
+                                                   32 + end_bit, s));
+    }
     unpack_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, keys, w.sorted, inverse,
+                                                             w.head, n);
+  } else if (n <= radix_sort_max_entries() && std::getenv("NVE_B200_DEDUP_LIBRARY_SORT") == nullptr) {
+    // the sort orders on the low end_bit bits; the head test compares whole keys, as the run-length
+    // encoding of the reference does after its sort
+    const uint64_t flip = end_bit == 64 ? (uint64_t{1} << 63) : 0;
+    RadixSource from;
+    from.keys = keys;
+    from.key64 = sizeof(KeyT) == 8;
+    from.flip = flip;
+    from.form = RadixSource::kWide;
+    radix_sort_pairs_u64(from, nullptr, w.packed_out, w.packed_tmp, nullptr, w.pos_out, w.pos_tmp, n, 0, end_bit,
+                         w.radix_scratch, s);
+    narrow_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, w.pos_out, flip, w.sorted, inverse,
                                                              w.head, n);
   } else {
     iota_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.pos, n);

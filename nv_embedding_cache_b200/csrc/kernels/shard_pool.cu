@@ -140,11 +140,27 @@ __global__ void __launch_bounds__(256) exchange_insert_kernel(const ShardPoolPar
     }
   }
   // Lanes of a warp that hold the same key send one of them to the table: a frequent key would
-  // otherwise be one address that thousands of compare-and-swaps queue up on.
+  // otherwise be one address that thousands of compare-and-swaps queue up on.  Lanes are grouped by
+  // eight bits of the key's hash (eight ballots; the hardware's match instruction would take a step
+  // per distinct key, about thirty per warp); a lane whose key differs from its group leader's goes
+  // to the table by itself.
   const uint32_t takers = __ballot_sync(0xffffffffu, exchanged);
+  const uint32_t tag = mix_key(static_cast<uint64_t>(key)) >> 24;
+  uint32_t group = takers;
+#pragma unroll
+  for (int b = 0; b < 8; b++) {
+    const bool bit = (tag >> b) & 1u;
+    const uint32_t vote = __ballot_sync(0xffffffffu, bit);
+    group &= bit ? vote : ~vote;
+  }
+  const int group_leader = exchanged ? __ffs(group) - 1 : lane;
+  const int64_t leader_key = __shfl_sync(0xffffffffu, key, group_leader);
+  const bool follows = exchanged && leader_key == key;
+  // the lanes that really share the leader's key
+  const uint32_t sharing = __ballot_sync(0xffffffffu, follows);
   if (exchanged) {
-    const uint32_t same = __match_any_sync(takers, static_cast<unsigned long long>(key));
-    const int leader = __ffs(same) - 1;
+    const uint32_t same = follows ? (group & sharing) : (1u << lane);
+    const int leader = follows ? group_leader : lane;
     uint32_t h = 0;
     if (lane == leader) {
       const uint32_t mask = x.capacity - 1u;
