@@ -892,6 +892,44 @@ def record_c3(steps=20, warmup=5, repeats=5, rows=100_000_000, dim=128, batch=26
                 "host_link_frac_of_probe": misses * row_bytes / sec / 1e9 / link,
                 "e2e": {"value": batch / (ms_e2e * 1e-3 / max(4, steps // 2)), "unit": "keys/s",
                         "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * row_bytes}}
+        # pooled lookups through the same cache (the cached layer's find_and_pool): 32768 bags x 8 keys, sum
+        bags, hot = 32_768, 8
+        pk_np = [dg.zipf_keys(bags * hot, rows, 1.2, 360 + b) for b in range(4)]
+        pk = [torch.from_numpy(k).cuda() for k in pk_np]
+        out_p = torch.empty((bags, dim), dtype=torch.float16, device="cuda")
+        hr_p = layer.lookup_pooled(ctx, bags * hot, pk[0], out_p, row_bytes, "sum", "float16", fixed_hotness=hot,
+                                   want_hitrate=True)
+        ctx.wait()
+        uniq, inv = np.unique(pk_np[0], return_inverse=True)
+        mirror = table[torch.from_numpy(uniq)].numpy()
+        from oracle.pyoracle import Oracle
+        want = Oracle().lookup_pooled(mirror.view(np.uint8).reshape(uniq.size, -1), "f16", dim, inv.astype(np.int64),
+                                      "sum", hotness=hot, out_dtype="f16")
+        same = bool(np.array_equal(out_p.cpu().numpy().view(np.uint16), want.view(np.uint16)))
+        ms_p, _ = timed_repeats(stream, lambda i: layer.lookup_pooled(ctx, bags * hot, pk[i % 4], out_p, row_bytes, "sum",
+                                                                      "float16", fixed_hotness=hot),
+                                steps, warmup, repeats)
+        sec_p = ms_p * 1e-3 / steps
+        alg_p = bags * hot * (8 + row_bytes) + bags * row_bytes
+        rec["pooled"] = {"workload": "32768 bags x 8 Zipf(1.2) keys, sum pooled through the cache (find_and_pool)",
+                         "keys_per_s": bags * hot / sec_p, "us_per_step": sec_p * 1e6, "hit_rate": hr_p, "bit_exact": same,
+                         "roofline": _roofline(alg_p, sec_p, "shard_pool_kernel (cache line or table row per key)")}
+        try:
+            from oracle.pyoracle import ReferenceGpu
+            rg = ReferenceGpu()
+            rc = rg.cache(int(rows * cache_frac) * row_bytes, row_bytes, max_modify=batch)
+            for b in range(20):
+                k = torch.from_numpy(dg.zipf_keys(batch, rows, 1.2, 300 + b)).cuda()
+                rc.insert_from_table(k.data_ptr(), batch, table.data_ptr(), row_bytes)
+            torch.cuda.synchronize()
+            ms_r = rc.find_and_combine(bags, table.data_ptr(), [k.data_ptr() for k in pk], hot, dim, out_p.data_ptr(),
+                                       warmup=warmup, iters=steps)
+            rec["pooled"]["reference_gpu_kernel"] = {
+                "kernel": "find_and_combine with the reference cache in front (same inserts, same batches)",
+                "us_per_step": ms_r * 1e3, "keys_per_s": bags * hot / (ms_r * 1e-3)}
+            rc.close()
+        except Exception as e:      # noqa: BLE001 - the reference GPU library is absent: say so
+            rec["pooled"]["reference_gpu_kernel"] = {"unavailable": str(e)[:200]}
     rec["clocks"] = clk.summary()
     try:
         from oracle.pyoracle import Reference

@@ -389,6 +389,8 @@ class ReferenceGpu:
             "refgpu_cache_insert_from_table": [_vp, _vp, _i64, _vp, _i64],
             "refgpu_cache_lookup_mask": [_vp, _vp, _i64, _vp, _i64, _vp, C.POINTER(_i64)],
             "refgpu_cache_lookup_table": [_vp, _vp, _i64, _vp, _i64, _vp, C.POINTER(_i64)],
+            "refgpu_cache_find_and_combine": [_vp, _i64, _vp, pp, _i32, _i32, _i32, _vp, _i32, _i32,
+                                              C.POINTER(C.c_float)],
             "refgpu_cache_lookup_table_timed": [_vp, pp, _i32, _i64, _vp, _i64, _vp, _i32, _i32,
                                                 C.POINTER(f32)],
             "refgpu_cache_update": [_vp, _vp, _i64, _vp, _i64],
@@ -488,6 +490,15 @@ class RefGpuCache:
         self.ref.check(self.ref.lib.refgpu_cache_lookup_table(self.h, keys_ptr, n, out_ptr, stride, table_ptr,
                                                               C.byref(m)))
         return m.value
+
+    def find_and_combine(self, bags, table_ptr, key_ptrs, hot, width, out_ptr, warmup=0, iters=0) -> float:
+        """The reference's pooled lookup with this cache in front of `table_ptr` (fp16 rows, fixed
+        hotness, sum, fp16 out); mean milliseconds per launch when iters > 0."""
+        nb = len(key_ptrs)
+        ms = C.c_float(0)
+        self.ref.check(self.ref.lib.refgpu_cache_find_and_combine(
+            self.h, bags, table_ptr, (_vp * nb)(*key_ptrs), nb, hot, width, out_ptr, warmup, iters, C.byref(ms)))
+        return ms.value
 
     def lookup_table_timed(self, key_ptrs, n, out_ptr, stride, table_ptr, warmup, iters) -> float:
         nb = len(key_ptrs)

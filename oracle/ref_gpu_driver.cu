@@ -257,6 +257,49 @@ int refgpu_cache_lookup_table(void* h, const int64_t* d_keys, int64_t n, void* d
   });
 }
 
+// find_and_combine with the reference cache in front of a linear table (what its LinearUVM layer
+// launches for a pooled lookup): fp16 rows, fixed hotness, sum, fp16 out, width <= 128.  `iters`
+// back-to-back launches over the key batches in turn, mean milliseconds per launch (iters == 0: one
+// launch, no timing).
+int refgpu_cache_find_and_combine(void* h, int64_t bags, const void* d_table,
+                                  const int64_t* const* d_key_batches, int num_batches, int hot, int width,
+                                  void* d_out, int warmup, int iters, float* ms_per_launch) {
+  return guarded([&] {
+    auto* c = static_cast<RefCache*>(h);
+    constexpr nve::DataType_t ELEM = nve::DataType_t::Float16;
+    using Q = nve::QuantizationHelper<ELEM>;
+    using Data = typename Cache::CacheData;
+    constexpr uint32_t MASK = NVE_FAC_MASK_LOAD_INDICES | NVE_FAC_MASK_FIXED_HOTNESS | NVE_FAC_MASK_SUM_POOLING;
+    const Data data = c->cache->get_cache_data(c->lookup);
+    auto once = [&](int b) {
+      nve_fac_launch<ELEM, Key, float, float, __half, typename Q::Vec4, typename nve::VecWidthHelper<__half>::Vec4,
+                     typename nve::VecWidthHelper<typename Q::ParamType>::Vec4,
+                     typename nve::VecWidthHelper<float>::Vec4, Data, 1, MASK>(
+          static_cast<uint32_t>(bags), static_cast<const int8_t*>(d_table), d_key_batches[b], nullptr, nullptr, hot,
+          data, width, d_out, 0);
+    };
+    if (iters <= 0) {
+      once(0);
+      ck(cudaDeviceSynchronize(), "sync");
+      return;
+    }
+    cudaEvent_t e0, e1;
+    ck(cudaEventCreate(&e0), "event");
+    ck(cudaEventCreate(&e1), "event");
+    for (int i = 0; i < warmup + iters; i++) {
+      if (i == warmup) ck(cudaEventRecord(e0, 0), "record");
+      once(i % num_batches);
+    }
+    ck(cudaEventRecord(e1, 0), "record");
+    ck(cudaEventSynchronize(e1), "sync");
+    float ms = 0.f;
+    ck(cudaEventElapsedTime(&ms, e0, e1), "elapsed");
+    *ms_per_launch = ms / static_cast<float>(iters);
+    ck(cudaEventDestroy(e0), "event");
+    ck(cudaEventDestroy(e1), "event");
+  });
+}
+
 // Timed form of the table-backed lookup: `iters` back-to-back calls, mean milliseconds per call.
 int refgpu_cache_lookup_table_timed(void* h, const int64_t* const* d_key_batches, int num_batches,
                                     int64_t n, void* d_values, int64_t stride, const void* d_table,

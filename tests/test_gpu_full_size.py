@@ -210,3 +210,37 @@ def test_cache_insert_is_idempotent_at_c3_batch_size(torch_cuda):
     hit = ~np.all(out == 0, axis=1)
     assert hit.any() and np.array_equal(out[hit], table[torch.from_numpy(probe[hit]).cuda()].cpu().numpy())
     cache.close()
+
+
+def test_c3_full_batch_cached_gather_matches_oracle_cache(torch_cuda, oracle):
+    """The cached-layer configuration at its own batch size and cache fraction: a table of fp16 rows
+    in pinned host memory (scaled to 4 M rows), a cache of 10 % of its rows warmed by 20 inserts of
+    262 144 Zipf(1.2) keys, then one lookup of 262 144 Zipf(1.2) keys and one of uniform keys.  Rows
+    byte-exact; resident tags of every (set, way) and the miss counts equal to the oracle cache that
+    saw the same inserts."""
+    torch = torch_cuda
+    from nve_helpers import CacheTable
+    from oracle.pyoracle import OracleCache
+    rows, dim, batch = 4_000_000, 128, 262_144
+    row_bytes = dim * 2
+    tb = np.random.default_rng(30).integers(0, 256, (rows, row_bytes), dtype=np.uint8)   # rows are copied as bytes
+    backing = torch.from_numpy(tb).pin_memory()
+    cache_bytes = int(rows * 0.10) * row_bytes
+    gpu = CacheTable(cache_bytes, row_bytes, value_dtype="f16", backing=backing, backing_rows=rows, max_modify=batch)
+    ref = OracleCache(oracle, cache_bytes, row_bytes)
+    assert gpu.num_sets == ref.num_sets
+    for b in range(20):
+        keys = dg.zipf_keys(batch, rows, 1.2, 300 + b)
+        gpu.insert_from_backing(keys)
+        ref.insert(keys, table=tb, max_modify=batch)
+    assert np.array_equal(gpu.tags(), ref.tags())
+    for name, keys in (("zipf", dg.zipf_keys(batch, rows, 1.2, 320)), ("uniform", dg.uniform_keys(batch, rows, 321))):
+        out = np.zeros((batch, row_bytes), np.uint8)
+        misses = gpu.find(keys, out)
+        assert np.array_equal(out, tb[keys]), name
+        ref.reset_misses()
+        ref.lookup(keys, None)
+        assert misses == ref.misses, (name, misses, ref.misses)
+        hit_rate = 1.0 - misses / batch
+        assert (hit_rate > 0.8) if name == "zipf" else (hit_rate < 0.3), (name, hit_rate)
+    gpu.close()
