@@ -475,6 +475,35 @@ NVE_C_API nve_status_t nve_b200_managed_block_create(void** out, uint64_t bytes,
                                                      int32_t num_gpus);
 NVE_C_API nve_status_t nve_b200_managed_block_destroy(void* block);
 
+/*
+ * Registry of layers by marker address, for hosts that reach a layer through a traced or exported
+ * graph instead of through a handle.  Replaces NVELayerRegistry and its free-function helpers
+ * (python/pynve/torch_bindings/nve_registry.hpp:39-108): the torch layer owns a one-element
+ * "marker" tensor, registers its layer under that tensor's data pointer, and the custom ops
+ * nve_ops::embedding_lookup / nve_ops::embedding_lookup_with_pooling (csrc/torch/nve_torch_ops.cpp,
+ * built as libnve_b200_torch_ops.so) find the layer by the pointer they are handed at run time.
+ *
+ * The registry does not own the layer: unregister before nve_layer_destroy.  It creates one execution
+ * context per caller stream on first use and destroys them at unregister.  Keys and offsets are int64
+ * (the key type of layers made through the Python edge); offsets follow the num_bags + 1 convention;
+ * `output` holds num_keys (or num_offsets - 1) rows of embedding_dim elements of the layer's type,
+ * tightly packed.  `weights` may be NULL; weight_dtype is then ignored.  Lookups may run concurrently
+ * with each other and with register / unregister of other markers.
+ */
+NVE_C_API nve_status_t nve_b200_registry_register(const void* marker, nve_layer_t layer, int64_t embedding_dim,
+                                                  nve_data_type_t dtype, int device_id);
+NVE_C_API nve_status_t nve_b200_registry_unregister(const void* marker); /* unknown markers are ignored */
+NVE_C_API nve_status_t nve_b200_registry_describe(const void* marker, int64_t* embedding_dim,
+                                                  nve_data_type_t* dtype, int* device_id);
+NVE_C_API int64_t nve_b200_registry_size(void);
+NVE_C_API nve_status_t nve_b200_registry_lookup(const void* marker, int64_t num_keys, const int64_t* keys,
+                                                void* output, void* stream);
+NVE_C_API nve_status_t nve_b200_registry_lookup_pooled(const void* marker, int64_t num_keys,
+                                                       const int64_t* keys, void* output,
+                                                       nve_pooling_type_t pooling_type, int64_t num_offsets,
+                                                       const int64_t* offsets, nve_data_type_t weight_dtype,
+                                                       const void* weights, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -78,6 +78,34 @@ def build(force: bool = False, verbose: bool = False, bounds_check: bool = False
     return lib
 
 
+TORCH_OPS_SRC = CSRC / "torch" / "nve_torch_ops.cpp"
+TORCH_OPS_LIB = PKG / "libnve_b200_torch_ops.so"
+
+
+def build_torch_ops(force: bool = False, verbose: bool = False) -> Path | None:
+    """Builds libnve_b200_torch_ops.so (the torch custom ops over the layer registry) with the host
+    compiler against the installed torch's stable-ABI headers.  Returns None when torch is not
+    importable; the rest of the library does not need it."""
+    try:
+        import torch
+    except ImportError:
+        return None
+    build()
+    torch_dir = Path(torch.__file__).resolve().parent
+    newest = max(TORCH_OPS_SRC.stat().st_mtime, (ROOT / "include" / "nve_b200_ops.h").stat().st_mtime)
+    if not force and TORCH_OPS_LIB.exists() and TORCH_OPS_LIB.stat().st_mtime >= newest:
+        return TORCH_OPS_LIB
+    cuda_include = Path(NVCC).resolve().parent.parent / "include"
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-I{torch_dir / 'include'}", f"-I{cuda_include}", f"-I{ROOT / 'include'}", str(TORCH_OPS_SRC),
+           "-o", str(TORCH_OPS_LIB), f"-L{PKG}", "-lnve_b200", "-Wl,-rpath,$ORIGIN",
+           f"-L{torch_dir / 'lib'}", "-ltorch", "-ltorch_cpu", "-lc10", f"-Wl,-rpath,{torch_dir / 'lib'}"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return TORCH_OPS_LIB
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
@@ -85,4 +113,6 @@ if __name__ == "__main__":
     ap.add_argument("--bounds-check", action="store_true")
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.bounds_check))
+    if not a.bounds_check:
+        print(build_torch_ops(a.force, a.verbose))
     sys.exit(0)

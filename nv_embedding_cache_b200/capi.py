@@ -12,6 +12,7 @@ import os
 
 # NVE_B200_LIBRARY: another build of the library to load, e.g. the checked one
 # (libnve_b200_checked.so, `python -m nv_embedding_cache_b200.build --bounds-check`)
+PACKAGE_DIR = Path(__file__).resolve().parent
 _LIB_PATH = Path(os.environ.get("NVE_B200_LIBRARY") or Path(__file__).resolve().parent / "libnve_b200.so")
 
 # ---- enums (include/nve_c_api.h) -------------------------------------------------------------
@@ -193,6 +194,12 @@ PROTOTYPES = {
     "nve_b200_dedup_grads_static": (_i32, [C.c_int, _i64, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
                                             _vp, _vp, _i64, _i32, _i64, C.c_float, _vp]),
     "nve_b200_dedup_grads_status": (_i32, [C.POINTER(_i32)]),
+    "nve_b200_registry_register": (_i32, [_vp, _vp, _i64, C.c_int, C.c_int]),
+    "nve_b200_registry_unregister": (_i32, [_vp]),
+    "nve_b200_registry_describe": (_i32, [_vp, C.POINTER(_i64), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "nve_b200_registry_size": (_i64, []),
+    "nve_b200_registry_lookup": (_i32, [_vp, _i64, _vp, _vp, _vp]),
+    "nve_b200_registry_lookup_pooled": (_i32, [_vp, _i64, _vp, _vp, C.c_int, _i64, _vp, C.c_int, _vp, _vp]),
     "nve_b200_nccl_unique_id": (_i32, [_vp]),
     "nve_b200_sharded_table_create": (_i32, [C.POINTER(_vp), C.POINTER(ShardedTableConfig)]),
     "nve_b200_sharded_table_destroy": (_i32, [_vp]),

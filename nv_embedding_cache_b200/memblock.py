@@ -16,6 +16,21 @@ import torch
 from . import capi
 
 
+def copy_bytes(dst: int, src: int, nbytes: int) -> None:
+    """Synchronous byte copy between any two addresses the process can name (host, pinned, managed
+    or device memory): the runtime works out the direction.  Without a CUDA driver only host
+    addresses exist, and a plain memmove does."""
+    if not torch.cuda.is_available():
+        C.memmove(dst, src, nbytes)
+        return
+    runtime = C.CDLL("libcudart.so.12")      # already in the process: torch loaded it
+    runtime.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    runtime.cudaMemcpy.restype = C.c_int
+    err = runtime.cudaMemcpy(dst, src, nbytes, 4)     # 4 = cudaMemcpyDefault
+    if err != 0:
+        raise RuntimeError(f"cudaMemcpy of {nbytes} bytes failed with error {err}")
+
+
 class ManagedMemBlock:
     """``ManagedMemBlock(size_in_bytes, gpu_ids)`` or, as the reference binding also offers,
     ``ManagedMemBlock(row_size, num_embeddings, elem_bytes, gpu_ids)`` through :meth:`for_table`."""

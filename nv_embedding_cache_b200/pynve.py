@@ -42,6 +42,14 @@ class EmbedLayerConfig:
         # population, threshold 0.75), "never", or a float threshold
         self.insert_heuristic = "default"
 
+    def to_json(self) -> str:
+        """The fields the reference serialises (binding_layers.hpp:62-65), as a JSON object; what a
+        loader hands back to ``config_to_nve_config``."""
+        import json
+        return json.dumps({name: getattr(self, name) for name in (
+            "logging_interval", "kernel_mode", "kernel_mode_value_1", "kernel_mode_value_2", "max_modify_size",
+            "default_row_index")} | {"default_embedding": [int(b) for b in self.default_embedding]})
+
 
 _POOL_NAME = {PoolingType_t.Concatenate: "concatenate", PoolingType_t.Sum: "sum",
               PoolingType_t.Mean: "mean", PoolingType_t.WeightedSum: "weighted_sum",
@@ -215,11 +223,29 @@ def device_tensor(ptr: int, shape, dtype, device):
     return t
 
 
+class MemBlockType(str, enum.Enum):
+    """What MemBlock.get_type() answers with (reference binding enum, python_binding.cu:229-236).
+    Members compare equal to their names, so ``block.get_type() == "Managed"`` also holds."""
+    Linear = "Linear"
+    NVL = "NVL"
+    MPI = "MPI"
+    Managed = "Managed"
+    User = "User"
+    Host = "Host"
+
+    def __str__(self) -> str:
+        return self.value
+
+
+def _element_bytes(data_type) -> int:
+    return 4 if DataType_t(data_type) == DataType_t.Float32 else 2
+
+
 class MemBlock:
     """Storage handed to a layer (reference MemBlock, include/memblock.hpp): an address, a size and
-    a type name.  The owner of the memory keeps it alive for as long as the layer lives."""
+    a type.  The owner of the memory keeps it alive for as long as the layer lives."""
 
-    TYPE = "User"
+    TYPE = MemBlockType.User
 
     def __init__(self, ptr: int, size_in_bytes: int):
         self._ptr = int(ptr)
@@ -234,27 +260,42 @@ class MemBlock:
     def get_size_in_bytes(self) -> int:
         return self._size
 
-    def get_type(self) -> str:
+    def get_type(self) -> MemBlockType:
         return self.TYPE
 
     def data_ptr(self) -> int:
         return self._ptr
 
+    def copy_from(self, src) -> None:
+        """Byte copy of a C-contiguous buffer (numpy array, bytes, ...) into the block, bounds-checked
+        (reference python_binding.cu:243-262).  Host, managed and device memory alike."""
+        import numpy as np
+        a = np.asarray(src)
+        if not a.flags["C_CONTIGUOUS"]:
+            raise ValueError("copy_from: source buffer must be C-contiguous")
+        if a.nbytes > self._size:
+            raise IndexError(f"copy_from: source is {a.nbytes} bytes but memblock holds {self._size} bytes")
+        if a.nbytes:
+            from .memblock import copy_bytes
+            copy_bytes(self._ptr, a.ctypes.data, a.nbytes)
+
 
 class UserMemBlock(MemBlock):
     """Memory the caller owns: ``UserMemBlock(tensor.data_ptr(), tensor.nbytes)``."""
+
+    def __init__(self, ptr: int, size: int):
+        super().__init__(ptr, size)
 
 
 class ManagedMemBlock(MemBlock):
     """Managed memory kept on the host and mapped into the listed GPUs, with the reference binding's
     signature: ``ManagedMemBlock(row_size, num_embeddings, data_type, gpu_ids)``."""
 
-    TYPE = "Managed"
+    TYPE = MemBlockType.Managed
 
     def __init__(self, row_size: int, num_embeddings: int, data_type: DataType_t, gpu_ids=(0,)):
         from .memblock import ManagedMemBlock as _Block
-        elem = 4 if DataType_t(data_type) == DataType_t.Float32 else 2
-        self._block = _Block(row_size * num_embeddings * elem, tuple(gpu_ids))
+        self._block = _Block(row_size * num_embeddings * _element_bytes(data_type), tuple(gpu_ids))
         super().__init__(self._block.get_ptr(), self._block.get_size_in_bytes())
 
     def copy_from(self, src) -> None:
@@ -267,9 +308,57 @@ class ManagedMemBlock(MemBlock):
         self._block.close()
 
 
-class MemBlockType:
-    """Type names that MemBlock.get_type() answers with (reference binding: a string-valued enum)."""
-    User, Managed, Linear, Host, NVL, MPI = "User", "Managed", "Linear", "Host", "NVL", "MPI"
+class LinearMemBlock(MemBlock):
+    """Plain device memory on one GPU: ``LinearMemBlock(row_size, num_embeddings, dtype, device_id)``
+    (reference python_binding.cu:264-267).  ``device_id = -1``, the reference's host-side form, is
+    not provided: use HostMemBlock."""
+
+    TYPE = MemBlockType.Linear
+
+    def __init__(self, row_size: int, num_embeddings: int, dtype: DataType_t, device_id: int = -1):
+        if device_id < 0:
+            raise NotImplementedError("LinearMemBlock on the host: use HostMemBlock")
+        import torch
+        self._tensor = torch.empty(row_size * num_embeddings * _element_bytes(dtype), dtype=torch.uint8,
+                                   device=torch.device("cuda", device_id))
+        super().__init__(self._tensor.data_ptr(), self._tensor.nbytes)
+
+
+class HostMemBlock(MemBlock):
+    """Pinned host memory that every GPU can read in place: ``HostMemBlock(row_size,
+    num_embeddings, dtype)`` (reference python_binding.cu:292-294)."""
+
+    TYPE = MemBlockType.Host
+
+    def __init__(self, row_size: int, num_embeddings: int, dtype: DataType_t):
+        import torch
+        self._tensor = torch.empty(row_size * num_embeddings * _element_bytes(dtype), dtype=torch.uint8,
+                                   pin_memory=True)
+        super().__init__(self._tensor.data_ptr(), self._tensor.nbytes)
+
+
+class NVLMemBlock(MemBlock):
+    """One allocation spread over several GPUs of one process.  Not provided: a table sharded over
+    GPUs is the ShardedEmbeddingTable of this library, one process per GPU."""
+
+    TYPE = MemBlockType.NVL
+
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("NVLMemBlock: use nv_embedding_cache_b200.sharded.ShardedEmbeddingTable")
+
+
+def resolve_memblock_devices(type, def_index: int, override=()):
+    """GPU ids for rebuilding a block at load time (reference src/memblock.cpp:144-164): `override`
+    if given; for NVL every GPU from `def_index` up; otherwise `def_index` alone."""
+    if len(override):
+        return list(override)
+    if MemBlockType(type) == MemBlockType.NVL:
+        import torch
+        count = torch.cuda.device_count()
+        if not 0 <= def_index < count:
+            raise ValueError(f"resolve_memblock_devices: def_index={def_index} out of range, system has {count} GPUs")
+        return list(range(def_index, count))
+    return [def_index]
 
 
 class Table:
@@ -317,17 +406,65 @@ def get_dl_tensor(layer: "NVEmbedBinding", data_type):
 
 
 _TORCH_REGISTRY: dict[int, "NVEmbedBinding"] = {}
+_TORCH_OPS_LIBRARY = capi.PACKAGE_DIR / "libnve_b200_torch_ops.so"
+_torch_ops_loaded = False
+
+
+def load_torch_ops() -> bool:
+    """Loads the compiled op library (nve_ops::embedding_lookup, nve_ops::embedding_lookup_with_pooling)
+    into torch, once.  False when it has not been built or NVE_B200_TORCH_OPS=0 asks for the
+    plain-Python path; callers then see HAS_TORCH_OPS false, as with a reference build without its
+    torch bindings."""
+    global _torch_ops_loaded
+    if _torch_ops_loaded:
+        return True
+    import os
+    if os.environ.get("NVE_B200_TORCH_OPS", "1") == "0" or not _TORCH_OPS_LIBRARY.exists():
+        return False
+    import torch
+    torch.ops.load_library(str(_TORCH_OPS_LIBRARY))
+    _torch_ops_loaded = True
+    return True
 
 
 def register_for_torch(marker_ptr: int, layer: "NVEmbedBinding") -> None:
-    """Registry of layers by marker address, as the reference keeps for its torch custom ops.  No
-    custom ops are built here (callers see HAS_TORCH_OPS false and take the plain-Python path); the
-    registry only keeps the calls valid."""
+    """Names `layer` by the address of its marker tensor in the library's registry, where the torch
+    custom ops look it up (reference python_binding.cu:372-377).  The layer object is kept alive
+    until unregister_from_torch."""
+    capi.check(capi.lib.nve_b200_registry_register(int(marker_ptr), layer._layer.handle, layer._row_elems,
+                                                   int(layer._dtype), layer._device))
     _TORCH_REGISTRY[int(marker_ptr)] = layer
 
 
 def unregister_from_torch(marker_ptr: int) -> None:
-    _TORCH_REGISTRY.pop(int(marker_ptr), None)
+    if _TORCH_REGISTRY.pop(int(marker_ptr), None) is not None:
+        capi.check(capi.lib.nve_b200_registry_unregister(int(marker_ptr)))
+
+
+class TensorFileFormat:
+    """Writer of the ``.nve`` container's file header (reference binding class of the same name,
+    python_binding.cu:196-202)."""
+
+    def write_table_file_header(self, stream) -> None:
+        from . import weight_files
+        weight_files.write_header(stream)
+
+
+def _table_view(layer: "NVEmbedBinding"):
+    import torch
+    dt = torch.float32 if layer._dtype == DataType_t.Float32 else torch.float16
+    device = torch.device("cuda", layer._device)
+    return device_tensor(_address(layer._memblock), (layer._num_rows, layer._row_elems), dt, device), device
+
+
+def write_tensor_to_stream(layer: "NVEmbedBinding", stream, name: int) -> None:
+    """Appends the table of `layer` as tensor `name` to a .nve container whose header is already
+    written (reference write_tensor_to_stream, binding_layers.hpp:626-630,693-703)."""
+    import torch
+    from . import weight_files
+    table, device = _table_view(layer)
+    torch.cuda.synchronize(device)
+    weight_files.write_tensor(stream, name, table.cpu().numpy())
 
 
 def load_tensor_from_stream(layer: "NVEmbedBinding", stream, name: int) -> None:
@@ -341,9 +478,8 @@ def load_tensor_from_stream(layer: "NVEmbedBinding", stream, name: int) -> None:
                     dtype=np.float32 if layer._dtype == DataType_t.Float32 else np.float16)
     if not weight_files.read_tensor(stream, name, host):
         raise KeyError(f"the file holds no tensor named {name}")
-    dt = torch.float32 if layer._dtype == DataType_t.Float32 else torch.float16
-    device = torch.device("cuda", layer._device)
-    device_tensor(_address(layer._memblock), host.shape, dt, device).copy_(torch.from_numpy(host))
+    table, device = _table_view(layer)
+    table.copy_(torch.from_numpy(host))
     torch.cuda.synchronize(device)
     if isinstance(layer, LinearUVMEmbedding):
         layer.clear(torch.cuda.current_stream(device).cuda_stream)
@@ -403,3 +539,10 @@ class LinearUVMEmbedding(NVEmbedBinding):
     def close(self) -> None:
         super().close()
         self._table.destroy()
+
+
+# As with the reference, importing the binding module is what makes the torch ops exist.
+try:
+    load_torch_ops()
+except ImportError:        # no torch in this interpreter: the ctypes edge works without it
+    pass

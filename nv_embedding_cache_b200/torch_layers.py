@@ -6,6 +6,12 @@ gradients.  Forward and backward run through the pynve-named edge (``pynve.py``)
 C ABI of the library; the autograd functions are those of the reference's plain-Python path
 (``CacheEmbeddingOp`` / ``CacheEmbeddingBagOp``, python/pynve/torch/nve_ops.py:229-316).
 
+Where the compiled op library is present (``HAS_TORCH_OPS``), forward goes through the torch custom
+ops ``nve_ops::embedding_lookup`` / ``nve_ops::embedding_lookup_with_pooling`` instead, which
+``torch.export`` can trace: every layer owns a one-element marker tensor whose address names it in
+the library's registry, and the ops find the layer by that address (reference nve_layers.py:310-327,
+nve_ops.py:66-221).  ``nv_embedding_cache_b200.export`` saves and reloads such models.
+
 Provided layer types: ``GPULayer`` (dense table in HBM) and ``LinearUVM`` (GPU cache in front of a
 host-resident table).  ``Hierarchical`` and ``HostLayer`` need host tables and parameter servers,
 which are outside this library: they raise NotImplementedError.
@@ -20,6 +26,8 @@ import torch
 
 from . import pynve as nve
 
+
+HAS_TORCH_OPS = nve.load_torch_ops()
 
 # value types a layer can hold, both ways (the binding's enum <-> torch)
 _TORCH_OF_NVE = {nve.DataType_t.Float32: torch.float32, nve.DataType_t.Float16: torch.float16}
@@ -205,6 +213,101 @@ class CacheEmbeddingBagOp(torch.autograd.Function):
         return None, grad, None, None, None
 
 
+def _register_shape_functions() -> None:
+    """Shape inference of the two ops for tracing (fake tensors carry no data, so the registry is
+    not consulted: rows and type come from the arguments baked into the call).  Another module in
+    the process may have registered the same functions already; that registration is kept."""
+    def lookup_shape(marker, keys, embedding_size, dtype):
+        return keys.new_empty((keys.numel(), embedding_size), dtype=nve_type_to_torch_type(dtype))
+
+    def pooled_shape(marker, keys, offsets, weights, pooling_type, embedding_size, dtype):
+        torch._check(offsets.size(0) >= 2, lambda: "offsets: at least two entries are needed")
+        return keys.new_empty((offsets.size(0) - 1, embedding_size), dtype=nve_type_to_torch_type(dtype))
+
+    for name, fn in (("nve_ops::embedding_lookup", lookup_shape),
+                     ("nve_ops::embedding_lookup_with_pooling", pooled_shape)):
+        try:
+            torch.library.register_fake(name)(fn)
+        except RuntimeError:
+            pass
+
+
+if HAS_TORCH_OPS:
+    _register_shape_functions()
+
+
+def _sparse_rows(unique_keys, rows, count, weight):
+    return torch.sparse_coo_tensor(unique_keys[:count].reshape(1, -1), rows[:count], weight.shape,
+                                   device=weight.device, check_invariants=False, is_coalesced=True)
+
+
+class MarkerLookupOp(torch.autograd.Function):
+    """Un-pooled lookup through ``nve_ops::embedding_lookup``.  ``weight`` is the layer's CachedTable
+    when gradients are wanted (it takes no part in the forward computation, it receives the sparse
+    gradient) and None for inference, where backward is refused."""
+
+    @staticmethod
+    def forward(marker, keys, weight, embedding_size: int, dtype_tag: int):
+        return torch.ops.nve_ops.embedding_lookup(marker, keys, embedding_size, dtype_tag)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        _, keys, weight, _, _ = inputs
+        ctx.trainable = weight is not None
+        if ctx.trainable:
+            ctx.save_for_backward(keys, weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if not ctx.trainable:
+            raise RuntimeError("this layer was built with optimize_for_training=False: it has no backward")
+        keys, weight = ctx.saved_tensors
+        num_keys = keys.numel()
+        grad_output = grad_output.contiguous()
+        unique_keys = torch.empty(num_keys, dtype=torch.int64, device=keys.device)
+        rows = torch.empty(num_keys, grad_output.shape[-1], dtype=grad_output.dtype, device=keys.device)
+        count = weight.emb_layer.concat_backprop(num_keys, keys.data_ptr(), grad_output.data_ptr(),
+                                                 unique_keys.data_ptr(), rows.data_ptr(),
+                                                 _stream_handle(keys.device))
+        return None, None, _sparse_rows(unique_keys, rows, count, weight), None, None
+
+
+class MarkerPooledLookupOp(torch.autograd.Function):
+    """Pooled lookup through ``nve_ops::embedding_lookup_with_pooling``; ``weight`` as in
+    MarkerLookupOp."""
+
+    @staticmethod
+    def forward(marker, keys, weight, offsets, per_sample_weights, pooling_type: int, embedding_size: int,
+                dtype_tag: int):
+        return torch.ops.nve_ops.embedding_lookup_with_pooling(marker, keys, offsets, per_sample_weights,
+                                                               pooling_type, embedding_size, dtype_tag)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        _, keys, weight, offsets, per_sample_weights, pooling_type, _, _ = inputs
+        ctx.trainable = weight is not None
+        ctx.pooling_type = pooling_type
+        ctx.weighted = per_sample_weights is not None
+        if ctx.trainable:
+            ctx.save_for_backward(keys, weight, offsets, *([per_sample_weights] if ctx.weighted else []))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if not ctx.trainable:
+            raise RuntimeError("this layer was built with optimize_for_training=False: it has no backward")
+        keys, weight, offsets, *rest = ctx.saved_tensors
+        per_sample_weights = rest[0] if ctx.weighted else None
+        num_keys = keys.numel()
+        grad_output = grad_output.contiguous()
+        unique_keys = torch.empty(num_keys, dtype=torch.int64, device=keys.device)
+        rows = torch.empty(num_keys, grad_output.shape[-1], dtype=grad_output.dtype, device=keys.device)
+        count = weight.emb_layer.pooling_backprop(
+            num_keys, keys.data_ptr(), grad_output.data_ptr(), unique_keys.data_ptr(), rows.data_ptr(),
+            ctx.pooling_type, offsets.numel() - 1, offsets.data_ptr(), int(_weight_type(per_sample_weights)),
+            per_sample_weights.data_ptr() if per_sample_weights is not None else 0, _stream_handle(keys.device))
+        return None, None, _sparse_rows(unique_keys, rows, count, weight), None, None, None, None, None
+
+
 class NVEmbeddingBase(torch.nn.Module):
     """Common part of NVEmbedding / NVEmbeddingBag (reference NVEmbeddingBase, nve_layers.py:124-401):
     builds the storage, the layer object and the ``weight`` Parameter that ties them together.
@@ -271,8 +374,28 @@ class NVEmbeddingBase(torch.nn.Module):
         self.storage = storage
         self.memblock_type = storage.get_type()
         self.weight = CachedTable(tensor_storage, cache=self.emb_layer)
+        # The layer's name in the registry of the op library: the address of this one-element buffer.
+        # Not part of the state dict; an exported graph carries it as a constant into every op call,
+        # and a loader points that constant at the marker of the layer it rebuilt.
+        self.register_buffer("marker_tensor", torch.tensor([self.id], dtype=torch.int64, device=self.device),
+                             persistent=False)
+        self.dtype_tag = int(self.layer_data_type)
+        self._registered_marker = None
+        if HAS_TORCH_OPS:
+            self._registered_marker = self.marker_tensor.data_ptr()
+            nve.register_for_torch(self._registered_marker, self.emb_layer)
+
+    def _grad_weight(self):
+        return self.weight if self.optimize_for_training else None
 
     def __del__(self):
+        marker = getattr(self, "_registered_marker", None)
+        if marker is not None:
+            try:
+                nve.unregister_from_torch(marker)
+            except Exception:
+                pass
+            self._registered_marker = None
         layer = getattr(self, "emb_layer", None)
         if layer is not None:
             try:
@@ -287,8 +410,9 @@ class NVEmbeddingBase(torch.nn.Module):
         for name, param in self.named_parameters():
             if name != "weight":
                 param.data = param.data.to(device, dtype if dtype else param.dtype, non_blocking)
-        for _, buf in self.named_buffers():
-            buf.data = buf.data.to(device, dtype if dtype else buf.dtype, non_blocking)
+        for name, buf in self.named_buffers():
+            if name != "marker_tensor":              # its address is the layer's name: it stays put
+                buf.data = buf.data.to(device, dtype if dtype else buf.dtype, non_blocking)
         return self
 
     def update(self, keys: torch.Tensor, updates: torch.Tensor):
@@ -332,6 +456,9 @@ class NVEmbedding(NVEmbeddingBase):
 
     def forward(self, keys: torch.Tensor):
         _check_forward_inputs(keys)
+        if HAS_TORCH_OPS:
+            return MarkerLookupOp.apply(self.marker_tensor, keys, self._grad_weight(), self.embedding_size,
+                                        self.dtype_tag)
         return CacheEmbeddingOp.apply(keys, self.weight)
 
 
@@ -350,6 +477,13 @@ class NVEmbeddingBag(NVEmbeddingBase):
     def forward(self, input: torch.Tensor, offsets: torch.Tensor,
                 per_sample_weights: Optional[torch.Tensor] = None):
         _check_forward_inputs(input, offsets, per_sample_weights)
+        if not HAS_TORCH_OPS:
+            if self.mode == "concat":
+                return CacheEmbeddingOp.apply(input, self.weight)
+            return CacheEmbeddingBagOp.apply(input, self.weight, offsets, self.mode, per_sample_weights)
         if self.mode == "concat":
-            return CacheEmbeddingOp.apply(input, self.weight)
-        return CacheEmbeddingBagOp.apply(input, self.weight, offsets, self.mode, per_sample_weights)
+            return MarkerLookupOp.apply(self.marker_tensor, input, self._grad_weight(), self.embedding_size,
+                                        self.dtype_tag)
+        pool = pooling_type_from_mode(self.mode, weighted=per_sample_weights is not None)
+        return MarkerPooledLookupOp.apply(self.marker_tensor, input, self._grad_weight(), offsets,
+                                          per_sample_weights, int(pool), self.embedding_size, self.dtype_tag)
