@@ -97,7 +97,7 @@ def config_to_nve_config(config: Optional[dict]):
                  "max_modify_size", "default_row_index", "insert_heuristic"):
         if name in config:
             setattr(cfg, name, config[name])
-    if "default_embedding" in config:
+    if len(config.get("default_embedding", ())) > 0:      # a reloaded config carries the empty default
         raise ValueError("config['default_embedding'] is only supported for HostLayer and Hierarchical layers")
     return cfg
 
@@ -389,20 +389,22 @@ class NVEmbeddingBase(torch.nn.Module):
         return self.weight if self.optimize_for_training else None
 
     def __del__(self):
-        marker = getattr(self, "_registered_marker", None)
-        if marker is not None:
-            try:
+        # Also runs while the interpreter shuts down, when torch's own module machinery may be half
+        # gone: attributes are cleared past Module.__setattr__ and nothing here may raise.
+        try:
+            marker = self.__dict__.get("_registered_marker")
+            if marker is not None:
+                self.__dict__["_registered_marker"] = None
                 nve.unregister_from_torch(marker)
-            except Exception:
-                pass
-            self._registered_marker = None
-        layer = getattr(self, "emb_layer", None)
-        if layer is not None:
-            try:
+        except Exception:
+            pass
+        try:
+            layer = self.__dict__.get("emb_layer")
+            if layer is not None:
+                self.__dict__["emb_layer"] = None
                 layer.close()
-            except Exception:
-                pass
-            self.emb_layer = None
+        except Exception:
+            pass
 
     def to(self, *args, **kwargs):
         """The table and its cache stay where they were built; other parameters and buffers move."""

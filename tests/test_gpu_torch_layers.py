@@ -25,6 +25,7 @@ def test_argument_checks_need_no_gpu():
                                 torch.zeros(3, dtype=torch.float32))
     with pytest.raises(ValueError):
         L.config_to_nve_config({"default_embedding": [0, 0]})
+    assert L.config_to_nve_config({"default_embedding": []}).default_embedding == []
     assert L.config_to_nve_config({"kernel_mode": 2, "default_row_index": 5}).default_row_index == 5
     assert L.torch_type_to_nve_type(torch.float16) == pynve.DataType_t.Float16
 

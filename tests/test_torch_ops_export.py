@@ -142,7 +142,8 @@ def test_ops_give_the_rows_of_the_plain_path(torch_cuda, layer_type, dtype_name)
     keys = torch.from_numpy(rng.integers(0, rows, 640)).cuda()
     cuts = np.sort(rng.integers(0, 641, 127))          # 128 bags, some of them empty
     offsets = torch.from_numpy(np.concatenate([[0], cuts, [640]])).cuda()
-    weights = torch.from_numpy(rng.integers(1, 5, 640).astype(np.float32)).cuda()
+    # the dense layer wants weights of the rows' own type (a rule of the reference layer)
+    weights = torch.from_numpy(rng.integers(1, 5, 640).astype(np.float32)).cuda().to(dtype)
     marker, tag = layer.marker_tensor, layer.dtype_tag
 
     got = torch.ops.nve_ops.embedding_lookup(marker, keys, dim, tag)
@@ -153,7 +154,8 @@ def test_ops_give_the_rows_of_the_plain_path(torch_cuda, layer_type, dtype_name)
         want = torch.empty_like(got)
         layer.emb_layer.lookup_with_pooling(keys.numel(), keys.data_ptr(), want.data_ptr(), int(pool),
                                             offsets.numel(), offsets.data_ptr(),
-                                            int(pynve.DataType_t.Float32), wts.data_ptr() if wts is not None else 0,
+                                            tag if wts is not None else int(pynve.DataType_t.Float32),
+                                            wts.data_ptr() if wts is not None else 0,
                                             torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
         assert torch.equal(got, want), pool
