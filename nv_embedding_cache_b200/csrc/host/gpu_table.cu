@@ -3,16 +3,22 @@
 //
 // Mirrors the contract of the reference's GpuTable<KeyType> (src/gpu_table.cu:194-1104,
 // include/gpu_table.hpp:44-74) with its device-side modify policy (modify_on_gpu = true, the
-// pynve default).  Differences in mechanism, not in results:
+// pynve default) and its host-side one (modify_on_gpu = false: tags, counters and the replacement
+// decisions live on the host, see HostPolicy below).  Differences in mechanism, not in results:
 //   * no host synchronisation inside insert / update / erase: lookups enqueued after a modify wait
 //     (on the device) for that modify's tag invalidation, and the modify waits (on the device) for
 //     every lookup enqueued before it, which gives the reference's invalidate -> drain -> copy ->
 //     commit guarantee without stalling the calling thread;
 //   * the backing-table write-through of update / update_accumulate always runs as a GPU kernel.
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 #include <shared_mutex>
 #include <random>
+#include <type_traits>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
 
 #include "../kernels/cache_modify.cuh"
 #include "layers.hpp"
@@ -28,6 +34,152 @@ constexpr float kDecayRate = 0.95f;  // reference include/ecache/ec_set_associat
 
 inline uint64_t align16(uint64_t x) { return (x + 15u) & ~uint64_t{15}; }
 
+// ---- host-side replacement policy (modify_on_gpu = 0) ------------------------------------------
+// The contract of the reference's CacheSAHostModify (include/ecache/ec_set_associative_host_modify.h
+// :217-316 insert, :318-383 update / update_accumulate, :134-176 invalidate) fed by its host
+// histogram (include/ecache/embed_cache.h:189-256): tags, replacement counters and per-set decay
+// clocks are mirrored on the host; a modification walks the mirror on the calling thread, in batch
+// order, and hands the device a list of (source row, cache line, tag) to apply.  The decisions are
+// sequential by definition (a key sees the counters the keys before it left), which is what
+// distinguishes this policy from the device one.
+struct HostPolicy {
+  std::vector<int64_t> tags;      // [sets * 8] tag (key / sets) or the sentinel
+  std::vector<float> counters;    // [sets * 8]
+  std::vector<int64_t> set_ts;    // [sets] insert number that last aged the set
+  int64_t global_ts = 0;
+  int64_t sentinel = -1;
+  uint32_t sets = 0;
+
+  void reset(size_t lines, uint32_t num_sets, int64_t sentinel_key) {
+    sets = num_sets;
+    sentinel = sentinel_key;
+    tags.assign(lines, sentinel_key);
+    counters.assign(lines, 0.f);
+    set_ts.assign(num_sets, 0);
+    global_ts = 0;
+  }
+
+  // Arithmetic in the key's own width, through its unsigned counterpart, as the device probe does.
+  template <typename KeyT>
+  struct Math {
+    using U = typename std::make_unsigned<KeyT>::type;
+    static uint32_t set_of(KeyT key, uint32_t sets) { return static_cast<uint32_t>(static_cast<U>(key) % sets); }
+    static KeyT tag_of(KeyT key, uint32_t sets) { return static_cast<KeyT>(static_cast<U>(key) / sets); }
+    static KeyT key_of(KeyT tag, uint32_t set, uint32_t sets) {
+      return static_cast<KeyT>(static_cast<U>(static_cast<U>(tag) * sets + set));
+    }
+  };
+
+  // Way of `set` whose stored tag spells `key`, lowest first, or -1.
+  template <typename KeyT>
+  int way_of(KeyT key, uint32_t set) const {
+    const int64_t* ways = tags.data() + size_t(set) * 8;
+    for (int j = 0; j < 8; j++) {
+      if (Math<KeyT>::key_of(static_cast<KeyT>(ways[j]), set, sets) == key) return j;
+    }
+    return -1;
+  }
+
+  // Distinct keys of the batch in order of first appearance, sorted by falling count (std::sort on
+  // the count alone, as the reference does: the order among equal counts is whatever that sort
+  // leaves, and is the same here because it is the same call on the same sequence), priority =
+  // count / batch size.  `first[i]` is the batch position of the key's first appearance.
+  template <typename KeyT>
+  struct Bin {
+    KeyT key;
+    float count;
+    int64_t first;
+  };
+  template <typename KeyT>
+  static std::vector<Bin<KeyT>> histogram(const KeyT* keys, int64_t n) {
+    std::vector<Bin<KeyT>> bins;
+    bins.reserve(size_t(n));
+    std::unordered_map<KeyT, size_t> where;
+    where.reserve(size_t(n));
+    for (int64_t i = 0; i < n; i++) {
+      auto it = where.find(keys[i]);
+      if (it == where.end()) {
+        where.emplace(keys[i], bins.size());
+        bins.push_back({keys[i], 1.f, i});
+      } else {
+        bins[it->second].count += 1.f;
+      }
+    }
+    std::sort(bins.begin(), bins.end(), [](const Bin<KeyT>& a, const Bin<KeyT>& b) { return a.count > b.count; });
+    return bins;
+  }
+
+  // Replacement decisions of one insert.  A resident key has its counter raised by its priority; a
+  // key that is not resident takes the way with the smallest counter unless that counter exceeds
+  // the key's priority or the way was already given away in this call; at most `max_entries` lines
+  // change per call.  A set's counters are aged by decay^(inserts since it was last touched) when
+  // the call first touches it.
+  template <typename KeyT>
+  void select_inserts(const std::vector<Bin<KeyT>>& bins, int64_t batch, float decay, int64_t max_entries,
+                      const uint8_t* src_base, int64_t src_stride, bool src_by_key,
+                      std::vector<ModifyEntry>& out) {
+    const int64_t now = ++global_ts;
+    std::unordered_set<uint64_t> taken;
+    out.clear();
+    for (size_t b = 0; b < bins.size() && int64_t(taken.size()) < max_entries; b++) {
+      const KeyT key = bins[b].key;
+      const float priority = bins[b].count / static_cast<float>(batch);
+      const uint32_t set = Math<KeyT>::set_of(key, sets);
+      float* sc = counters.data() + size_t(set) * 8;
+      if (set_ts[set] != now) {
+        const float factor = static_cast<float>(
+            std::pow(static_cast<double>(decay), static_cast<double>(now - set_ts[set])));
+        for (int j = 0; j < 8; j++) sc[j] *= factor;
+        set_ts[set] = now;
+      }
+      const int hit = way_of<KeyT>(key, set);
+      if (hit >= 0) {
+        sc[hit] += priority;
+        continue;
+      }
+      float* victim = std::min_element(sc, sc + 8);
+      if (*victim > priority) continue;
+      const uint64_t line = uint64_t(set) * 8 + uint64_t(victim - sc);
+      if (!taken.insert(line).second) continue;
+      *victim = priority;
+      const KeyT tag = Math<KeyT>::tag_of(key, sets);
+      tags[line] = static_cast<int64_t>(tag);
+      const int64_t row = src_by_key ? static_cast<int64_t>(key) : bins[b].first;
+      out.push_back({src_base + row * src_stride, line, static_cast<int64_t>(tag)});
+    }
+  }
+
+  // One entry per key that is resident (its first matching way), at most `max_entries`.
+  template <typename KeyT>
+  void find_resident(const KeyT* keys, int64_t n, const uint8_t* values, int64_t stride, int64_t max_entries,
+                     std::vector<ModifyEntry>& out) const {
+    out.clear();
+    for (int64_t i = 0; i < n && int64_t(out.size()) < max_entries; i++) {
+      const uint32_t set = Math<KeyT>::set_of(keys[i], sets);
+      const int way = way_of<KeyT>(keys[i], set);
+      if (way < 0) continue;
+      const uint64_t line = uint64_t(set) * 8 + uint64_t(way);
+      out.push_back({values + i * stride, line, tags[line]});
+    }
+  }
+
+  // Every way that holds one of the keys is emptied.
+  template <typename KeyT>
+  void invalidate(const KeyT* keys, int64_t n, std::vector<ModifyEntry>& out) {
+    out.clear();
+    for (int64_t i = 0; i < n; i++) {
+      const uint32_t set = Math<KeyT>::set_of(keys[i], sets);
+      int64_t* ways = tags.data() + size_t(set) * 8;
+      for (int j = 0; j < 8; j++) {
+        if (Math<KeyT>::key_of(static_cast<KeyT>(ways[j]), set, sets) == keys[i]) {
+          ways[j] = sentinel;
+          out.push_back({nullptr, uint64_t(set) * 8 + uint64_t(j), sentinel});
+        }
+      }
+    }
+  }
+};
+
 class GpuTable : public Table {
  public:
   GpuTable(const nve_gpu_table_config_t& cfg, nve_key_type_t key_type)
@@ -36,12 +188,6 @@ class GpuTable : public Table {
                    "Invalid cache row size (must divide by 2)");
     NVE_B200_CHECK(cfg.uvm_table == nullptr || cfg.uvm_num_rows > 0,
                    "uvm_num_rows must be set to the number of rows in uvm_table");
-    if (!cfg.modify_on_gpu) {
-      throw NotImplemented("host-side cache modification (modify_on_gpu = 0) is not provided");
-    }
-    if (cfg.data_storage_on_host) {
-      throw NotImplemented("cache data storage on host is not provided");
-    }
     if (cfg.kernel_mode_type == NVE_KERNEL_PIPELINE_GATHER && cfg.kernel_mode_value != 0) {
       // the value is the address of the schedule's parameters (as in the reference, where it points
       // at a GatherKernelPipelineParams); they are read once, here
@@ -51,9 +197,11 @@ class GpuTable : public Table {
     // sets that fit: tags + rows + counters per set, each rounded up to 16 bytes
     // (reference include/ecache/ec_set_associative.h:666-685, device-modify counters
     //  include/ecache/ec_set_associative_device_modify.cuh:472-474)
+    // With the host-side policy the counters live on the host and take no share of cache_size
+    // (reference get_counter_size_per_set, include/ecache/ec_set_associative.h:672-681).
     const uint64_t per_set = align16(uint64_t(kWays) * kb) +
                              align16(uint64_t(kWays) * cfg.row_size_in_bytes) +
-                             align16(uint64_t(kWays) * sizeof(float));
+                             (cfg.modify_on_gpu ? align16(uint64_t(kWays) * sizeof(float)) : 0);
     const uint64_t sets = cfg.cache_size / per_set;
     NVE_B200_CHECK(sets > 0, "Failed to Init cache: memory allocated to cache too small");
     NVE_B200_CHECK(sets <= 0xffffffffull, "cache has too many sets");
@@ -64,13 +212,23 @@ class GpuTable : public Table {
     ScopedDevice sd(cfg_.device_id);
     const size_t lines = size_t(num_sets_) * kWays;
     NVE_B200_CUDA(cudaMalloc(&cs_.tags, lines * kb));
-    NVE_B200_CUDA(cudaMalloc(&cs_.data, lines * size_t(cfg.row_size_in_bytes)));
+    if (cfg.data_storage_on_host) {
+      // rows of the cache in pinned host memory that the GPU maps; tags and counters stay in HBM
+      // (reference CacheConfig::allocate_data_on_host, include/ecache/ec_set_associative.h)
+      void* rows = nullptr;
+      NVE_B200_CUDA(cudaHostAlloc(&rows, lines * size_t(cfg.row_size_in_bytes),
+                                  cudaHostAllocMapped | cudaHostAllocPortable));
+      cs_.data = static_cast<decltype(cs_.data)>(rows);
+    } else {
+      NVE_B200_CUDA(cudaMalloc(&cs_.data, lines * size_t(cfg.row_size_in_bytes)));
+    }
     NVE_B200_CUDA(cudaMalloc(&cs_.counters, lines * sizeof(float)));
     NVE_B200_CUDA(cudaMalloc(&cs_.set_ts, size_t(num_sets_) * sizeof(int64_t)));
     cs_.row_bytes = cfg.row_size_in_bytes;
     cs_.sentinel = cfg.invalid_key;
     cache_clear(cs_, key_type_, num_sets_, nullptr);
     NVE_B200_CUDA(cudaStreamSynchronize(nullptr));
+    if (!cfg.modify_on_gpu) host_.reset(lines, num_sets_, cfg.invalid_key);
     NVE_B200_CUDA(cudaEventCreateWithFlags(&invalidate_done_, cudaEventDisableTiming));
     NVE_B200_CUDA(cudaEventCreateWithFlags(&modify_done_, cudaEventDisableTiming));
     contexts_ = std::make_shared<ContextRegistry>();
@@ -82,7 +240,8 @@ class GpuTable : public Table {
     (void)cudaSetDevice(cfg_.device_id);
     (void)cudaDeviceSynchronize();
     (void)cudaFree(cs_.tags);
-    (void)cudaFree(cs_.data);
+    if (cfg_.data_storage_on_host) (void)cudaFreeHost(cs_.data);
+    else (void)cudaFree(cs_.data);
     (void)cudaFree(cs_.counters);
     (void)cudaFree(cs_.set_ts);
     if (invalidate_done_) (void)cudaEventDestroy(invalidate_done_);
@@ -288,6 +447,7 @@ class GpuTable : public Table {
     contexts_->order_after_lookups(s);
     cache_clear(cs_, key_type_, num_sets_, s);
     global_ts_ = 0;
+    if (!cfg_.modify_on_gpu) host_.reset(size_t(num_sets_) * kWays, num_sets_, cfg_.invalid_key);
     publish_invalidate(s);
   }
 
@@ -324,6 +484,10 @@ class GpuTable : public Table {
                    int64_t value_stride, bool from_table, int64_t default_row,
                    cudaEvent_t keys_ready) {
     ScopedDevice sd(cfg_.device_id);
+    if (!cfg_.modify_on_gpu) {
+      host_insert(ctx, n, keys, values, value_stride, from_table, default_row, keys_ready);
+      return;
+    }
     ExecutionContext& c = *ctx;
     const cudaStream_t s = c.modify_stream();
     // staging buffers of their own: a lookup of the same context may still be reading "keys"
@@ -352,6 +516,10 @@ class GpuTable : public Table {
   void modify_resident(context_ptr_t& ctx, int64_t n, const void* keys, const void* values,
                        int64_t stride, int mode, nve_data_type_t dtype) {
     ScopedDevice sd(cfg_.device_id);
+    if (!cfg_.modify_on_gpu) {
+      host_modify_resident(ctx, n, keys, values, stride, mode, dtype);
+      return;
+    }
     ExecutionContext& c = *ctx;
     const cudaStream_t s = c.modify_stream();
     const Staged d_keys = stage_in(c, "modify_keys", keys, size_t(n) * key_bytes(key_type_), true, s);
@@ -388,6 +556,124 @@ class GpuTable : public Table {
     }
   }
 
+  // ---- host-side policy: the mirror decides, the device applies --------------------------------
+  // Keys on the host, where the policy reads them (a device buffer is copied over first, which
+  // waits for the modify stream, as the reference's access_buffer(cudaMemoryTypeHost) does).
+  const void* keys_on_host(ExecutionContext& c, const void* keys, int64_t n, cudaStream_t s,
+                           cudaEvent_t keys_ready) {
+    if (residency_of(keys) != Residency::Device) return keys;
+    const size_t bytes = size_t(n) * key_bytes(key_type_);
+    void* h = c.scratch("modify_keys_host", bytes, true);
+    if (keys_ready != nullptr) NVE_B200_CUDA(cudaStreamWaitEvent(s, keys_ready, 0));
+    NVE_B200_CUDA(cudaMemcpyAsync(h, keys, bytes, cudaMemcpyDeviceToHost, s));
+    NVE_B200_CUDA(cudaStreamSynchronize(s));
+    return h;
+  }
+
+  // Uploads the host's entry list and applies it: mode < 0 empties the lines, 0 writes rows and
+  // commits tags, 1 / 2 add fp32 / fp16 rows.  Waits until the list is on the device; the
+  // modification itself stays asynchronous on `s`.
+  void host_apply(ExecutionContext& c, cudaStream_t s, const std::vector<ModifyEntry>& list, int mode,
+                  int64_t src_stride, const uint8_t* src_base) {
+    if (list.empty()) return;
+    const uint32_t cap = static_cast<uint32_t>(list.size());
+    auto* h_entries = static_cast<ModifyEntry*>(c.scratch("host_entries", size_t(cap) * sizeof(ModifyEntry) + 64, true));
+    auto* h_count = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(h_entries) + size_t(cap) * sizeof(ModifyEntry));
+    std::copy(list.begin(), list.end(), h_entries);
+    *h_count = cap;
+    auto* entries = static_cast<ModifyEntry*>(c.scratch("cache_entries", size_t(cap) * sizeof(ModifyEntry), false));
+    auto* count = static_cast<uint32_t*>(c.scratch("cache_entry_count", 256, false));
+    NVE_B200_CUDA(cudaStreamWaitEvent(s, modify_done_, 0));
+    NVE_B200_CUDA(cudaMemcpyAsync(entries, h_entries, size_t(cap) * sizeof(ModifyEntry), cudaMemcpyHostToDevice, s));
+    NVE_B200_CUDA(cudaMemcpyAsync(count, h_count, sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    // the pinned staging buffer is free again once the list is on the device (the reference waits
+    // for its modify stream at the same point, ec_set_associative_host_modify.h:452-455)
+    NVE_B200_CUDA(cudaStreamSynchronize(s));
+    if (mode < 0) {
+      cache_write_tags(cs_, key_type_, entries, count, cap, /*invalidate=*/true, s);
+      publish_invalidate(s);
+      NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
+    } else {
+      commit_entries(s, entries, count, cap, mode, src_stride, src_base);
+    }
+  }
+
+  void host_insert(context_ptr_t& ctx, int64_t n, const void* keys, const void* values, int64_t value_stride,
+                   bool from_table, int64_t default_row, cudaEvent_t keys_ready) {
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.modify_stream();
+    const void* h_keys = keys_on_host(c, keys, n, s, keys_ready);
+    const uint8_t* src = static_cast<const uint8_t*>(cfg_.uvm_table);
+    if (!from_table) {
+      src = static_cast<const uint8_t*>(
+          stage_in(c, "modify_values", values, size_t(n) * value_stride, true, s).device);
+    }
+    std::unique_lock<std::shared_mutex> lock(flow_mu_);
+    std::vector<ModifyEntry> list;
+    const int64_t max_entries = cfg_.max_modify_size > 0 ? cfg_.max_modify_size : n;
+    auto run = [&](auto key_tag) {
+      using KeyT = decltype(key_tag);
+      const KeyT* k = static_cast<const KeyT*>(h_keys);
+      std::vector<KeyT> clean;
+      if (from_table) {
+        // keys that are no rows of the backing table: the default row, or nothing
+        clean.reserve(size_t(n));
+        for (int64_t i = 0; i < n; i++) {
+          const bool row = k[i] >= 0 && static_cast<int64_t>(k[i]) < cfg_.uvm_num_rows;
+          if (row) clean.push_back(k[i]);
+          else if (default_row >= 0 && default_row < cfg_.uvm_num_rows) clean.push_back(static_cast<KeyT>(default_row));
+        }
+        k = clean.data();
+      }
+      const int64_t batch = from_table ? int64_t(clean.size()) : n;
+      if (batch == 0) return;
+      const auto bins = HostPolicy::histogram<KeyT>(k, batch);
+      host_.select_inserts<KeyT>(bins, batch, kDecayRate, max_entries, src, value_stride, from_table, list);
+    };
+    if (key_type_ == NVE_KEY_INT64) run(int64_t{});
+    else run(int32_t{});
+    host_apply(c, s, list, /*mode=*/0, value_stride, src);
+  }
+
+  void host_modify_resident(context_ptr_t& ctx, int64_t n, const void* keys, const void* values,
+                            int64_t stride, int mode, nve_data_type_t dtype) {
+    ExecutionContext& c = *ctx;
+    const cudaStream_t s = c.modify_stream();
+    const void* h_keys = keys_on_host(c, keys, n, s, nullptr);
+    const uint8_t* d_vals = nullptr;
+    if (values) {
+      d_vals = static_cast<const uint8_t*>(
+          stage_in(c, "modify_values", values, size_t(n) * stride, true, s).device);
+    }
+    std::unique_lock<std::shared_mutex> lock(flow_mu_);
+    std::vector<ModifyEntry> list;
+    // an update longer than max_modify_size goes in parts of that size (reference src/gpu_table.cu:606-628)
+    const int64_t part = (mode >= 0 && cfg_.max_modify_size > 0) ? cfg_.max_modify_size : n;
+    for (int64_t start = 0; start < n; start += part) {
+      const int64_t len = std::min(part, n - start);
+      auto run = [&](auto key_tag) {
+        using KeyT = decltype(key_tag);
+        const KeyT* k = static_cast<const KeyT*>(h_keys) + start;
+        if (mode < 0) host_.invalidate<KeyT>(k, len, list);
+        else host_.find_resident<KeyT>(k, len, d_vals + start * stride, stride, len, list);
+      };
+      if (key_type_ == NVE_KEY_INT64) run(int64_t{});
+      else run(int32_t{});
+      host_apply(c, s, list, mode, stride, d_vals);
+    }
+    if (mode >= 0 && cfg_.uvm_table && !cfg_.disable_uvm_update) {
+      // write-through to the backing table, by a kernel: it wants the keys on the device
+      const Staged d_keys = stage_in(c, "modify_keys", h_keys, size_t(n) * key_bytes(key_type_), true, s);
+      contexts_->order_after_lookups(s);
+      update_rows(cfg_.uvm_table, cfg_.uvm_num_rows, cfg_.row_size_in_bytes, dtype,
+                  cfg_.row_size_in_bytes, key_type_, d_keys.device, n, d_vals, stride, mode != 0,
+                  /*keys_unique=*/false, s);
+      NVE_B200_CUDA(cudaEventRecord(modify_done_, s));
+      contexts_->lookups_wait_event(modify_done_);
+      if (d_keys.staged) NVE_B200_CUDA(cudaStreamSynchronize(s));   // h_keys may be the caller's buffer
+    }
+  }
+
   // invalidate victims -> drain lookups in flight -> write rows -> commit tags
   void commit_entries(cudaStream_t s, const ModifyEntry* entries, const uint32_t* count,
                       uint32_t cap, int mode, int64_t src_stride, const uint8_t* src_base) {
@@ -417,6 +703,7 @@ class GpuTable : public Table {
   cudaEvent_t invalidate_done_ = nullptr;
   cudaEvent_t modify_done_ = nullptr;
   int64_t global_ts_ = 0;
+  HostPolicy host_;             // modify_on_gpu = 0 only
   nve_b200_pipeline_params_t pipeline_{1024, 16};   // reference defaults (src/gpu_table.cu:343-347)
   PipelineResources pipeline_res_;
 

@@ -131,8 +131,11 @@ class GpuTable:
                  key_type: int = capi.KEY_INT64, device_id: int = 0, uvm_table=None,
                  uvm_num_rows: int = 0, count_misses: bool = True,
                  max_modify_size: int = 1 << 20, invalid_key: int = -1,
-                 kernel_mode_type: int = 0, kernel_mode_value: int = 0):
+                 kernel_mode_type: int = 0, kernel_mode_value: int = 0,
+                 modify_on_gpu: bool = True, data_storage_on_host: bool = False):
         cfg = capi.lib.nve_gpu_table_config_default()
+        cfg.modify_on_gpu = int(modify_on_gpu)            # False: replacement decided on the host
+        cfg.data_storage_on_host = int(data_storage_on_host)   # True: cached rows in pinned host memory
         cfg.kernel_mode_type = kernel_mode_type     # 0 dynamic, 1 fused lookup, 2 sort-gather, 3 pipeline
         cfg.kernel_mode_value = kernel_mode_value
         cfg.device_id = device_id

@@ -397,6 +397,15 @@ class ReferenceGpu:
             "refgpu_cache_update_accumulate": [_vp, _vp, _i64, _vp, _i64, _i32],
             "refgpu_cache_invalidate": [_vp, _vp, _i64],
             "refgpu_cache_clear": [_vp],
+            "refgpu_hostcache_create": [pp, _i64, _i64, _i64, f32, _i64],
+            "refgpu_hostcache_destroy": [_vp],
+            "refgpu_hostcache_view": [_vp, C.POINTER(_i64), pp, pp],
+            "refgpu_hostcache_insert": [_vp, _vp, _i64, _vp, _i64, _i32],
+            "refgpu_hostcache_update": [_vp, _vp, _i64, _vp, _i64],
+            "refgpu_hostcache_update_accumulate": [_vp, _vp, _i64, _vp, _i64, _i32],
+            "refgpu_hostcache_invalidate": [_vp, _vp, _i64],
+            "refgpu_hostcache_clear": [_vp],
+            "refgpu_hostcache_lookup_mask": [_vp, _vp, _i64, _vp, _i64, _vp],
             "refgpu_deduper_create": [pp, _i32, _i64],
             "refgpu_deduper_destroy": [_vp],
             "refgpu_deduper_dedup": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32],
@@ -421,6 +430,9 @@ class ReferenceGpu:
     # ---- cache
     def cache(self, cache_bytes, row_bytes, sentinel=-1, decay=0.95, max_modify=1 << 20):
         return RefGpuCache(self, cache_bytes, row_bytes, sentinel, decay, max_modify)
+
+    def host_cache(self, cache_bytes, row_bytes, sentinel=-1, decay=0.95, max_modify=1 << 20):
+        return RefGpuHostCache(self, cache_bytes, row_bytes, sentinel, decay, max_modify)
 
     def update_accumulate_table(self, src_ptr, keys_ptr, table_ptr, width, n, num_rows, warmup=0, iters=0):
         """table[keys[i]] += src[i] (fp32 rows); returns mean ms per call when iters > 0."""
@@ -519,6 +531,48 @@ class RefGpuCache:
 
     def clear(self):
         self.ref.check(self.ref.lib.refgpu_cache_clear(self.h))
+
+
+class RefGpuHostCache:
+    """The reference cache with its host-side modify policy (CacheSAHostModify<int64, int64>): keys of
+    the modifying calls are HOST addresses, rows are device addresses."""
+
+    def __init__(self, ref: ReferenceGpu, cache_bytes, row_bytes, sentinel, decay, max_modify):
+        self.ref = ref
+        self.h = _vp()
+        ref.check(ref.lib.refgpu_hostcache_create(C.byref(self.h), cache_bytes, row_bytes, sentinel, decay,
+                                                  max_modify))
+        self.row_bytes = row_bytes
+
+    def close(self):
+        if self.h:
+            self.ref.check(self.ref.lib.refgpu_hostcache_destroy(self.h))
+            self.h = _vp()
+
+    def view(self):
+        n, tags, rows = _i64(0), _vp(), _vp()
+        self.ref.check(self.ref.lib.refgpu_hostcache_view(self.h, C.byref(n), C.byref(tags), C.byref(rows)))
+        return n.value, tags.value, rows.value
+
+    def insert(self, host_keys_ptr, n, values_ptr, stride, linear=False):
+        self.ref.check(self.ref.lib.refgpu_hostcache_insert(self.h, host_keys_ptr, n, values_ptr, stride,
+                                                            1 if linear else 0))
+
+    def update(self, host_keys_ptr, n, values_ptr, stride):
+        self.ref.check(self.ref.lib.refgpu_hostcache_update(self.h, host_keys_ptr, n, values_ptr, stride))
+
+    def update_accumulate(self, host_keys_ptr, n, values_ptr, stride, fp16=False):
+        self.ref.check(self.ref.lib.refgpu_hostcache_update_accumulate(self.h, host_keys_ptr, n, values_ptr, stride,
+                                                                       1 if fp16 else 0))
+
+    def invalidate(self, host_keys_ptr, n):
+        self.ref.check(self.ref.lib.refgpu_hostcache_invalidate(self.h, host_keys_ptr, n))
+
+    def clear(self):
+        self.ref.check(self.ref.lib.refgpu_hostcache_clear(self.h))
+
+    def lookup_mask(self, keys_ptr, n, out_ptr, stride, mask_ptr):
+        self.ref.check(self.ref.lib.refgpu_hostcache_lookup_mask(self.h, keys_ptr, n, out_ptr, stride, mask_ptr))
 
 
 class RefGpuDeduper:

@@ -6,6 +6,9 @@
 // Reference entry points used:
 //   include/ecache/ec_set_associative_device_modify.cuh   CacheSADeviceModify (insert, update,
 //                                                         update_accumulate, invalidate, clear)
+//   include/ecache/ec_set_associative_host_modify.h       CacheSAHostModify, fed by DefaultHistogram
+//                                                         (include/ecache/embed_cache.h), in the call
+//                                                         order of src/gpu_table.cu:468-490
 //   include/ecache/ec_set_associative.h                   EmbedCacheSA::lookup (hit mask / table)
 //   cuda_ops/gather_keys_data_ptrs.cuh                    DefaultGPUHistogram (src/gpu_table.cu:443-467
 //                                                         shows the call order reproduced below)
@@ -364,6 +367,128 @@ int refgpu_cache_clear(void* h) {
   return guarded([&] {
     auto* c = static_cast<RefCache*>(h);
     ec(c->cache->clear_cache(0), "clear");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+// ---- cache with the host-side modify policy -------------------------------------------------
+// Keys are host pointers here (the policy walks them on the CPU); rows are device pointers.
+namespace {
+using HostCache = nve::CacheSAHostModify<Key, Key>;
+struct RefHostCache {
+  nve::allocator_ptr_t allocator;
+  nve::Logger logger;
+  std::unique_ptr<HostCache> cache;
+  nve::PerformanceMetric misses;
+  nve::LookupContextHandle lookup;
+  nve::ModifyContextHandle modify;
+};
+}  // namespace
+
+int refgpu_hostcache_create(void** out, int64_t cache_bytes, int64_t row_bytes, int64_t sentinel, float decay,
+                            int64_t max_modify) {
+  return guarded([&] {
+    auto c = std::make_unique<RefHostCache>();
+    c->allocator = nve::GetDefaultAllocator();
+    HostCache::CacheConfig cfg;
+    cfg.cache_sz_in_bytes = static_cast<size_t>(cache_bytes);
+    cfg.embed_width_in_bytes = static_cast<uint64_t>(row_bytes);
+    cfg.num_tables = 1;
+    cfg.decay_rate = decay;
+    cfg.sentinel_key = sentinel;
+    c->cache = std::make_unique<HostCache>(c->allocator.get(), &c->logger, cfg);
+    ec(c->cache->init(), "init");
+    ec(c->cache->performance_metric_create(c->misses, nve::MERTIC_COUNT_MISSES), "metric");
+    ec(c->cache->lookup_context_create(c->lookup, &c->misses, 1), "lookup context");
+    ec(c->cache->modify_context_create(c->modify, static_cast<uint32_t>(max_modify)), "modify context");
+    *out = c.release();
+  });
+}
+
+int refgpu_hostcache_destroy(void* h) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    (void)c->cache->lookup_context_destroy(c->lookup);
+    (void)c->cache->modify_context_destroy(c->modify);
+    (void)c->cache->performance_metric_destroy(c->misses);
+    delete c;
+  });
+}
+
+int refgpu_hostcache_view(void* h, int64_t* num_sets, const void** d_tags, const void** d_rows) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    const auto data = c->cache->get_cache_data(c->lookup);
+    *num_sets = static_cast<int64_t>(data.num_sets);
+    *d_tags = data.tags_ptr;
+    *d_rows = data.cache_ptr;
+  });
+}
+
+// linear != 0: rows are read from a table indexed by key (insert_from_uvm); else row i belongs to key i
+int refgpu_hostcache_insert(void* h, const int64_t* h_keys, int64_t n, const void* d_values, int64_t stride,
+                            int linear) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    nve::DefaultHistogram<Key> hist(h_keys, static_cast<size_t>(n), static_cast<const int8_t*>(d_values),
+                                    static_cast<size_t>(stride), linear != 0);
+    nve::DefaultECEvent sync{std::unordered_set<cudaStream_t>()};
+    ec(c->cache->insert(c->modify, hist.get_keys(), hist.get_priority(), hist.get_data(), hist.get_num_bins(), 0,
+                        &sync, 0),
+       "insert");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+int refgpu_hostcache_update(void* h, const int64_t* h_keys, int64_t n, const void* d_values, int64_t stride) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    nve::DefaultECEvent sync{std::unordered_set<cudaStream_t>()};
+    ec(c->cache->update(c->modify, h_keys, static_cast<const int8_t*>(d_values), stride, static_cast<size_t>(n),
+                        0, &sync, 0),
+       "update");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+int refgpu_hostcache_update_accumulate(void* h, const int64_t* h_keys, int64_t n, const void* d_values,
+                                       int64_t stride, int fmt) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    nve::DefaultECEvent sync{std::unordered_set<cudaStream_t>()};
+    const auto f = fmt == 0 ? nve::DATATYPE_FP32 : nve::DATATYPE_FP16;
+    ec(c->cache->update_accumulate(c->modify, h_keys, static_cast<const int8_t*>(d_values), stride,
+                                   static_cast<size_t>(n), 0, f, f, &sync, 0),
+       "update_accumulate");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+int refgpu_hostcache_invalidate(void* h, const int64_t* h_keys, int64_t n) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    nve::DefaultECEvent sync{std::unordered_set<cudaStream_t>()};
+    ec(c->cache->invalidate(c->modify, h_keys, static_cast<size_t>(n), 0, &sync, 0), "invalidate");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+int refgpu_hostcache_clear(void* h) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    ec(c->cache->clear_cache(0), "clear");
+    ck(cudaDeviceSynchronize(), "sync");
+  });
+}
+
+int refgpu_hostcache_lookup_mask(void* h, const int64_t* d_keys, int64_t n, void* d_values, int64_t stride,
+                                 uint64_t* d_hit_mask) {
+  return guarded([&] {
+    auto* c = static_cast<RefHostCache*>(h);
+    ck(cudaMemsetAsync(d_hit_mask, 0, static_cast<size_t>((n + 63) / 64) * 8, 0), "memset");
+    ec(c->cache->lookup(c->lookup, d_keys, static_cast<size_t>(n), static_cast<int8_t*>(d_values), d_hit_mask, 0,
+                        static_cast<size_t>(stride), 0),
+       "lookup(hit mask)");
     ck(cudaDeviceSynchronize(), "sync");
   });
 }

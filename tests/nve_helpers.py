@@ -126,14 +126,16 @@ class CacheTable:
     """nve_gpu_table_create + one execution context; state readers for parity checks."""
 
     def __init__(self, cache_bytes, row_bytes, value_dtype="f16", key_dtype=np.int64, backing=None,
-                 backing_rows=0, max_modify=1 << 20, sentinel=-1):
+                 backing_rows=0, max_modify=1 << 20, sentinel=-1, modify_on_gpu=True,
+                 data_storage_on_host=False):
         from nv_embedding_cache_b200.layers import GpuTable
         self.key_dtype = np.dtype(key_dtype)
         self.row_bytes = row_bytes
         kt = capi.KEY_INT64 if self.key_dtype.itemsize == 8 else capi.KEY_INT32
         self.table = GpuTable(cache_bytes, row_bytes, DT[value_dtype], key_type=kt, uvm_table=backing,
                               uvm_num_rows=backing_rows, max_modify_size=max_modify,
-                              invalid_key=sentinel)
+                              invalid_key=sentinel, modify_on_gpu=modify_on_gpu,
+                              data_storage_on_host=data_storage_on_host)
         self.ctx = self.table.create_execution_context()
         view = capi.CacheData()
         capi.check(capi.lib.nve_b200_gpu_table_get_cache_data(self.table.handle, self.ctx.handle,

@@ -5,7 +5,8 @@ gradient de-duplication and the pooled find_and_combine kernel.
 Integer state (tags per (set, way), hit masks, miss counts, unique keys, counts, offsets, inverse
 positions, chunk maps) and copied rows must be identical.  Floating-point sums must agree exactly
 where the reference adds in a fixed order and within 1e-5 relative (1e-6 for gradient sums) where
-it uses atomics or fused multiply-adds."""
+it uses atomics or fused multiply-adds.  The cache is compared under both of its modify policies:
+decided on the device (the default) and decided on the host (modify_on_gpu = 0)."""
 import ctypes as C
 
 import numpy as np
@@ -353,3 +354,157 @@ def test_pooled_lookup_int8(torch_cuda, reference_gpu):
     g, w = got.cpu().numpy(), want.cpu().numpy()
     assert np.max(np.abs(g - w) / np.maximum(np.abs(w), 1e-3)) <= 1e-5
     layer.close()
+
+
+# ---- the host-side modify policy (modify_on_gpu = 0) --------------------------------------------
+def per_set_host(row=ROW, key_bytes=8):
+    """Bytes of cache_size one set takes when the counters live on the host."""
+    return 8 * key_bytes + 8 * row
+
+
+@pytest.mark.parametrize("sets,steps", [(37, 6), (1, 3), (256, 6)])
+def test_host_policy_cache_state_after_inserts(torch_cuda, reference_gpu, sets, steps):
+    """The same Zipf batches as for the device policy, through the reference's CacheSAHostModify (fed
+    by its host histogram) and through this library's table with modify_on_gpu = 0: the policy is
+    sequential and deterministic, so the tags of every (set, way), the cached rows, hit masks and
+    looked-up rows must be identical after every insert."""
+    torch = torch_cuda
+    rows = 5000
+    t = byte_table(rows, seed=11)
+    cache_bytes = sets * per_set_host()
+    mine = CacheTable(cache_bytes, ROW, key_dtype=np.int64, modify_on_gpu=False)
+    ref = reference_gpu.host_cache(cache_bytes, ROW)
+    assert ref.view()[0] == mine.num_sets == sets
+    perm = dg.permutation(rows)
+    for step in range(steps):
+        n = [700, 64, 2000, 1, 333, 4096][step]
+        keys = dg.zipf_keys(n, rows, 1.2, 100 + step, perm)
+        vals = t[keys]
+        v_dev = to_dev(torch, vals)
+        mine.insert(keys, vals)
+        ref.insert(keys.ctypes.data, n, v_dev.data_ptr(), ROW)
+        rt = ref_tags(ref)
+        assert np.array_equal(mine.tags(), rt), f"library vs reference tags, insert {step}"
+        valid = rt != -1
+        assert valid.any()
+        assert np.array_equal(mine.data()[valid], ref_rows(ref, ROW)[valid])
+
+        probe = dg.zipf_keys(1000, rows, 1.2, 200 + step, perm)
+        p_dev = to_dev(torch, probe)
+        r_out = torch.zeros((1000, ROW), dtype=torch.uint8, device="cuda")
+        r_mask = torch.zeros(16, dtype=torch.int64, device="cuda")
+        ref.lookup_mask(p_dev.data_ptr(), 1000, r_out.data_ptr(), ROW, r_mask.data_ptr())
+        g_out, g_mask = np.zeros((1000, ROW), np.uint8), np.zeros(16, np.uint64)
+        mine.find(probe, g_out, g_mask)
+        assert np.array_equal(g_mask, r_mask.cpu().numpy().view(np.uint64))
+        assert np.array_equal(g_out, r_out.cpu().numpy())
+    mine.close()
+    ref.close()
+
+
+def test_host_policy_differs_from_device_policy_and_caps_an_insert(torch_cuda, reference_gpu):
+    """max_modify_size bounds the lines one insert may change under the host policy too, and a device
+    key buffer is accepted (copied to the host first)."""
+    torch = torch_cuda
+    rows = 4000
+    t = byte_table(rows, seed=5)
+    cache_bytes = 128 * per_set_host()
+    mine = CacheTable(cache_bytes, ROW, key_dtype=np.int64, modify_on_gpu=False, max_modify=50)
+    ref = reference_gpu.host_cache(cache_bytes, ROW, max_modify=50)
+    keys = dg.zipf_keys(3000, rows, 1.05, 9, dg.permutation(rows))
+    vals = t[keys]
+    v_dev, k_dev = to_dev(torch, vals), to_dev(torch, keys)
+    # keys handed over as a device buffer
+    mine.table.insert(mine.ctx, keys.size, k_dev.data_ptr(), ROW, ROW, v_dev.data_ptr())
+    mine.ctx.wait()
+    ref.insert(keys.ctypes.data, keys.size, v_dev.data_ptr(), ROW)
+    rt = ref_tags(ref)
+    assert (rt != -1).sum() == 50
+    assert np.array_equal(mine.tags(), rt)
+    mine.close()
+    ref.close()
+
+
+def test_host_policy_modify_ops(torch_cuda, reference_gpu):
+    """update, update_accumulate (fp32), invalidate and clear under the host policy; and an insert
+    whose rows come from a backing table indexed by key."""
+    torch = torch_cuda
+    rows, width = 3000, 16
+    t = dg.dyadic_table(rows, width, 3, np.float32)
+    t_dev = to_dev(torch, t)
+    cache_bytes = 64 * per_set_host()
+    mine = CacheTable(cache_bytes, ROW, value_dtype="f32", key_dtype=np.int64, modify_on_gpu=False,
+                      backing=t_dev.data_ptr(), backing_rows=rows)
+    ref = reference_gpu.host_cache(cache_bytes, ROW)
+    keys = dg.zipf_keys(1500, rows, 1.1, 7, dg.permutation(rows))
+    mine.insert_from_backing(keys)
+    ref.insert(keys.ctypes.data, keys.size, t_dev.data_ptr(), ROW, linear=True)
+    rt = ref_tags(ref)
+    assert np.array_equal(mine.tags(), rt)
+    valid = rt != -1
+    assert np.array_equal(mine.data()[valid], ref_rows(ref, ROW)[valid])
+
+    uk = np.unique(keys)[:400]
+    new = dg.dyadic_table(uk.size, width, 31, np.float32)
+    new_dev = to_dev(torch, new)
+    mine.update(uk, new.view(np.uint8).reshape(-1, ROW))
+    ref.update(uk.ctypes.data, uk.size, new_dev.data_ptr(), ROW)
+    assert np.array_equal(mine.data()[valid], ref_rows(ref, ROW)[valid])
+    # write-through: the backing table took the new rows as well
+    assert np.array_equal(t_dev.cpu().numpy()[uk], new)
+
+    upd = dg.dyadic_table(uk.size, width, 32, np.float32)
+    upd_dev = to_dev(torch, upd)
+    mine.update_accumulate(uk, upd, "f32")
+    ref.update_accumulate(uk.ctypes.data, uk.size, upd_dev.data_ptr(), ROW)
+    assert np.array_equal(mine.data()[valid], ref_rows(ref, ROW)[valid])
+    assert np.array_equal(t_dev.cpu().numpy()[uk], new + upd)
+
+    gone = np.unique(keys)[100:300]
+    mine.erase(gone)
+    ref.invalidate(gone.ctypes.data, gone.size)
+    assert np.array_equal(mine.tags(), ref_tags(ref))
+    # an insert after the erase sees the emptied ways (counters kept, as in the reference)
+    more = dg.zipf_keys(900, rows, 1.1, 8, dg.permutation(rows))
+    mine.insert_from_backing(more)
+    ref.insert(more.ctypes.data, more.size, t_dev.data_ptr(), ROW, linear=True)
+    assert np.array_equal(mine.tags(), ref_tags(ref))
+    mine.clear()
+    ref.clear()
+    assert np.array_equal(mine.tags(), ref_tags(ref))
+    assert (mine.tags() == -1).all()
+    mine.insert_from_backing(more)
+    ref.insert(more.ctypes.data, more.size, t_dev.data_ptr(), ROW, linear=True)
+    assert np.array_equal(mine.tags(), ref_tags(ref))
+    mine.close()
+    ref.close()
+
+
+def test_cache_rows_in_host_memory(torch_cuda, oracle):
+    """data_storage_on_host = 1: the rows of the cache live in pinned host memory the GPU maps; tags,
+    hit masks and rows read through the cache are those of a cache with rows in HBM."""
+    torch = torch_cuda
+    rows, width = 3000, 16
+    t = dg.dyadic_table(rows, width, 3, np.float32)
+    cache_bytes = 64 * per_set()
+    hbm = CacheTable(cache_bytes, ROW, value_dtype="f32", key_dtype=np.int64)
+    host = CacheTable(cache_bytes, ROW, value_dtype="f32", key_dtype=np.int64, data_storage_on_host=True)
+    keys = dg.zipf_keys(1500, rows, 1.1, 7, dg.permutation(rows))
+    vals = t[keys].view(np.uint8).reshape(-1, ROW)
+    upd = dg.dyadic_table(keys.size, width, 32, np.float32)
+    for c in (hbm, host):
+        c.insert(keys, vals)
+        c.update_accumulate(keys, upd, "f32")       # duplicates of a batch are summed
+    assert np.array_equal(hbm.tags(), host.tags())
+    valid = hbm.tags() != -1
+    assert np.array_equal(hbm.data()[valid], host.data()[valid])
+    probe = dg.zipf_keys(1000, rows, 1.1, 8, dg.permutation(rows))
+    outs = []
+    for c in (hbm, host):
+        out, mask = np.zeros((1000, ROW), np.uint8), np.zeros(16, np.uint64)
+        c.find(probe, out, mask)
+        outs.append((out, mask))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert outs[0][1].any()
+    hbm.close()
+    host.close()
