@@ -210,3 +210,33 @@ def test_two_tier_lookup_with_scatter_merge(torch_cuda, oracle):
     got = d_dst.cpu().numpy()
     assert np.array_equal(got[:, :21], src[:, :21]) and not got[:, 21:].any()
     gpu.close()
+
+
+@pytest.mark.gpu
+def test_host_side_policy_is_the_same_for_both_key_widths(torch_cuda):
+    """modify_on_gpu = 0 with int32 and with int64 keys: the same batches leave the same tags (the
+    policy works in the key's own width through its unsigned counterpart, like the device probe)."""
+    from nve_helpers import CacheTable
+    rows, row = 6000, 64
+    t = np.random.default_rng(2).integers(0, 256, (rows, row), dtype=np.uint8)
+    sets = 41
+    c64 = CacheTable(sets * (8 * 8 + 8 * row), row, key_dtype=np.int64, modify_on_gpu=False)
+    c32 = CacheTable(sets * (8 * 4 + 8 * row), row, key_dtype=np.int32, modify_on_gpu=False)
+    assert c64.num_sets == c32.num_sets == sets
+    perm = dg.permutation(rows)
+    for step in range(4):
+        keys = dg.zipf_keys(1500, rows, 1.15, 40 + step, perm)
+        for c in (c64, c32):
+            c.insert(keys, t[keys])
+        assert np.array_equal(c64.tags(), c32.tags())
+        gone = np.unique(keys)[::7]
+        for c in (c64, c32):
+            c.erase(gone)
+        assert np.array_equal(c64.tags(), c32.tags())
+        out64, out32 = np.zeros((keys.size, row), np.uint8), np.zeros((keys.size, row), np.uint8)
+        m64, m32 = np.zeros((keys.size + 63) // 64, np.uint64), np.zeros((keys.size + 63) // 64, np.uint64)
+        c64.find(keys, out64, m64)
+        c32.find(keys, out32, m32)
+        assert np.array_equal(m64, m32) and np.array_equal(out64, out32)
+    c64.close()
+    c32.close()

@@ -179,3 +179,44 @@ def test_pynve_named_edge(torch_cuda, oracle):
     want_t[u_np] += -0.5 * want_g
     assert np.array_equal(t_dev.cpu().numpy().astype(np.float64), want_t)
     emb.close()
+
+
+@pytest.mark.parametrize("host_rows", [False, True])
+def test_cached_layer_over_the_host_side_policy(torch_cuda, host_rows):
+    """A cached layer whose table decides replacements on the host (modify_on_gpu = 0), with the
+    cached rows in HBM or in pinned host memory: lookups are exact whatever is cached, explicit
+    inserts, updates and the automatic inserts (whose keys are collected on the device) all go through
+    the host mirror, and the cache does fill."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GpuTable, LinearUVMEmbeddingLayer
+    rows, dim = 20000, 64
+    table = dg.normal_table(rows, dim, 0.02, 1, np.float16)
+    backing = torch.from_numpy(table).cuda()
+    gt = GpuTable(2000 // 8 * (64 + 8 * dim * 2), dim * 2, "float16", uvm_table=backing, uvm_num_rows=rows,
+                  modify_on_gpu=False, data_storage_on_host=host_rows)
+    layer = LinearUVMEmbeddingLayer(gt)
+    ctx = layer.create_execution_context()
+    perm = dg.permutation(rows)
+    tb = table.view(np.uint8).reshape(rows, -1)
+    rates = []
+    for step in range(6):
+        if step == 1:
+            warm = dg.zipf_keys(3000, rows, 1.2, 10, perm)
+            layer.insert(ctx, warm.size, warm, dim * 2, dim * 2, tb[warm])
+            ctx.wait()
+        keys = dg.zipf_keys(70000, rows, 1.2, 20 + step, perm)     # enough keys to trigger automatic inserts
+        out = np.zeros((keys.size, dim), np.float16)
+        rates.append(layer.lookup(ctx, keys.size, keys, out, dim * 2, want_hitrate=True))
+        ctx.wait()
+        assert np.array_equal(out, table[keys])
+    assert rates[0] == 0.0 and rates[-1] > 0.3, rates
+    # an update reaches the cached copy and the backing table
+    uk = np.unique(dg.zipf_keys(500, rows, 1.2, 20, perm))
+    new = dg.normal_table(uk.size, dim, 0.02, 2, np.float16)
+    layer.update(ctx, uk.size, uk, dim * 2, dim * 2, new, -1)
+    ctx.wait()
+    out = np.zeros((uk.size, dim), np.float16)
+    layer.lookup(ctx, uk.size, uk, out, dim * 2)
+    ctx.wait()
+    assert np.array_equal(out, new)
+    assert np.array_equal(backing.cpu().numpy()[uk], new)
