@@ -325,7 +325,7 @@ def run_ours(args):
     alg_bytes = algorithmic_bytes(keys_region // launches)
     peak, peak_kind = bw.hbm_peak()
     achieved = alg_bytes / mean_launch_s / 1e9
-    roofline = {"bound": "hbm", "kernel": "pool_dense_kernel<F16,GROUP=16,U=4>",
+    roofline = {"bound": "hbm", "kernel": "pool_dense_kernel<F16,GROUP=16,U=8>",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": None,
                 "algorithmic_bytes_per_launch": alg_bytes, "mean_launch_us": mean_launch_s * 1e6}

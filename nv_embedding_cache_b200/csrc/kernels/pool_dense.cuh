@@ -112,7 +112,7 @@ __device__ __forceinline__ void accumulate_bytes_packed(uint64_t* acc, const uin
 // group covers one contiguous run of the row.  Lane l then holds the columns
 // 4 * (j * nvec + l) .. + 3 for j = 0..3 and stores them as four short vectors.
 template <In IN, int GROUP, int U, bool WEIGHTED, bool SANITIZE, bool WORDS = false>
-__global__ void __launch_bounds__(128) pool_dense_kernel(const PoolKernelParams p) {
+__global__ void __launch_bounds__(128, 8) pool_dense_kernel(const PoolKernelParams p) {
   constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
   constexpr bool QUANT = (IN == In::I8 || IN == In::U8);
   const int lane = threadIdx.x & 31;

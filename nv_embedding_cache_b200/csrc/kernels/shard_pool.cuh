@@ -121,7 +121,7 @@ __device__ __forceinline__ const uint8_t* shard_row_address(const ShardPoolParam
 // Same accumulation order and arithmetic as pool_dense_kernel / lookup_pool_kernel: every output
 // element is summed by one lane, in key order, in fp32; Mean multiplies by 1 / denominator.
 template <In IN, int GROUP, int U, bool WEIGHTED, typename CodeT>
-__global__ void __launch_bounds__(128) shard_pool_kernel(const ShardPoolParams p) {
+__global__ void __launch_bounds__(128, 8) shard_pool_kernel(const ShardPoolParams p) {
   static_assert(IN == In::F16 || IN == In::F32, "float rows only");
   constexpr int EPV = 16 / InTraits<IN>::kElemBytes;
   const int lane = threadIdx.x & 31;
