@@ -11,6 +11,8 @@
 
 #include "nve_b200_ops.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 namespace nve_b200 {
 
 // Exceptions carry the status the C boundary reports.  The mapping follows the reference's
@@ -41,6 +43,17 @@ struct CudaFailure : Error {
 };
 
 nve_status_t set_last_error(nve_status_t status, const std::string& message);
+
+// Named range around an entry point for timeline profilers (the reference marks its entry points
+// the same way, include/cuda_support.hpp:26-55).  Header-only NVTX: without a profiler attached a
+// push or pop is a call through a null-checked pointer.
+struct ScopedRange {
+  explicit ScopedRange(const char* name) { nvtxRangePushA(name); }
+  ~ScopedRange() { nvtxRangePop(); }
+  ScopedRange(const ScopedRange&) = delete;
+  ScopedRange& operator=(const ScopedRange&) = delete;
+};
+#define NVE_B200_RANGE() ::nve_b200::ScopedRange nve_b200_range_(__func__)
 
 template <typename... Args>
 std::string cat(Args&&... args) {

@@ -153,7 +153,8 @@ nve_status_t nve_table_destroy(nve_table_t table) {
   return NVE_SUCCESS;
 }
 #define NVE_TABLE_CTX_CHECK() \
-  if (!table || !table->ptr || !ctx || !ctx->ptr) return bad_arg("table and ctx must not be NULL")
+  if (!table || !table->ptr || !ctx || !ctx->ptr) return bad_arg("table and ctx must not be NULL"); \
+  NVE_B200_RANGE()
 
 nve_status_t nve_table_find(nve_table_t table, nve_context_t ctx, int64_t n, const void* keys,
                             uint64_t* hit_mask, int64_t value_stride, void* values,
@@ -291,7 +292,8 @@ nve_status_t nve_layer_destroy(nve_layer_t layer) {
   return NVE_SUCCESS;
 }
 #define NVE_LAYER_CTX_CHECK() \
-  if (!layer || !layer->ptr || !ctx || !ctx->ptr) return bad_arg("layer and ctx must not be NULL")
+  if (!layer || !layer->ptr || !ctx || !ctx->ptr) return bad_arg("layer and ctx must not be NULL"); \
+  NVE_B200_RANGE()
 
 nve_status_t nve_layer_lookup(nve_layer_t layer, nve_context_t ctx, int64_t num_keys,
                               const void* keys, void* output, int64_t output_stride,

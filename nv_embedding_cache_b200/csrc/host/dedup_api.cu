@@ -93,6 +93,7 @@ nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, in
                                     void* d_unique_out, void* d_counts_out, void* d_loc_map_out,
                                     void* h_num_runs_out, void* d_inverse_buffer, void* d_offsets,
                                     void* stream, int32_t end_bit) {
+  NVE_B200_RANGE();
   if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
   return guarded([&] {
     const int kb = nve_b200::key_bytes(d->key_type);
@@ -135,6 +136,7 @@ nve_status_t nve_b200_dedup_grads(nve_b200_deduper_t d, const void* d_grads, int
                                   const void* d_loc_map, void* d_dst, int64_t dst_stride,
                                   int32_t apply_to_table, int64_t table_rows, float alpha,
                                   void* stream) {
+  NVE_B200_RANGE();
   if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
   return guarded([&] {
     if (num_keys <= 0) return;
@@ -190,6 +192,7 @@ nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, c
                                        const void* d_csr_offsets, int64_t num_bags, int64_t fixed_hotness,
                                        const float* d_weights, void* d_unique_out, void* d_grads_out,
                                        int64_t out_stride, int64_t* h_num_unique, void* stream) {
+  NVE_B200_RANGE();
   if (!d) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "deduper must not be NULL");
   return guarded([&] {
     NVE_B200_ARG(h_num_unique != nullptr, "pooling_backprop: h_num_unique must not be NULL");

@@ -138,6 +138,7 @@ int64_t nve_b200_registry_size(void) {
 
 nve_status_t nve_b200_registry_lookup(const void* marker, int64_t num_keys, const int64_t* keys, void* output,
                                       void* stream) {
+  NVE_B200_RANGE();
   return guarded([&] {
     auto entry = nve_b200::find_layer(marker);
     nve_context_t ctx = entry->context_for(stream);
@@ -151,6 +152,7 @@ nve_status_t nve_b200_registry_lookup_pooled(const void* marker, int64_t num_key
                                              void* output, nve_pooling_type_t pooling_type,
                                              int64_t num_offsets, const int64_t* offsets,
                                              nve_data_type_t weight_dtype, const void* weights, void* stream) {
+  NVE_B200_RANGE();
   return guarded([&] {
     auto entry = nve_b200::find_layer(marker);
     nve_context_t ctx = entry->context_for(stream);

@@ -751,6 +751,7 @@ nve_status_t nve_b200_sharded_table_destroy(nve_b200_sharded_table_t table) {
 
 nve_status_t nve_b200_sharded_table_lookup_pooled(nve_b200_sharded_table_t table,
                                                   const nve_b200_sharded_lookup_t* lookup, void* stream) {
+  NVE_B200_RANGE();
   if (!table || !lookup) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "table and lookup must not be NULL");
   return guarded([&] {
     check_lookup(*table, *lookup);
@@ -765,6 +766,7 @@ nve_status_t nve_b200_sharded_table_lookup_pooled(nve_b200_sharded_table_t table
 
 nve_status_t nve_b200_sharded_table_set_hot_keys(nve_b200_sharded_table_t table, const void* d_keys, int64_t n,
                                                  int64_t* num_hot, void* stream) {
+  NVE_B200_RANGE();
   if (!table) return set_last_error(NVE_ERROR_INVALID_ARGUMENT, "table must not be NULL");
   return guarded([&] {
     std::lock_guard<std::mutex> lock(table->mu);
