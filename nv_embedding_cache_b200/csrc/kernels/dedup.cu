@@ -8,10 +8,10 @@
 //                  max_run consecutive entries of a group when max_run > 0), offsets[C] = n,
 //   loc_map[c]     index u of the unique key chunk c belongs to (max_run > 0 only),
 //   num_runs       {U, C} on the host.
-// The ordering step is a radix sort of (key, position) pairs (cub::DeviceRadixSort, a library
-// primitive, over `end_bit` key bits); run detection, counting, chunk splitting and the maps are
-// fused into two kernels around one prefix scan, and the only host synchronisation is the final
-// read-back of {U, C}.
+// The ordering step is a stable radix sort of (key, position) over `end_bit` key bits (this
+// library's own, radix_sort.cu; the toolkit's for batches beyond its range); run detection, ranks,
+// counts, chunk splitting and the maps are one kernel behind it (dedup_emit_kernel: two chained
+// scans with look-back), and the only host synchronisation is the final read-back of {U, C}.
 //
 // dedup_grads (reference cuda_ops/dedup_grads_kernel.cuh:56-253): unique_grad[u] = sum of the
 // gradient rows at the positions of group u.  Here every chunk is summed by one lane group in
@@ -151,6 +151,289 @@ __global__ void emit_chunks_kernel(const KeyT* group_start, const KeyT* num_grou
   }
 }
 
+// ---- everything after the sort in one kernel -------------------------------------------------
+// From the sorted (key, position) entries: group heads, the rank of every group (a prefix sum over
+// heads), unique keys, counts, and the chunk table (a prefix sum over chunks per group) -- two
+// dependent scans.  Run as one launch: tiles of kEmitTile entries, taken in order from a counter, each
+// tile publishing its totals in a status word and reading those of the tiles before it (a chained
+// scan with look-back).  A group is finished by the tile that holds the NEXT head (or by the last
+// tile), which then knows its count and its chunks; so the state of the first scan carries, besides
+// the number of heads, the position of the last head seen, and the second scan runs over the groups
+// each tile finishes.  Every wait is bounded; a wait that runs out sets *error and the launch
+// reports {0, 0}.
+// 1024 threads x 8 entries: 128 tiles for 2^20 entries, so a look-back needs at most four windows
+// (measured: de-duplication of 2^20 keys 139.5 us against 145-147 us with tiles of 2048 or 4096
+// entries, and 147.8 us with the six launches this kernel replaces).
+constexpr int kEmitThreads = 1024;
+constexpr int kEmitItems = 8;
+constexpr int kEmitTile = kEmitThreads * kEmitItems;
+constexpr int kEmitGroups = kEmitItems + 1;   // a tile finishes at most kEmitTile + 1 groups
+constexpr int64_t kEmitMaxEntries = int64_t{1} << 30;   // what the 30-bit head count of a status word holds
+constexpr uint32_t kEmitSpinLimit = 1u << 24;
+
+enum class EmitSource { kPackedWords, kWideWords, kSortedKeys };
+
+struct EmitScratch {
+  unsigned long long* heads;    // [tiles] flag << 62 | heads << 32 | (last head position + 1)
+  unsigned long long* chunks;   // [tiles] flag << 62 | chunks
+  uint32_t* next_tile;          // tile counter
+  uint32_t* error;              // set when a wait ran out
+};
+
+__device__ __forceinline__ unsigned long long emit_wait(const unsigned long long* word, uint32_t* error) {
+  const volatile unsigned long long* w = word;
+  unsigned long long v = *w;
+  uint32_t spins = 0;
+  while ((v >> 62) == 0) {
+    if (++spins > kEmitSpinLimit) {
+      *error = 1u;
+      return ~0ull;
+    }
+    __nanosleep(32);
+    v = *w;
+  }
+  return v;
+}
+
+// Block-wide exclusive prefix sum of one value per thread (kEmitThreads threads); *total = the sum.
+__device__ __forceinline__ uint32_t emit_block_scan(uint32_t value, uint32_t* warp_sums, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t incl = value;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  uint32_t before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < kEmitThreads / 32; w++) {
+    const uint32_t sum = warp_sums[w];
+    if (w < warp) before += sum;
+    all += sum;
+  }
+  __syncthreads();
+  *total = all;
+  return before + incl - value;
+}
+
+template <typename KeyT, EmitSource SRC>
+__global__ void __launch_bounds__(kEmitThreads) dedup_emit_kernel(
+    const uint64_t* __restrict__ words, const uint32_t* __restrict__ word_pos, uint64_t flip,
+    const KeyT* __restrict__ keys, const KeyT* __restrict__ sorted_keys, int64_t n, int64_t max_run,
+    KeyT* __restrict__ unique, KeyT* __restrict__ counts, KeyT* __restrict__ loc_map, KeyT* __restrict__ inverse,
+    KeyT* __restrict__ offsets, KeyT* __restrict__ num_out, EmitScratch st) {
+  __shared__ uint32_t s_tile;
+  __shared__ uint32_t s_warp[kEmitThreads / 32];
+  __shared__ KeyT s_edge[kEmitThreads];             // last key of every thread
+  __shared__ uint32_t s_head_pos[kEmitTile + 1];    // positions of the tile's heads, then the end marker
+  __shared__ unsigned long long s_prefix[2];        // results of the two look-backs
+  if (threadIdx.x == 0) s_tile = atomicAdd(st.next_tile, 1u);
+  __syncthreads();
+  const uint32_t tile = s_tile;
+  const uint32_t tiles = static_cast<uint32_t>((n + kEmitTile - 1) / kEmitTile);
+  const int64_t base = static_cast<int64_t>(tile) * kEmitTile + static_cast<int64_t>(threadIdx.x) * kEmitItems;
+  const bool last_tile = tile + 1 == tiles;
+
+  // ---- keys and positions of my entries, and the key just before them
+  KeyT key[kEmitItems];
+  auto entry = [&](int64_t i, uint32_t* pos_out) -> KeyT {
+    if constexpr (SRC == EmitSource::kPackedWords) {
+      const uint32_t pos = static_cast<uint32_t>(words[i]);
+      *pos_out = pos;
+      return keys[pos];
+    } else if constexpr (SRC == EmitSource::kWideWords) {
+      *pos_out = word_pos[i];
+      return static_cast<KeyT>(static_cast<int64_t>(words[i] ^ flip));
+    } else {
+      *pos_out = 0;
+      return sorted_keys[i];
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < kEmitItems; j++) {
+    const int64_t i = base + j;
+    key[j] = 0;
+    if (i < n) {
+      uint32_t pos;
+      key[j] = entry(i, &pos);
+      if constexpr (SRC != EmitSource::kSortedKeys) inverse[i] = static_cast<KeyT>(pos);
+    }
+  }
+  s_edge[threadIdx.x] = key[kEmitItems - 1];
+  __syncthreads();
+  KeyT before = 0;
+  if (threadIdx.x > 0) {
+    before = s_edge[threadIdx.x - 1];
+  } else if (base > 0) {
+    uint32_t pos;
+    before = entry(base - 1, &pos);
+  }
+
+  // ---- heads of my entries
+  uint32_t head_bits = 0;
+#pragma unroll
+  for (int j = 0; j < kEmitItems; j++) {
+    const int64_t i = base + j;
+    const KeyT prev = j == 0 ? before : key[j - 1];
+    if (i < n && (i == 0 || key[j] != prev)) head_bits |= 1u << j;
+  }
+  uint32_t tile_heads;
+  const uint32_t my_first = emit_block_scan(__popc(head_bits), s_warp, &tile_heads);
+  {
+    uint32_t r = my_first;
+#pragma unroll
+    for (int j = 0; j < kEmitItems; j++) {
+      if (head_bits & (1u << j)) s_head_pos[r++] = static_cast<uint32_t>(base + j);
+    }
+  }
+  __syncthreads();
+  const uint32_t tile_last_head = tile_heads ? s_head_pos[tile_heads - 1] + 1u : 0u;   // position + 1, 0 = none
+
+  // ---- first scan: heads before this tile, and where the last of them is.  Warp 0 looks back over
+  // 32 earlier tiles at a time and stops at the nearest one that has published its inclusive totals.
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const unsigned long long mine = (static_cast<unsigned long long>(tile_heads) << 32) | tile_last_head;
+    if (lane == 0 && tile > 0) {
+      reinterpret_cast<volatile unsigned long long*>(st.heads)[tile] = (1ull << 62) | mine;
+    }
+    uint32_t heads_sum = 0, last_seen = 0;
+    for (int64_t t0 = static_cast<int64_t>(tile) - 1; t0 >= 0; t0 -= 32) {
+      const int64_t t = t0 - lane;
+      const unsigned long long v = t >= 0 ? emit_wait(st.heads + t, st.error) : (2ull << 62);
+      if (__any_sync(0xffffffffu, v == ~0ull)) break;
+      const uint32_t done = __ballot_sync(0xffffffffu, (v >> 62) == 2);
+      const int stop = done ? __ffs(done) - 1 : 31;
+      const bool take = lane <= stop;
+      heads_sum += __reduce_add_sync(0xffffffffu, take ? static_cast<uint32_t>((v >> 32) & 0x3fffffffull) : 0u);
+      const uint32_t last = take ? static_cast<uint32_t>(v) : 0u;
+      const uint32_t has_last = __ballot_sync(0xffffffffu, last != 0);
+      const uint32_t nearest = __shfl_sync(0xffffffffu, last, has_last ? __ffs(has_last) - 1 : 0);
+      if (last_seen == 0 && has_last) last_seen = nearest;
+      if (done) break;
+    }
+    if (lane == 0) {
+      const unsigned long long incl_heads = static_cast<unsigned long long>(heads_sum) + tile_heads;
+      const unsigned long long incl_last = tile_last_head ? tile_last_head : last_seen;
+      __threadfence();
+      reinterpret_cast<volatile unsigned long long*>(st.heads)[tile] = (2ull << 62) | (incl_heads << 32) | incl_last;
+      s_prefix[0] = (static_cast<unsigned long long>(heads_sum) << 32) | last_seen;
+    }
+  }
+  __syncthreads();
+  const uint32_t heads_before = static_cast<uint32_t>(s_prefix[0] >> 32);
+  const uint32_t last_before = static_cast<uint32_t>(s_prefix[0]);          // position + 1 of the open group's head
+
+  // ---- unique keys of the groups that start here
+  {
+    uint32_t r = my_first;
+#pragma unroll
+    for (int j = 0; j < kEmitItems; j++) {
+      if (head_bits & (1u << j)) unique[heads_before + r++] = key[j];
+    }
+  }
+
+  // ---- groups finished here, in rank order: the open group from earlier tiles (if a head of this
+  // tile ends it), the groups that start here and end here, and in the last tile whatever is still open.
+  // Finished group g: rank first_rank + g, start start_of(g), end start_of(g + 1).
+  const bool open_before = last_before != 0;                 // a group started in an earlier tile is still open
+  const uint32_t closes_open = (open_before && tile_heads > 0) ? 1u : 0u;
+  uint32_t finished = closes_open + (tile_heads > 0 ? tile_heads - 1 : 0);
+  if (last_tile && (tile_heads > 0 || open_before)) finished += 1;
+  if (threadIdx.x == 0) s_head_pos[tile_heads] = static_cast<uint32_t>(n);   // end of the last group (last tile only)
+  __syncthreads();
+  // boundaries: b(0) = start of the first finished group, b(g + 1) = its end
+  const bool from_open = closes_open || (last_tile && tile_heads == 0 && open_before);
+  auto boundary = [&](uint32_t g) -> int64_t {
+    if (from_open) return g == 0 ? static_cast<int64_t>(last_before) - 1 : static_cast<int64_t>(s_head_pos[g - 1]);
+    return static_cast<int64_t>(s_head_pos[g]);
+  };
+  const uint32_t first_rank = from_open ? heads_before - 1 : heads_before;
+
+  uint32_t my_chunks[kEmitGroups];
+  uint32_t my_sum = 0;
+#pragma unroll
+  for (int j = 0; j < kEmitGroups; j++) {
+    const uint32_t g = threadIdx.x * kEmitGroups + j;
+    my_chunks[j] = 0;
+    if (g < finished) {
+      const int64_t count = boundary(g + 1) - boundary(g);
+      counts[first_rank + g] = static_cast<KeyT>(count);
+      my_chunks[j] = max_run > 0 ? static_cast<uint32_t>((count + max_run - 1) / max_run) : 1u;
+      my_sum += my_chunks[j];
+    }
+  }
+  uint32_t tile_chunks;
+  uint32_t chunk_at = emit_block_scan(my_sum, s_warp, &tile_chunks);
+
+  // ---- second scan: chunks before this tile
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    if (lane == 0 && tile > 0) {
+      reinterpret_cast<volatile unsigned long long*>(st.chunks)[tile] = (1ull << 62) | tile_chunks;
+    }
+    unsigned long long chunks_sum = 0;
+    for (int64_t t0 = static_cast<int64_t>(tile) - 1; t0 >= 0; t0 -= 32) {
+      const int64_t t = t0 - lane;
+      const unsigned long long v = t >= 0 ? emit_wait(st.chunks + t, st.error) : (2ull << 62);
+      if (__any_sync(0xffffffffu, v == ~0ull)) break;
+      const uint32_t done = __ballot_sync(0xffffffffu, (v >> 62) == 2);
+      const int stop = done ? __ffs(done) - 1 : 31;
+      unsigned long long part = lane <= stop ? (v & 0x3fffffffffffffffull) : 0ull;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
+      chunks_sum += part;
+      if (done) break;
+    }
+    if (lane == 0) {
+      __threadfence();
+      reinterpret_cast<volatile unsigned long long*>(st.chunks)[tile] = (2ull << 62) | (chunks_sum + tile_chunks);
+      s_prefix[1] = chunks_sum;
+    }
+  }
+  __syncthreads();
+  const uint64_t chunks_before = s_prefix[1];
+
+  // ---- chunk table of the finished groups
+#pragma unroll
+  for (int j = 0; j < kEmitGroups; j++) {
+    const uint32_t g = threadIdx.x * kEmitGroups + j;
+    if (g < finished) {
+      const int64_t start = boundary(g);
+      const uint64_t at = chunks_before + chunk_at;
+      for (uint32_t k = 0; k < my_chunks[j]; k++) {
+        offsets[at + k] = static_cast<KeyT>(start + static_cast<int64_t>(k) * (max_run > 0 ? max_run : 0));
+        if (loc_map) loc_map[at + k] = static_cast<KeyT>(first_rank + g);
+      }
+      chunk_at += my_chunks[j];
+    }
+  }
+  if (last_tile && threadIdx.x == 0) {
+    const bool failed = *reinterpret_cast<volatile uint32_t*>(st.error) != 0;
+    const uint64_t total_chunks = chunks_before + tile_chunks;
+    offsets[failed ? 0 : total_chunks] = static_cast<KeyT>(failed ? 0 : n);
+    num_out[0] = static_cast<KeyT>(failed ? 0 : heads_before + tile_heads);
+    num_out[1] = static_cast<KeyT>(failed ? 0 : total_chunks);
+  }
+}
+
+inline size_t emit_scratch_bytes(int64_t n) {
+  const size_t tiles = static_cast<size_t>((n + kEmitTile - 1) / kEmitTile) + 1;
+  return 2 * tiles * sizeof(unsigned long long) + 64;
+}
+
+inline EmitScratch emit_scratch_at(void* base, int64_t capacity) {
+  const size_t tiles = static_cast<size_t>((capacity + kEmitTile - 1) / kEmitTile) + 1;
+  EmitScratch st;
+  st.heads = static_cast<unsigned long long*>(base);
+  st.chunks = st.heads + tiles;
+  st.next_tile = reinterpret_cast<uint32_t*>(st.chunks + tiles);
+  st.error = st.next_tile + 1;
+  return st;
+}
+
 template <typename KeyT>
 struct Workspace {
   KeyT *sorted, *pos, *group_start, *num_out;
@@ -158,6 +441,7 @@ struct Workspace {
   uint64_t *packed_in, *packed_out, *packed_tmp;
   uint32_t *pos_in, *pos_out, *pos_tmp;
   void* radix_scratch;
+  void* emit_scratch;
   void* cub_tmp;
   size_t cub_bytes;
   size_t total;
@@ -189,6 +473,7 @@ Workspace<KeyT> carve(void* base, int64_t n, size_t cub_bytes) {
   w.pos_out = static_cast<uint32_t*>(take(N * 4));
   w.pos_tmp = static_cast<uint32_t*>(take(N * 4));
   w.radix_scratch = take(radix_sort_scratch_bytes(n));
+  w.emit_scratch = take(emit_scratch_bytes(n));
   w.cub_tmp = take(cub_bytes);
   w.cub_bytes = cub_bytes;
   w.total = off + 256;
@@ -221,6 +506,14 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
   const int T = 256;
   const int N = static_cast<int>(n);
   size_t tmp = w.cub_bytes;
+  // Everything after the sort runs as one kernel (dedup_emit_kernel) unless
+  // NVE_B200_DEDUP_SPLIT_EMIT asks for the earlier form: heads, two library scans and three emit
+  // kernels.
+  static const bool split_emit = std::getenv("NVE_B200_DEDUP_SPLIT_EMIT") != nullptr;
+  const bool fused_emit = !split_emit && n <= kEmitMaxEntries;
+  const EmitScratch emit = emit_scratch_at(w.emit_scratch, capacity);
+  const unsigned emit_tiles = static_cast<unsigned>((n + kEmitTile - 1) / kEmitTile);
+  if (fused_emit) NVE_B200_CUDA(cudaMemsetAsync(w.emit_scratch, 0, emit_scratch_bytes(capacity), s));
   if (end_bit <= 32) {
     const uint32_t flip = (sizeof(KeyT) == 4 && end_bit == 32) ? 0x80000000u : 0u;
     // this library's own stable radix sort, whose first pass packs (key bits, position) on the fly;
@@ -238,8 +531,14 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
       NVE_B200_CUDA(cub::DeviceRadixSort::SortKeys(w.cub_tmp, tmp, w.packed_in, w.packed_out, N, 32,
                                                    32 + end_bit, s));
     }
-    unpack_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, keys, w.sorted, inverse,
-                                                             w.head, n);
+    if (fused_emit) {
+      dedup_emit_kernel<KeyT, EmitSource::kPackedWords><<<emit_tiles, kEmitThreads, 0, s>>>(
+          w.packed_out, nullptr, 0, keys, nullptr, n, max_run, unique, counts, max_run > 0 ? loc_map : nullptr,
+          inverse, offsets, w.num_out, emit);
+    } else {
+      unpack_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, keys, w.sorted, inverse,
+                                                               w.head, n);
+    }
   } else if (n <= radix_sort_max_entries() && std::getenv("NVE_B200_DEDUP_LIBRARY_SORT") == nullptr) {
     // the sort orders on the low end_bit bits; the head test compares whole keys, as the run-length
     // encoding of the reference does after its sort
@@ -251,26 +550,40 @@ void dedup_typed(void* workspace, int64_t capacity, const void* keys_v, int64_t 
     from.form = RadixSource::kWide;
     radix_sort_pairs_u64(from, nullptr, w.packed_out, w.packed_tmp, nullptr, w.pos_out, w.pos_tmp, n, 0, end_bit,
                          w.radix_scratch, s);
-    narrow_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, w.pos_out, flip, w.sorted, inverse,
-                                                             w.head, n);
+    if (fused_emit) {
+      dedup_emit_kernel<KeyT, EmitSource::kWideWords><<<emit_tiles, kEmitThreads, 0, s>>>(
+          w.packed_out, w.pos_out, flip, keys, nullptr, n, max_run, unique, counts, max_run > 0 ? loc_map : nullptr,
+          inverse, offsets, w.num_out, emit);
+    } else {
+      narrow_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.packed_out, w.pos_out, flip, w.sorted, inverse,
+                                                               w.head, n);
+    }
   } else {
     iota_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.pos, n);
     NVE_B200_CUDA(cub::DeviceRadixSort::SortPairs(w.cub_tmp, tmp, keys, w.sorted, w.pos, inverse, N,
                                                   0, end_bit, s));
-    mark_group_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, n);
+    if (fused_emit) {
+      dedup_emit_kernel<KeyT, EmitSource::kSortedKeys><<<emit_tiles, kEmitThreads, 0, s>>>(
+          nullptr, nullptr, 0, keys, w.sorted, n, max_run, unique, counts, max_run > 0 ? loc_map : nullptr,
+          inverse, offsets, w.num_out, emit);
+    } else {
+      mark_group_heads_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, n);
+    }
   }
-  tmp = w.cub_bytes;
-  NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.head, w.rank, N, s));
-  emit_groups_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, w.rank, n, unique,
-                                                           w.group_start, w.num_out);
-  group_counts_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, n, max_run,
-                                                            counts, w.chunks);
-  tmp = w.cub_bytes;
-  NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.chunks, w.chunk_base, N, s));
-  emit_chunks_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, w.chunks,
-                                                           w.chunk_base, n, max_run, offsets,
-                                                           max_run > 0 ? loc_map : nullptr,
-                                                           w.num_out);
+  if (!fused_emit) {
+    tmp = w.cub_bytes;
+    NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.head, w.rank, N, s));
+    emit_groups_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.sorted, w.head, w.rank, n, unique,
+                                                             w.group_start, w.num_out);
+    group_counts_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, n, max_run,
+                                                              counts, w.chunks);
+    tmp = w.cub_bytes;
+    NVE_B200_CUDA(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.chunks, w.chunk_base, N, s));
+    emit_chunks_kernel<KeyT><<<blocks_for(n, T), T, 0, s>>>(w.group_start, w.num_out, w.chunks,
+                                                             w.chunk_base, n, max_run, offsets,
+                                                             max_run > 0 ? loc_map : nullptr,
+                                                             w.num_out);
+  }
   NVE_B200_CUDA(cudaGetLastError());
   NVE_B200_CUDA(cudaMemcpyAsync(pinned_num_runs, w.num_out, 2 * sizeof(KeyT),
                                 cudaMemcpyDeviceToHost, s));
