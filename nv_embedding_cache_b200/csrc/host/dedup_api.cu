@@ -127,6 +127,9 @@ nve_status_t nve_b200_deduper_dedup(nve_b200_deduper_t d, const void* d_keys, in
     d->last_num_keys = num_keys;
     d->last_chunks = kb == 8 ? static_cast<const int64_t*>(d->pinned)[1]
                              : static_cast<const int32_t*>(d->pinned)[1];
+    // a batch of at least one key has at least one chunk: {0, 0} is what the emit kernel reports
+    // when one of its bounded waits ran out
+    NVE_B200_CHECK(d->last_chunks > 0, "dedup: the tile scan behind the sort did not complete");
   });
 }
 
@@ -260,6 +263,7 @@ nve_status_t nve_b200_pooling_backprop(nve_b200_deduper_t d, int64_t num_keys, c
     NVE_B200_CUDA(cudaStreamSynchronize(s));   // the number of unique keys is part of the return value
     *h_num_unique = kb == 8 ? static_cast<const int64_t*>(d->pinned)[0]
                             : static_cast<const int32_t*>(d->pinned)[0];
+    NVE_B200_CHECK(*h_num_unique > 0, "pooled backward: the tile scan behind the sort did not complete");
     d->last_num_keys = -1;   // the caller's own dedup() arrays no longer match the workspace
   });
 }
