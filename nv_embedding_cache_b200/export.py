@@ -153,7 +153,8 @@ def load_nve_layers(save_dir: str, *, gpu_cache_size_override: Optional[int] = N
                     resource_remap: Optional[dict] = None) -> list:
     """Rebuilds the layers a directory describes, tables loaded.  `registry` (resource key ->
     block), when passed to several calls, lets models saved from one process share blocks again;
-    `resource_remap` renames keys of the file before they are looked up in it.  The caller keeps
+    `resource_remap` renames keys of the file before they are looked up in it.  The flat metadata
+    of schema 1 (a list of layers, each with storage of its own) is read as well.  The caller keeps
     the returned layers alive for as long as a graph refers to them."""
     _need_ops("load_nve_layers")
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -164,7 +165,9 @@ def load_nve_layers(save_dir: str, *, gpu_cache_size_override: Optional[int] = N
     with open(os.path.join(save_dir, "metadata.json")) as f:
         doc = json.load(f)
     if isinstance(doc, list):
-        raise ValueError("metadata.json is in the legacy flat layout (version 1); re-save it with a current writer")
+        # the flat layout of schema 1: one entry per layer, no resources section, every layer with
+        # storage of its own and its table in weights/<module path with dots as underscores>.nve
+        doc = {"version": 1, "layers": doc}
     if doc.get("version", 1) > METADATA_SCHEMA_VERSION:
         raise RuntimeError(f"metadata.json has schema version {doc['version']}; this reader knows up to "
                            f"{METADATA_SCHEMA_VERSION}")
@@ -179,20 +182,25 @@ def load_nve_layers(save_dir: str, *, gpu_cache_size_override: Optional[int] = N
         if kind not in (LayerType.GPULayer, LayerType.LinearUVM):
             raise NotImplementedError(f"layer '{path}': {kind.name} layers are outside this library")
         ref = entry.get("storage_ref")
-        if not ref:
-            raise ValueError(f"layer '{path}' names no storage block")
-        key = remap.get(ref, ref)
-        desc = described.get(key)
-        if desc is not None and (desc["row_elements"], desc["num_rows"]) != (cols, rows):
-            raise ValueError(f"block '{key}' is {desc['num_rows']} x {desc['row_elements']} but layer '{path}' "
-                             f"expects {rows} x {cols}: stale or hand-edited metadata?")
-        fresh = key not in registry
-        if fresh:
-            if desc is None:
-                raise ValueError(f"storage_ref '{key}' is not among resources.memblocks")
-            registry[key] = _build_block(desc, device.index)
+        if doc.get("version", 1) < 2:
+            # schema 1: the layer allocates its own storage; the file is named after the module path
+            ref, key, fresh, storage = path.replace(".", "_"), None, True, None
+        else:
+            if not ref:
+                raise ValueError(f"layer '{path}' names no storage block")
+            key = remap.get(ref, ref)
+            desc = described.get(key)
+            if desc is not None and (desc["row_elements"], desc["num_rows"]) != (cols, rows):
+                raise ValueError(f"block '{key}' is {desc['num_rows']} x {desc['row_elements']} but layer '{path}' "
+                                 f"expects {rows} x {cols}: stale or hand-edited metadata?")
+            fresh = key not in registry
+            if fresh:
+                if desc is None:
+                    raise ValueError(f"storage_ref '{key}' is not among resources.memblocks")
+                registry[key] = _build_block(desc, device.index)
+            storage = registry[key]
         kwargs = dict(optimize_for_training=entry["optimize_for_training"], device=device, id=entry["id"],
-                      config=entry.get("config"), storage=registry[key])
+                      config=entry.get("config"), storage=storage)
         if kind == LayerType.LinearUVM:
             kwargs["gpu_cache_size"] = (entry["gpu_cache_size"] if gpu_cache_size_override is None
                                         else gpu_cache_size_override)

@@ -120,6 +120,37 @@ def test_config_and_block_names_for_metadata():
     assert pynve.resolve_memblock_devices(pynve.MemBlockType.NVL, 0, [2, 5]) == [2, 5]
 
 
+def test_metadata_rules_need_no_gpu(tmp_path):
+    """Which block replaces a caller-owned one, and what a loader refuses before it builds anything."""
+    import torch
+    from nv_embedding_cache_b200 import export as E, torch_layers as L
+    G, U = L.LayerType.GPULayer, L.LayerType.LinearUVM
+    assert E._block_kind_for({G}) == "Linear" and E._block_kind_for({G, U}) == "Linear"
+    assert E._block_kind_for({U}) == "Managed"
+    with pytest.raises(ValueError):
+        E._block_kind_for({L.LayerType.HostLayer})
+    where = torch.device("cuda", 0)
+    (tmp_path / "metadata.json").write_text(json.dumps({"version": 3, "resources": {}, "layers": []}))
+    with pytest.raises(RuntimeError, match="schema version 3"):
+        E.load_nve_layers(str(tmp_path), device=where)
+    entry = {"id": 1, "module_path": "emb", "num_embeddings": 10, "embedding_size": 4, "dtype": "float32",
+             "layer_type": "Hierarchical", "gpu_cache_size": 0, "optimize_for_training": False}
+    (tmp_path / "metadata.json").write_text(json.dumps({"version": 2, "resources": {}, "layers": [entry]}))
+    with pytest.raises(NotImplementedError, match="Hierarchical"):
+        E.load_nve_layers(str(tmp_path), device=where)
+    entry["layer_type"] = "GPULayer"
+    (tmp_path / "metadata.json").write_text(json.dumps({"version": 2, "resources": {}, "layers": [entry]}))
+    with pytest.raises(ValueError, match="names no storage block"):
+        E.load_nve_layers(str(tmp_path), device=where)
+    entry["storage_ref"] = "mb-1"
+    (tmp_path / "metadata.json").write_text(json.dumps({"version": 2, "resources": {"memblocks": {}},
+                                                        "layers": [entry]}))
+    with pytest.raises(ValueError, match="not among resources"):
+        E.load_nve_layers(str(tmp_path), device=where)
+    with pytest.raises(ValueError, match="layers of this library live on a cuda device"):
+        E.load_nve_layers(str(tmp_path), device=torch.device("cpu"))
+
+
 def _table(torch, rows, dim, dtype):
     g = torch.Generator(device="cuda").manual_seed(rows + dim)
     return (torch.randint(-64, 65, (rows, dim), generator=g, device="cuda") / 32.0).to(dtype)
@@ -323,3 +354,63 @@ def test_layers_that_share_a_block_are_saved_once_and_come_back_sharing(torch_cu
     (tmp_path / "metadata.json").write_text(json.dumps(doc))
     with pytest.raises(ValueError, match="stale or hand-edited"):
         E.load_nve_layers(str(tmp_path))
+
+
+@pytest.mark.gpu
+def test_one_export_loaded_twice_remapped_and_from_the_legacy_layout(torch_cuda, tmp_path):
+    """Two loads of one directory in one process give independent layers under their own markers;
+    `resource_remap` lets a second directory reuse a block of the first under another key; the layer
+    configuration survives the round trip; the flat metadata of schema 1 loads too."""
+    torch, L = _ops()
+    from nv_embedding_cache_b200 import export as E
+    rows, dim = 900, 16
+    w = _table(torch, rows, dim, torch.float16)
+
+    class One(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = L.NVEmbedding(rows, dim, torch.float16, L.LayerType.LinearUVM, gpu_cache_size=1 << 20,
+                                     weight_init=w, optimize_for_training=False, id=5,
+                                     config={"kernel_mode": 2, "kernel_mode_value_1": 512, "default_row_index": 3})
+
+        def forward(self, keys):
+            return self.emb(keys)
+
+    model = One().eval()
+    keys = torch.randint(0, rows, (128,), device="cuda")
+    want = model(keys)
+    E.export(model, (keys,), str(tmp_path / "a"))
+    m1, l1 = E.load(str(tmp_path / "a"))
+    m2, l2 = E.load(str(tmp_path / "a"))
+    assert l1[0].marker_tensor.data_ptr() != l2[0].marker_tensor.data_ptr()
+    assert torch.equal(m1(keys), want) and torch.equal(m2(keys), want)
+    cfg = l1[0].config
+    assert (cfg.kernel_mode, cfg.kernel_mode_value_1, cfg.default_row_index) == (2, 512, 3)
+    # keys past the table come back as the default row, through the loaded graph as well
+    beyond = torch.full((4,), rows + 7, dtype=torch.int64, device="cuda")
+    assert torch.equal(m1(beyond), w[3].expand(4, dim))
+    # an update through one loaded copy does not reach the other: they own separate blocks
+    l1[0].update(keys[:1], torch.zeros(1, dim, dtype=torch.float16, device="cuda"))
+    torch.cuda.synchronize()
+    assert torch.equal(m2(keys[:1]), want[:1]) and not torch.equal(m1(keys[:1]), want[:1])
+
+    # second directory, same block under another key: the registry entry of the first serves it
+    E.save_nve(model, str(tmp_path / "b"))
+    doc_a = json.loads((tmp_path / "a" / "metadata.json").read_text())
+    doc_b = json.loads((tmp_path / "b" / "metadata.json").read_text())
+    key_a, key_b = doc_a["layers"][0]["storage_ref"], doc_b["layers"][0]["storage_ref"]
+    registry = {}
+    (la,) = E.load_nve_layers(str(tmp_path / "a"), registry=registry)
+    (lb,) = E.load_nve_layers(str(tmp_path / "b"), registry=registry, resource_remap={key_b: key_a})
+    assert la.storage is lb.storage and list(registry) == [key_a]
+
+    # schema 1: a flat list, the table under the module path
+    legacy = [dict(doc_a["layers"][0])]
+    legacy[0].pop("storage_ref")
+    old = tmp_path / "v1"
+    (old / "weights").mkdir(parents=True)
+    (old / "metadata.json").write_text(json.dumps(legacy))
+    (old / "weights" / "emb.nve").write_bytes((tmp_path / "a" / "weights" / (key_a + ".nve")).read_bytes())
+    (lv1,) = E.load_nve_layers(str(old))
+    assert torch.equal(lv1(keys), want)
+
