@@ -379,7 +379,8 @@ def test_one_export_loaded_twice_remapped_and_from_the_legacy_layout(torch_cuda,
     model = One().eval()
     keys = torch.randint(0, rows, (128,), device="cuda")
     want = model(keys)
-    E.export(model, (keys,), str(tmp_path / "a"))
+    E.export(model, (keys,), str(tmp_path / "a"),
+             dynamic_shapes={"keys": {0: torch.export.Dim("n", min=2, max=4096)}})
     m1, l1 = E.load(str(tmp_path / "a"))
     m2, l2 = E.load(str(tmp_path / "a"))
     assert l1[0].marker_tensor.data_ptr() != l2[0].marker_tensor.data_ptr()
@@ -390,9 +391,10 @@ def test_one_export_loaded_twice_remapped_and_from_the_legacy_layout(torch_cuda,
     beyond = torch.full((4,), rows + 7, dtype=torch.int64, device="cuda")
     assert torch.equal(m1(beyond), w[3].expand(4, dim))
     # an update through one loaded copy does not reach the other: they own separate blocks
-    l1[0].update(keys[:1], torch.zeros(1, dim, dtype=torch.float16, device="cuda"))
+    first = keys[:2].contiguous()
+    l1[0].update(first, torch.zeros(2, dim, dtype=torch.float16, device="cuda"))
     torch.cuda.synchronize()
-    assert torch.equal(m2(keys[:1]), want[:1]) and not torch.equal(m1(keys[:1]), want[:1])
+    assert torch.equal(m2(first), want[:2]) and not torch.equal(m1(first), want[:2])
 
     # second directory, same block under another key: the registry entry of the first serves it
     E.save_nve(model, str(tmp_path / "b"))
