@@ -563,7 +563,7 @@ def touched_rows_mirror(keys_np: np.ndarray, width: int, seed: int):
 
 
 def sharded_record(steps=20, warmup=5, repeats=5, rows_per_rank=250_000_000, dim=64, bags=131_072, hot=8,
-                   sample_batches=20, hot_capacity=6_000_000, modes=("peer", "peer_hot", "alltoall_hot"),
+                   sample_batches=80, hot_capacity=20_000_000, modes=("peer", "peer_hot", "alltoall_hot"),
                    table_seed=60):
     """The NVLink-sharded configuration: one table of rows_per_rank x W rows x 64 fp16 (32 GB per
     GPU), row r on rank r mod W; per rank 131 072 bags x 8 int64 keys, Zipf(1.05) over a permuted row
@@ -611,7 +611,8 @@ def sharded_record(steps=20, warmup=5, repeats=5, rows_per_rank=250_000_000, dim
                        "per rank 131072 bags x 8 int64 keys, Zipf(1.05), sum pooled in fp32 -> fp16",
            "n_gpus": world, "rows_per_rank": rows_per_rank, "keys_per_step_per_rank": n,
            "unique_keys_per_rank": int(np.unique(keys_np[0]).size), "steps": steps, "repeats": repeats,
-           "setup_s": round(setup_s, 1), "scaling": "weak", "modes": {}}
+           "setup_s": round(setup_s, 1), "hot_sample_batches": sample_batches, "hot_capacity_rows": hot_capacity,
+           "scaling": "weak", "modes": {}}
     tables = {}
     with ClockSampler.for_current_device() as clk:
         for mode in modes:
@@ -665,7 +666,12 @@ def sharded_record(steps=20, warmup=5, repeats=5, rows_per_rank=250_000_000, dim
 
 def run_c5(root, steps=30, warmup=5, rows_per_rank=250_000_000, **kw):
     modes = tuple(os.environ.get("NVE_B200_SHARD_MODES", "peer,peer_hot,alltoall_hot,alltoall").split(","))
-    return sharded_record(steps=steps, warmup=warmup, rows_per_rank=rows_per_rank, modes=modes)
+    extra = {}
+    if os.environ.get("NVE_B200_SHARD_SAMPLE"):          # batches of the key sample the hot rows are chosen from
+        extra["sample_batches"] = int(os.environ["NVE_B200_SHARD_SAMPLE"])
+    if os.environ.get("NVE_B200_SHARD_HOT"):             # capacity of the hot-row table, in rows
+        extra["hot_capacity"] = int(os.environ["NVE_B200_SHARD_HOT"])
+    return sharded_record(steps=steps, warmup=warmup, rows_per_rank=rows_per_rank, modes=modes, **extra)
 
 
 # ---- records of the single-GPU configurations for bench.py's JSON line --------------------------------
