@@ -95,7 +95,12 @@ nve_status_t nve_abi_version(int32_t* major, int32_t* minor) {
 }
 
 // ---- thread pool: CPU worker pools are not part of the GPU hot path ----
-nve_status_t nve_thread_pool_create(nve_thread_pool_t*, const char*) { return not_impl("nve_thread_pool_create"); }
+// A creator that fails leaves NULL in *out, so that a caller never sees a stale handle (what the
+// reference's creators do on their failure paths, tests/c_api/c_api_handle_lifecycle_test.cpp:150-173).
+nve_status_t nve_thread_pool_create(nve_thread_pool_t* out, const char*) {
+  if (out) *out = nullptr;
+  return not_impl("nve_thread_pool_create");
+}
 nve_status_t nve_thread_pool_destroy(nve_thread_pool_t) { return not_impl("nve_thread_pool_destroy"); }
 nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t, int64_t*) { return not_impl("nve_thread_pool_num_workers"); }
 nve_status_t nve_configure_default_thread_pool(const char*) { return not_impl("nve_configure_default_thread_pool"); }
@@ -243,9 +248,15 @@ nve_status_t nve_b200_gpu_table_insert_from_backing(nve_table_t table, nve_conte
 }
 
 // ---- host-table plugins ----
-nve_status_t nve_create_table_factory(nve_table_factory_t*, const char*, const char*) { return not_impl("nve_create_table_factory"); }
+nve_status_t nve_create_table_factory(nve_table_factory_t* out, const char*, const char*) {
+  if (out) *out = nullptr;
+  return not_impl("nve_create_table_factory");
+}
 nve_status_t nve_table_factory_destroy(nve_table_factory_t) { return not_impl("nve_table_factory_destroy"); }
-nve_status_t nve_table_factory_produce(nve_table_factory_t, int64_t, const char*, nve_table_t*) { return not_impl("nve_table_factory_produce"); }
+nve_status_t nve_table_factory_produce(nve_table_factory_t, int64_t, const char*, nve_table_t* out) {
+  if (out) *out = nullptr;
+  return not_impl("nve_table_factory_produce");
+}
 
 // ---- layers ----
 nve_status_t nve_gpu_embedding_layer_create(nve_layer_t* out, nve_key_type_t key_type,
@@ -276,14 +287,16 @@ nve_status_t nve_linear_uvm_layer_create(nve_layer_t* out, nve_key_type_t key_ty
     *out = new nve_layer_s{nve_b200::make_linear_uvm_layer(*config, key_type, gpu_table->ptr), key_type};
   });
 }
-nve_status_t nve_hierarchical_layer_create(nve_layer_t*, nve_key_type_t,
+nve_status_t nve_hierarchical_layer_create(nve_layer_t* out, nve_key_type_t,
                                            const nve_hierarchical_layer_config_t*,
                                            const nve_table_t*, int64_t, nve_allocator_t) {
+  if (out) *out = nullptr;
   return not_impl("nve_hierarchical_layer_create");
 }
-nve_status_t nve_host_embedding_layer_create(nve_layer_t*, nve_key_type_t,
+nve_status_t nve_host_embedding_layer_create(nve_layer_t* out, nve_key_type_t,
                                              const nve_host_embedding_layer_config_t*, nve_table_t,
                                              nve_allocator_t) {
+  if (out) *out = nullptr;
   return not_impl("nve_host_embedding_layer_create");
 }
 nve_status_t nve_layer_destroy(nve_layer_t layer) {

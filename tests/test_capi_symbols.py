@@ -76,3 +76,28 @@ def test_kernel_level_entry_points_check_arguments_before_any_gpu_work(capi):
     assert capi.lib.nve_b200_scatter_rows(None, 64, None, 64, 64, None, 0, None) == 0   # zero rows: nothing to do
     assert capi.lib.nve_b200_scatter_rows(None, 64, None, 64, 64, None, 4, None) == inv
     assert "NULL" in capi.last_error()
+
+
+def test_failed_creators_leave_null_and_bad_key_types_are_rejected(capi):
+    """What the reference's tests/c_api/c_api_malformed_input_test.cpp:97-110 and
+    c_api_handle_lifecycle_test.cpp:150-173 ask of creators: an unsupported key type is an invalid
+    argument, and a creator that fails never leaves a stale handle behind."""
+    lib = capi.lib
+    cfg = lib.nve_gpu_table_config_default()
+    cfg.cache_size, cfg.row_size_in_bytes = 1 << 20, 128
+    table = C.c_void_p()
+    assert lib.nve_gpu_table_create(C.byref(table), 99, C.byref(cfg), None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    assert table.value is None and "Unsupported key type" in capi.last_error()
+    assert lib.nve_gpu_table_create(None, capi.KEY_INT64, C.byref(cfg), None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    assert lib.nve_gpu_table_create(C.byref(table), capi.KEY_INT64, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
+    for call in (lambda h: lib.nve_thread_pool_create(C.byref(h), b"{}"),
+                 lambda h: lib.nve_create_table_factory(C.byref(h), b"nonexistent_plugin_xyz.so", b"{}"),
+                 lambda h: lib.nve_table_factory_produce(None, 0, b"not valid json", C.byref(h)),
+                 lambda h: lib.nve_hierarchical_layer_create(C.byref(h), capi.KEY_INT64, None, None, 0, None),
+                 lambda h: lib.nve_host_embedding_layer_create(C.byref(h), capi.KEY_INT64, None, None, None)):
+        sentinel = C.c_void_p(1)
+        assert call(sentinel) == capi.NVE_ERROR_NOT_IMPLEMENTED
+        assert sentinel.value is None
+    # getters answer NULL handles and NULL outputs with a status, never a crash
+    for name in ("nve_table_get_device_id", "nve_table_get_max_row_size", "nve_table_get_key_size"):
+        assert getattr(lib, name)(None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
