@@ -416,3 +416,54 @@ def test_one_export_loaded_twice_remapped_and_from_the_legacy_layout(torch_cuda,
     (lv1,) = E.load_nve_layers(str(old))
     assert torch.equal(lv1(keys), want)
 
+
+
+@pytest.mark.gpu
+def test_ops_from_several_threads_and_streams(torch_cuda):
+    """Lookups through the registry run concurrently: four threads, each on a stream of its own,
+    against two layers, while a fifth thread registers and unregisters other layers."""
+    import threading
+    torch, L = _ops()
+    rows, dim = 5000, 32
+    w = [_table(torch, rows + i, dim, torch.float32)[:rows].contiguous() for i in range(2)]
+    layers = [L.NVEmbedding(rows, dim, torch.float32, L.LayerType.GPULayer, weight_init=w[i],
+                            optimize_for_training=False) for i in range(2)]
+    errors, stop = [], threading.Event()
+
+    def reader(tid):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            rng = np.random.default_rng(tid)
+            with torch.cuda.stream(stream):
+                for it in range(60):
+                    which = (tid + it) % 2
+                    keys = torch.from_numpy(rng.integers(0, rows, 777)).cuda(non_blocking=False)
+                    got = torch.ops.nve_ops.embedding_lookup(layers[which].marker_tensor, keys, dim,
+                                                             layers[which].dtype_tag)
+                    stream.synchronize()
+                    if not torch.equal(got, w[which][keys]):
+                        errors.append(f"thread {tid} iteration {it}: wrong rows")
+                        return
+        except Exception as e:                      # noqa: BLE001 - reported by the main thread
+            errors.append(f"thread {tid}: {e!r}")
+
+    def churn():
+        try:
+            torch.cuda.set_device(0)
+            while not stop.is_set():
+                tmp = L.NVEmbedding(64, 8, torch.float32, L.LayerType.GPULayer, optimize_for_training=False)
+                del tmp
+        except Exception as e:                      # noqa: BLE001
+            errors.append(f"churn: {e!r}")
+
+    threads = [threading.Thread(target=reader, args=(i,)) for i in range(4)]
+    side = threading.Thread(target=churn)
+    side.start()
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    stop.set()
+    side.join(60)
+    assert not errors, errors
