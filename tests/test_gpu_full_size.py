@@ -244,3 +244,31 @@ def test_c3_full_batch_cached_gather_matches_oracle_cache(torch_cuda, oracle):
         hit_rate = 1.0 - misses / batch
         assert (hit_rate > 0.8) if name == "zipf" else (hit_rate < 0.3), (name, hit_rate)
     gpu.close()
+
+
+def test_c1_host_layer_configuration_on_the_gpu(torch_cuda, oracle):
+    """The reference's CPU-runnable configuration with its own inputs: one table of 1 000 000 x 64
+    fp32 uniform[-0.05, 0.05] (seed 1), 8192 bags at a fixed pooling factor of 16, Zipf(1.05) keys over
+    a permuted row order, fp32 sums.  The dense layer on the GPU must give the oracle's bits (the
+    oracle is pinned to the reference's HostEmbeddingLayer on exactly this shape)."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import GPUEmbeddingLayer
+    rows, dim, bags, hot = 1_000_000, 64, 8192, 16
+    table_np = np.random.default_rng(1).uniform(-0.05, 0.05, (rows, dim)).astype(np.float32)
+    keys = dg.zipf_keys(bags * hot, rows, 1.05, 1000, dg.permutation(rows))
+    table = torch.from_numpy(table_np).cuda()
+    layer = GPUEmbeddingLayer(table, rows, dim * 4, "float32")
+    ctx = layer.create_execution_context()
+    out = torch.zeros((bags, dim), dtype=torch.float32, device="cuda")
+    layer.lookup_pooled(ctx, keys.size, to_dev(torch, keys), out, dim * 4, "sum", "float32", fixed_hotness=hot)
+    ctx.wait()
+    want = oracle.lookup_pooled(table_np.view(np.uint8).reshape(rows, -1), "f32", dim, keys, "sum", hotness=hot,
+                                out_dtype="f32")
+    got = out.cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # host buffers in, host buffer out: the call a CPU user of the reference layer makes
+    out_h = np.zeros((bags, dim), np.float32)
+    layer.lookup_pooled(ctx, keys.size, keys, out_h, dim * 4, "sum", "float32", fixed_hotness=hot)
+    ctx.wait()
+    assert np.array_equal(out_h.view(np.uint32), want.view(np.uint32))
+    ctx.destroy(); layer.destroy()

@@ -95,3 +95,20 @@ def test_gather_skips_out_of_range_and_honours_hit_mask(oracle):
     assert int(mask[0]) == 0b111001
     assert np.array_equal(out[0], t[3]) and np.array_equal(out[3], t[0]) and np.array_equal(out[4], t[9])
     assert (out[1] == -7).all() and (out[2] == -7).all() and (out[5] == -7).all()
+
+
+def test_c1_configuration_at_full_size_matches_live_reference(oracle, reference):
+    """The reference's CPU-runnable configuration with its own inputs and sizes: 1 000 000 x 64 fp32
+    uniform[-0.05, 0.05] (seed 1), 8192 bags x 16 Zipf(1.05) keys over a permuted row order, fp32
+    sums -- the oracle against the reference's HostEmbeddingLayer, every bit of all 8192 x 64 sums.
+    (The GPU test of the same configuration compares the library with the oracle.)"""
+    rows, dim, bags, hot = 1_000_000, 64, 8192, 16
+    table = np.random.default_rng(1).uniform(-0.05, 0.05, (rows, dim)).astype(np.float32)
+    keys = dg.zipf_keys(bags * hot, rows, 1.05, 1000, dg.permutation(rows))
+    tb = table.view(np.uint8).reshape(rows, -1)
+    a = oracle.lookup_pooled(tb, "f32", dim, keys, "sum", hotness=hot, out_dtype="f32")
+    layer = reference.layer(tb, "f32")
+    b = layer.lookup_pooled(keys, "sum", dim, hotness=hot, out_dtype="f32")
+    layer.close()
+    assert a.shape == (bags, dim)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
