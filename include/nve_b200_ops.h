@@ -2,7 +2,7 @@
  * nve_b200_ops.h — kernel-level C ABI of the B200 lookup hot path.
  *
  * These are the launchers the layer code in libnve_b200.so itself uses.  They correspond to the
- * reference's header-only device operators (cuda_ops/*.cuh and include/ecache/*.cuh), which a
+ * reference's header-only device operators (the .cuh files under cuda_ops/ and include/ecache/), which a
  * reference user calls as C++ templates; here each is one `extern "C"` launcher taking plain
  * device pointers, sizes and a cudaStream_t (cast to void*).  All pointers are DEVICE-accessible
  * unless a parameter says otherwise; nothing here allocates unless it says so.  Every launcher
