@@ -200,7 +200,10 @@ NVE_C_API nve_host_table_config_t nve_host_table_config_default(void);
 NVE_C_API nve_status_t nve_version(int32_t* major, int32_t* minor, int32_t* patch);
 NVE_C_API nve_status_t nve_abi_version(int32_t* major, int32_t* minor);
 
-/* ---- thread pool (reference :311-333): outside the hot path, NOT_IMPLEMENTED ---- */
+/* ---- thread pool (reference :311-333).  config_json is a JSON object such as
+ * {"name": "simple", "num_workers": 3}; the threads serve the host half of the pipeline-gather lookup
+ * schedule of the execution contexts created with the pool (NULL there = the process-wide default pool,
+ * which nve_configure_default_thread_pool sizes until it is first used). ---- */
 NVE_C_API nve_status_t nve_thread_pool_create(nve_thread_pool_t* out, const char* json_config);
 NVE_C_API nve_status_t nve_thread_pool_destroy(nve_thread_pool_t pool);
 NVE_C_API nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t pool, int64_t* out);

@@ -1,5 +1,9 @@
 // The C ABI of include/nve_c_api.h: opaque handles over the C++ layer / table objects, argument
 // checks at the boundary, exception -> status translation, thread-local last error.
+#include <cctype>
+#include <cstring>
+
+#include "host_workers.hpp"
 #include "layers.hpp"
 #include "ops_internal.hpp"
 #include "tables.hpp"
@@ -7,7 +11,7 @@
 struct nve_context_s { nve_b200::context_ptr_t ptr; };
 struct nve_table_s { std::shared_ptr<nve_b200::Table> ptr; nve_key_type_t key_type; };
 struct nve_layer_s { std::shared_ptr<nve_b200::EmbeddingLayer> ptr; nve_key_type_t key_type; };
-struct nve_thread_pool_s { int unused; };
+struct nve_thread_pool_s { std::shared_ptr<nve_b200::HostWorkers> pool; };
 struct nve_allocator_s { int unused; };
 struct nve_table_factory_s { int unused; };
 
@@ -19,6 +23,140 @@ nve_status_t bad_arg(const char* msg) { return set_last_error(NVE_ERROR_INVALID_
 nve_status_t not_impl(const char* what) {
   return set_last_error(NVE_ERROR_NOT_IMPLEMENTED,
                         std::string(what) + " is outside the lookup hot path and not provided by libnve_b200");
+}
+
+// ---- thread-pool configuration: a JSON object such as {"name": "simple", "num_workers": 3}
+// (reference src/thread_pool.cpp: the name picks an implementation there; here every name means the
+// same pool).  A small validating reader: the whole text must be one well-formed JSON value, it must
+// be an object, and "num_workers", when present at the top level, a non-negative integer.
+class JsonReader {
+ public:
+  explicit JsonReader(const char* text) : p_(text) {}
+
+  // Parses the text; returns false with a message when it is not a well-formed JSON object.
+  bool read_config(int64_t* num_workers, std::string* why) {
+    try {
+      skip();
+      if (*p_ != '{') fail("a thread-pool configuration must be a JSON object");
+      object(/*top=*/true);
+      skip();
+      if (*p_ != '\0') fail("trailing characters after the JSON object");
+    } catch (const std::runtime_error& e) {
+      *why = e.what();
+      return false;
+    }
+    *num_workers = num_workers_;
+    return true;
+  }
+
+ private:
+  [[noreturn]] void fail(const char* what) { throw std::runtime_error(what); }
+  void skip() {
+    while (*p_ == ' ' || *p_ == '\t' || *p_ == '\n' || *p_ == '\r') p_++;
+  }
+  std::string string() {
+    if (*p_ != '"') fail("malformed JSON: expected a string");
+    p_++;
+    std::string out;
+    while (*p_ != '"') {
+      if (*p_ == '\0') fail("malformed JSON: unterminated string");
+      if (*p_ == '\\') {
+        p_++;
+        if (*p_ == '\0') fail("malformed JSON: unterminated escape");
+      }
+      out.push_back(*p_++);
+    }
+    p_++;
+    return out;
+  }
+  bool number(double* value) {
+    char* end = nullptr;
+    *value = std::strtod(p_, &end);
+    if (end == p_) return false;
+    p_ = end;
+    return true;
+  }
+  void literal(const char* word) {
+    const size_t n = std::strlen(word);
+    if (std::strncmp(p_, word, n) != 0) fail("malformed JSON: unknown literal");
+    p_ += n;
+  }
+  void value(bool top, const std::string& key) {
+    skip();
+    if (*p_ == '{') {
+      object(false);
+    } else if (*p_ == '[') {
+      p_++;
+      skip();
+      if (*p_ == ']') {
+        p_++;
+        return;
+      }
+      for (;;) {
+        value(false, "");
+        skip();
+        if (*p_ == ',') {
+          p_++;
+          continue;
+        }
+        if (*p_ == ']') {
+          p_++;
+          return;
+        }
+        fail("malformed JSON: expected ',' or ']'");
+      }
+    } else if (*p_ == '"') {
+      (void)string();
+      if (top && key == "num_workers") fail("num_workers must be an integer");
+    } else if (*p_ == 't') {
+      literal("true");
+    } else if (*p_ == 'f') {
+      literal("false");
+    } else if (*p_ == 'n') {
+      literal("null");
+    } else {
+      double v = 0;
+      if (!number(&v)) fail("malformed JSON: expected a value");
+      if (top && key == "num_workers") {
+        if (v < 0 || v != static_cast<double>(static_cast<int64_t>(v))) fail("num_workers must be a non-negative integer");
+        num_workers_ = static_cast<int64_t>(v);
+      }
+    }
+  }
+  void object(bool top) {
+    p_++;   // '{'
+    skip();
+    if (*p_ == '}') {
+      p_++;
+      return;
+    }
+    for (;;) {
+      skip();
+      const std::string key = string();
+      skip();
+      if (*p_ != ':') fail("malformed JSON: expected ':'");
+      p_++;
+      value(top, key);
+      skip();
+      if (*p_ == ',') {
+        p_++;
+        continue;
+      }
+      if (*p_ == '}') {
+        p_++;
+        return;
+      }
+      fail("malformed JSON: expected ',' or '}'");
+    }
+  }
+
+  const char* p_;
+  int64_t num_workers_ = -1;   // -1: not given
+};
+
+int default_worker_count() {
+  const int hw = static_cast<int>(std::thread::hardware_concurrency());
+  return std::max(hw - 2, 1);   // the reference's default (src/thread_pool.cpp:112-116)
 }
 }  // namespace
 
@@ -95,15 +233,47 @@ nve_status_t nve_abi_version(int32_t* major, int32_t* minor) {
 }
 
 // ---- thread pool: CPU worker pools are not part of the GPU hot path ----
-// A creator that fails leaves NULL in *out, so that a caller never sees a stale handle (what the
-// reference's creators do on their failure paths, tests/c_api/c_api_handle_lifecycle_test.cpp:150-173).
-nve_status_t nve_thread_pool_create(nve_thread_pool_t* out, const char*) {
-  if (out) *out = nullptr;
-  return not_impl("nve_thread_pool_create");
+// Thread pools (reference include/nve_c_api.h:311-333, src/nve_c_api_util.cpp): host threads that an
+// execution context uses for the host half of the pipeline-gather lookup schedule.  A creator that
+// fails leaves NULL in *out, so that a caller never sees a stale handle (what the reference's creators
+// do on their failure paths, tests/c_api/c_api_handle_lifecycle_test.cpp:150-173).
+nve_status_t nve_thread_pool_create(nve_thread_pool_t* out, const char* config_json) {
+  if (!out) return bad_arg("out must not be NULL");
+  *out = nullptr;
+  if (!config_json) return bad_arg("config_json must not be NULL");
+  int64_t workers = -1;
+  std::string why;
+  if (!JsonReader(config_json).read_config(&workers, &why)) return bad_arg(why.c_str());
+  if (workers > 1024) return bad_arg("num_workers is unreasonably large");
+  return guarded([&] {
+    const int n = workers >= 0 ? static_cast<int>(workers) : default_worker_count();
+    *out = new nve_thread_pool_s{std::make_shared<nve_b200::HostWorkers>(n)};
+  });
 }
-nve_status_t nve_thread_pool_destroy(nve_thread_pool_t) { return not_impl("nve_thread_pool_destroy"); }
-nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t, int64_t*) { return not_impl("nve_thread_pool_num_workers"); }
-nve_status_t nve_configure_default_thread_pool(const char*) { return not_impl("nve_configure_default_thread_pool"); }
+nve_status_t nve_thread_pool_destroy(nve_thread_pool_t pool) {
+  if (!pool) return bad_arg("thread pool must not be NULL");
+  delete pool;   // contexts created with it keep the threads alive until they are destroyed
+  return NVE_SUCCESS;
+}
+nve_status_t nve_thread_pool_num_workers(nve_thread_pool_t pool, int64_t* out) {
+  if (!pool || !pool->pool || !out) return bad_arg("thread pool and out must not be NULL");
+  *out = pool->pool->workers();
+  return NVE_SUCCESS;
+}
+// Size of the process-wide default pool; refused once that pool exists (the reference throws in the
+// same situation, tests/c_api/c_api_threadpool_test.cpp:72-104).
+nve_status_t nve_configure_default_thread_pool(const char* config_json) {
+  if (!config_json) return bad_arg("config_json must not be NULL");
+  int64_t workers = -1;
+  std::string why;
+  if (!JsonReader(config_json).read_config(&workers, &why)) return bad_arg(why.c_str());
+  if (workers > 1024) return bad_arg("num_workers is unreasonably large");
+  const int n = workers >= 0 ? static_cast<int>(workers) : default_worker_count();
+  if (!nve_b200::HostWorkers::configure_default(n)) {
+    return set_last_error(NVE_ERROR_RUNTIME, "the default thread pool is already in use and cannot be reconfigured");
+  }
+  return NVE_SUCCESS;
+}
 
 // ---- insert heuristics (used by the cached layer's automatic cache population) ----
 nve_status_t nve_heuristic_create_default(nve_heuristic_t* out, const float* thresholds,
@@ -196,11 +366,12 @@ nve_status_t nve_table_erase(nve_table_t table, nve_context_t ctx, int64_t n, co
 }
 nve_status_t nve_table_create_execution_context(nve_table_t table, nve_context_t* out,
                                                 void* lookup_stream, void* modify_stream,
-                                                nve_thread_pool_t, nve_allocator_t) {
+                                                nve_thread_pool_t thread_pool, nve_allocator_t) {
   if (!table || !table->ptr || !out) return bad_arg("table and out must not be NULL");
   return guarded([&] {
     *out = new nve_context_s{table->ptr->create_execution_context(
         static_cast<cudaStream_t>(lookup_stream), static_cast<cudaStream_t>(modify_stream))};
+    if (thread_pool && thread_pool->pool) (*out)->ptr->set_host_workers(thread_pool->pool);
   });
 }
 nve_status_t nve_table_get_device_id(const nve_table_t table, int32_t* out) {
@@ -373,11 +544,12 @@ nve_status_t nve_layer_erase(nve_layer_t layer, nve_context_t ctx, int64_t num_k
 }
 nve_status_t nve_layer_create_execution_context(nve_layer_t layer, nve_context_t* out,
                                                 void* lookup_stream, void* modify_stream,
-                                                nve_thread_pool_t, nve_allocator_t) {
+                                                nve_thread_pool_t thread_pool, nve_allocator_t) {
   if (!layer || !layer->ptr || !out) return bad_arg("layer and out must not be NULL");
   return guarded([&] {
     *out = new nve_context_s{layer->ptr->create_execution_context(
         static_cast<cudaStream_t>(lookup_stream), static_cast<cudaStream_t>(modify_stream))};
+    if (thread_pool && thread_pool->pool) (*out)->ptr->set_host_workers(thread_pool->pool);
   });
 }
 nve_status_t nve_layer_get_num_tables(nve_layer_t layer, int64_t* out) {

@@ -20,6 +20,8 @@ namespace nve_b200 {
 
 class ContextRegistry;
 
+class HostWorkers;
+
 class ExecutionContext {
  public:
   ExecutionContext(int device, cudaStream_t lookup_stream, cudaStream_t modify_stream,
@@ -42,12 +44,17 @@ class ExecutionContext {
   // Blocks until both streams are idle.
   void wait();
 
+  // Host thread pool handed to nve_*_create_execution_context (null: the process-wide default).
+  void set_host_workers(std::shared_ptr<HostWorkers> pool) { host_workers_ = std::move(pool); }
+  HostWorkers* host_workers() const { return host_workers_.get(); }
+
  private:
   struct Buffer {
     void* ptr = nullptr;
     size_t bytes = 0;
     bool host = false;
   };
+  std::shared_ptr<HostWorkers> host_workers_;
   int device_;
   cudaStream_t lookup_stream_;
   cudaStream_t modify_stream_;

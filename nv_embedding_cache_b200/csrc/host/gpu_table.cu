@@ -339,7 +339,10 @@ class GpuTable : public Table {
       const PipelineBufferFn buffer = [&c](const char* name, size_t bytes, bool pinned) {
         return c.scratch(name, bytes, pinned);
       };
-      if (gather_rows_pipeline(g, cfg_.invalid_key, pipeline_.task_size, pipeline_res_, buffer, s)) return;
+      if (gather_rows_pipeline(g, cfg_.invalid_key, pipeline_.task_size, pipeline_res_, buffer, s,
+                               c.host_workers())) {
+        return;
+      }
     }
     if (cfg_.uvm_table != nullptr && lookup_schedule(n) == NVE_KERNEL_SORT_GATHER) {
       // two-call protocol of the sort-gather schedule: size the scratch, then run

@@ -1,7 +1,10 @@
-// A small process-wide pool of host threads for the host half of the pipeline-gather schedule
-// (the reference takes these from the execution context's thread pool,
-// cuda_ops/pipeline_gather.cuh:188-262).  One parallel_for runs at a time; the calling thread works
-// alongside the pool.  Size: NVE_B200_HOST_WORKERS, else the hardware concurrency, at most 32.
+// Pools of host threads for the host half of the pipeline-gather schedule (the reference takes
+// these from the execution context's thread pool, cuda_ops/pipeline_gather.cuh:188-262).  One
+// parallel_for runs at a time per pool; the calling thread works alongside the pool's threads.
+// The process-wide default pool has NVE_B200_HOST_WORKERS threads, else what
+// nve_configure_default_thread_pool asked for, else the hardware concurrency, at most 32; a pool
+// made through nve_thread_pool_create has the number of workers its configuration names and is used
+// by the execution contexts created with it.
 #pragma once
 
 #include <atomic>
@@ -18,9 +21,25 @@ namespace nve_b200 {
 class HostWorkers {
  public:
   static HostWorkers& instance() {
-    static HostWorkers pool;
+    static HostWorkers pool(default_size(/*lock=*/true));
     return pool;
   }
+
+  // `workers` threads besides the caller of parallel_for.
+  explicit HostWorkers(int workers) {
+    for (int i = 0; i < workers; i++) threads_.emplace_back([this] { loop(); });
+  }
+
+  // Size of the default pool.  configure_default() may change it until the pool exists.
+  static bool configure_default(int workers) {
+    std::lock_guard<std::mutex> lock(config_mu());
+    if (default_locked()) return false;
+    configured_workers() = workers;
+    return true;
+  }
+
+  // Worker threads of this pool (the reference's num_workers).
+  int workers() const { return static_cast<int>(threads_.size()); }
 
   // Threads that work on a parallel_for, the caller included.
   int size() const { return static_cast<int>(threads_.size()) + 1; }
@@ -50,15 +69,6 @@ class HostWorkers {
   HostWorkers(const HostWorkers&) = delete;
   HostWorkers& operator=(const HostWorkers&) = delete;
 
- private:
-  HostWorkers() {
-    int n = static_cast<int>(std::thread::hardware_concurrency());
-    if (const char* env = std::getenv("NVE_B200_HOST_WORKERS")) n = std::atoi(env);
-    if (n < 1) n = 1;
-    if (n > 32) n = 32;
-    for (int i = 0; i + 1 < n; i++) threads_.emplace_back([this] { loop(); });
-  }
-
   ~HostWorkers() {
     {
       std::lock_guard<std::mutex> lock(mu_);
@@ -66,6 +76,31 @@ class HostWorkers {
     }
     wake_.notify_all();
     for (auto& t : threads_) t.join();
+  }
+
+ private:
+  static std::mutex& config_mu() {
+    static std::mutex m;
+    return m;
+  }
+  static int& configured_workers() {
+    static int n = -1;
+    return n;
+  }
+  static bool& default_locked() {
+    static bool locked = false;
+    return locked;
+  }
+  // threads of the default pool besides the caller
+  static int default_size(bool lock) {
+    std::lock_guard<std::mutex> guard(config_mu());
+    if (lock) default_locked() = true;
+    int n = static_cast<int>(std::thread::hardware_concurrency());
+    if (configured_workers() >= 0) n = configured_workers() + 1;
+    if (const char* env = std::getenv("NVE_B200_HOST_WORKERS")) n = std::atoi(env);
+    if (n < 1) n = 1;
+    if (n > 32) n = 32;
+    return n - 1;
   }
 
   void drain() {

@@ -370,7 +370,8 @@ bool gather_rows_sorted(const nve_b200_gather_args_t& a, int64_t sentinel_tag, i
 }
 
 bool gather_rows_pipeline(const nve_b200_gather_args_t& a, int64_t sentinel_tag, uint64_t task_size,
-                          PipelineResources& res, const PipelineBufferFn& buffer, cudaStream_t stream) {
+                          PipelineResources& res, const PipelineBufferFn& buffer, cudaStream_t stream,
+                          HostWorkers* pool) {
   NVE_B200_ARG(a.num_keys >= 0, "gather_rows_pipeline: negative key count");
   if (a.num_keys == 0) return true;
   GatherKernelParams p{};
@@ -412,7 +413,7 @@ bool gather_rows_pipeline(const nve_b200_gather_args_t& a, int64_t sentinel_tag,
     auto* h_rows = static_cast<uint8_t*>(buffer("pipeline_rows", size_t(from_table) * row, true));
     NVE_B200_CUDA(cudaMemcpyAsync(h_words, sorted, size_t(from_table) * 8, cudaMemcpyDeviceToHost, stream));
     NVE_B200_CUDA(cudaEventRecord(res.words, stream));
-    HostWorkers& workers = HostWorkers::instance();
+    HostWorkers& workers = pool != nullptr ? *pool : HostWorkers::instance();
     int64_t per_task = (from_table + workers.size() - 1) / workers.size();
     if (task_size > 0 && static_cast<int64_t>(task_size) < per_task) per_task = static_cast<int64_t>(task_size);
     const int64_t tasks = (from_table + per_task - 1) / per_task;

@@ -43,8 +43,11 @@ using PipelineBufferFn = std::function<void*(const char*, size_t, bool)>;
 // until everything is enqueued; `stream` ends up ordered after all of it.  Returns false (nothing
 // done) for a decoding lookup, a probe-only call, a table in device memory, or a layout that does
 // not fit the sort word.
+class HostWorkers;
+// `pool`: the host threads that stage table rows (null: the process-wide default pool).
 bool gather_rows_pipeline(const nve_b200_gather_args_t& args, int64_t sentinel_tag, uint64_t task_size,
-                          PipelineResources& res, const PipelineBufferFn& buffer, cudaStream_t stream);
+                          PipelineResources& res, const PipelineBufferFn& buffer, cudaStream_t stream,
+                          HostWorkers* pool = nullptr);
 void update_rows(void* table, int64_t num_rows, int64_t row_stride, nve_data_type_t value_dtype,
                  int64_t row_bytes, nve_key_type_t key_type, const void* keys, int64_t num_keys,
                  const void* values, int64_t value_stride, bool accumulate, bool keys_unique,

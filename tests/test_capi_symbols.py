@@ -48,7 +48,7 @@ def test_null_handles_are_invalid_argument(capi):
     assert capi.lib.nve_table_find(None, None, 0, None, None, 0, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
     assert capi.lib.nve_version(None, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
     out = C.c_void_p()
-    assert capi.lib.nve_thread_pool_create(C.byref(out), b"{}") == capi.NVE_ERROR_NOT_IMPLEMENTED
+    assert capi.lib.nve_create_table_factory(C.byref(out), b"plugin.so", b"{}") == capi.NVE_ERROR_NOT_IMPLEMENTED
     assert capi.lib.nve_gpu_embedding_layer_create(None, 1, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
 
 
@@ -90,8 +90,7 @@ def test_failed_creators_leave_null_and_bad_key_types_are_rejected(capi):
     assert table.value is None and "Unsupported key type" in capi.last_error()
     assert lib.nve_gpu_table_create(None, capi.KEY_INT64, C.byref(cfg), None) == capi.NVE_ERROR_INVALID_ARGUMENT
     assert lib.nve_gpu_table_create(C.byref(table), capi.KEY_INT64, None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
-    for call in (lambda h: lib.nve_thread_pool_create(C.byref(h), b"{}"),
-                 lambda h: lib.nve_create_table_factory(C.byref(h), b"nonexistent_plugin_xyz.so", b"{}"),
+    for call in (lambda h: lib.nve_create_table_factory(C.byref(h), b"nonexistent_plugin_xyz.so", b"{}"),
                  lambda h: lib.nve_table_factory_produce(None, 0, b"not valid json", C.byref(h)),
                  lambda h: lib.nve_hierarchical_layer_create(C.byref(h), capi.KEY_INT64, None, None, 0, None),
                  lambda h: lib.nve_host_embedding_layer_create(C.byref(h), capi.KEY_INT64, None, None, None)):
@@ -101,3 +100,33 @@ def test_failed_creators_leave_null_and_bad_key_types_are_rejected(capi):
     # getters answer NULL handles and NULL outputs with a status, never a crash
     for name in ("nve_table_get_device_id", "nve_table_get_max_row_size", "nve_table_get_key_size"):
         assert getattr(lib, name)(None, None) == capi.NVE_ERROR_INVALID_ARGUMENT
+
+
+def test_thread_pool_lifecycle_and_malformed_configurations(capi):
+    """After the reference's tests/c_api/c_api_threadpool_test.cpp: create with a valid configuration,
+    num_workers reports it, destroy succeeds; malformed JSON and non-object JSON are statuses, not
+    exceptions; NULL arguments are invalid."""
+    lib, inv = capi.lib, capi.NVE_ERROR_INVALID_ARGUMENT
+    pool = C.c_void_p()
+    assert lib.nve_thread_pool_create(C.byref(pool), b'{"name": "simple", "num_workers": 3}') == 0
+    assert pool.value
+    n = C.c_int64(-1)
+    assert lib.nve_thread_pool_num_workers(pool, C.byref(n)) == 0 and n.value == 3
+    assert lib.nve_thread_pool_num_workers(None, C.byref(n)) == inv
+    assert lib.nve_thread_pool_num_workers(pool, None) == inv
+    assert lib.nve_thread_pool_destroy(pool) == 0
+    assert lib.nve_thread_pool_destroy(None) == inv
+    for bad in (b"{not valid json", b"[1, 2, 3]", b"42", b'{"num_workers": "three"}', b'{"num_workers": -1}',
+                b'{"num_workers": 2.5}', b'{"num_workers": 3} trailing', b'{"a": [1, 2,}'):
+        h = C.c_void_p(1)
+        assert lib.nve_thread_pool_create(C.byref(h), bad) == inv, bad
+        assert h.value is None
+    assert lib.nve_thread_pool_create(None, b"{}") == inv
+    assert lib.nve_thread_pool_create(C.byref(pool), None) == inv
+    # nested values and escapes are read past; without num_workers the pool takes the default size
+    ok = b'{"name": "simple \\"quoted\\"", "extra": {"list": [1, 2.5e3, true, null, {"x": []}]}}'
+    assert lib.nve_thread_pool_create(C.byref(pool), ok) == 0
+    assert lib.nve_thread_pool_num_workers(pool, C.byref(n)) == 0 and n.value >= 1
+    assert lib.nve_thread_pool_destroy(pool) == 0
+    assert lib.nve_configure_default_thread_pool(b"{oops") == inv
+    assert lib.nve_configure_default_thread_pool(None) == inv

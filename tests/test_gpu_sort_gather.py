@@ -224,6 +224,42 @@ def test_pipeline_schedule_repeated_and_device_table(torch_cuda):
         gt.destroy()
 
 
+def test_pipeline_schedule_with_a_thread_pool_of_the_callers(torch_cuda):
+    """An execution context created with a pool from nve_thread_pool_create stages its table rows
+    on that pool's threads (one worker, then five); outputs are those of the default pool.  The pool
+    handle may be destroyed while a context still uses it.  Once the default pool has served a
+    lookup it can no longer be re-sized (the reference refuses the same,
+    tests/c_api/c_api_threadpool_test.cpp:72-104)."""
+    torch = torch_cuda
+    from nv_embedding_cache_b200.layers import ExecutionContext, GpuTable
+    rows, rb = 6000, 128
+    table = np.random.default_rng(23).integers(0, 256, (rows, rb), dtype=np.uint8)
+    backing = torch.from_numpy(table).pin_memory()
+    gt = GpuTable(256 * (64 + 8 * rb + 32), rb, "float16", uvm_table=backing, uvm_num_rows=rows, kernel_mode_type=3)
+    keys = dg.zipf_keys(20000, rows, 1.05, 77, dg.permutation(rows))
+    default_ctx = gt.create_execution_context()
+    want = np.zeros((keys.size, rb), np.uint8)
+    gt.find(default_ctx, keys.size, keys, None, rb, want)
+    default_ctx.wait()
+    assert np.array_equal(want, table[keys])
+    for workers in (1, 5):
+        pool = C.c_void_p()
+        capi.check(capi.lib.nve_thread_pool_create(C.byref(pool), b'{"name": "simple", "num_workers": %d}' % workers))
+        h = C.c_void_p()
+        capi.check(capi.lib.nve_table_create_execution_context(gt.handle, C.byref(h), None, None, pool, None))
+        capi.check(capi.lib.nve_thread_pool_destroy(pool))          # the context keeps the threads
+        ctx = ExecutionContext(h)
+        out = np.zeros((keys.size, rb), np.uint8)
+        gt.find(ctx, keys.size, keys, None, rb, out)
+        ctx.wait()
+        assert np.array_equal(out, want)
+        ctx.destroy()
+    assert capi.lib.nve_configure_default_thread_pool(b'{"name": "simple", "num_workers": 2}') == capi.NVE_ERROR_RUNTIME
+    assert "already in use" in capi.last_error()
+    default_ctx.destroy()
+    gt.destroy()
+
+
 def test_rejections(torch_cuda):
     torch = torch_cuda
     table = np.zeros((10, 64), np.uint8)
