@@ -3,6 +3,7 @@
 
 #include "../common.hpp"
 #include "device_common.cuh"
+#include "modify_entry.hpp"
 
 namespace nve_b200 {
 
@@ -21,14 +22,6 @@ struct SetHash {
   uint64_t magic;
   uint32_t shift;
   uint32_t num_sets;
-};
-
-// One pending change of a cache line (reference ModifyEntry,
-// include/ecache/ec_set_associative.h:127-134).
-struct ModifyEntry {
-  const uint8_t* src;  // row payload (new row, or update to add)
-  uint64_t line;       // set * 8 + way
-  int64_t tag;         // tag to commit
 };
 
 size_t cache_insert_scratch_bytes(nve_key_type_t key_type, int64_t n);
