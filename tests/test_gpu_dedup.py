@@ -156,3 +156,21 @@ def test_fused_reduce_and_update_matches_cpu_update(torch_cuda, oracle):
     np.add.at(exact, keys[ok], -0.01 * grads[ok].astype(np.float64))
     assert np.max(np.abs(got - exact) / np.maximum(np.abs(exact), 1e-3)) <= 1e-6 * 10
     d.close()
+
+
+@pytest.mark.parametrize("switch", ["NVE_B200_DEDUP_LIBRARY_SORT", "NVE_B200_DEDUP_SPLIT_EMIT"])
+def test_alternative_paths_give_the_same_results(torch_cuda, switch):
+    """The de-duplication has two switches that are read once per process: the toolkit's sort instead
+    of this library's, and the six launches after the sort instead of the one kernel.  Both forms
+    stay tested: the known-answer cases of this file run again in a child process under each."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get(switch):
+        pytest.skip("already running under this switch")
+    here = os.path.abspath(__file__)
+    res = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-m", "gpu", "-k", "kats or grad_sums",
+                          "-p", "no:cacheprovider"],
+                         env=dict(os.environ, **{switch: "1"}), capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-1000:]
+    assert " passed" in res.stdout and " failed" not in res.stdout
